@@ -1,0 +1,515 @@
+// Host orchestration of the boosting loop: every launch of a round is queued on one stream and
+// nothing in boost() waits for the device, so the level loop never round-trips through the host
+// (the reference synchronises after every launch, include/thundergbm/util/device_lambda.cuh:49).
+#include "tgbm_booster.h"
+
+#include <cub/cub.cuh>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
+#include "tgbm_kernels.cuh"
+#include "tgbm_rank.cuh"
+
+namespace tgbm {
+
+struct BoosterImpl {
+    GBMParam p;
+    const Comm *comm = nullptr;
+    cudaStream_t stream = nullptr;
+    int objective = REG_LINEAR;
+    int N = 0, F = 0, Fpad = 0, G = 0, B = 0, K = 1, n_nodes = 0, depth = 0;
+    long long N_global = 0;
+    long long row_offset = 0;  // global id of local row 0
+    size_t Npad = 0;
+    int num_class = 1;
+    float base_score = 0;
+    int rounds = 0;
+    int num_sms = 148;
+    int window_rows = 0;
+    bool profile_on = false;
+
+    std::vector<float> h_cut_val;
+    std::vector<int> h_cut_ptr;
+    std::vector<float> label;
+
+    DevBuf<unsigned char> bins, binsT;
+    DevBuf<float> cut_val, y, ypred, metric;
+    DevBuf<int> cut_ptr, cut_fid;
+    DevBuf<float2> gh;
+    DevBuf<int2> ghq;
+    DevBuf<unsigned> maxbits;
+    DevBuf<unsigned long long> root_sum;
+    DevBuf<QuantInfo> qinfo, qinfo_log;
+    DevBuf<TreeNode> nodes, model;
+    DevBuf<int> rec_idx[2];
+    DevBuf<int2> rec_gh[2];
+    DevBuf<int> seg_begin[2], seg_cnt[2], gcnt;
+    DevBuf<int> done_idx, done_nid, nid_keep;
+    DevBuf<long long> hist_full, hist_built;
+    DevBuf<int> built_right, hist_tile_base;
+    DevBuf<HistWork> hist_work;
+    DevBuf<SplitRec> recs;
+    DevBuf<int> tile_node, tile_start, node_tile0, tile_left, node_done_base;
+    DevBuf<unsigned> bits;
+    DevBuf<TreeCtl> ctl;
+    DevBuf<double> metric_partial, metric_sum;
+    int max_tiles = 0;
+    RankState rank;
+
+    struct TimedEvent { cudaEvent_t a, b; int kind; };
+    std::vector<TimedEvent> events;
+    long long launches = 0;
+
+    ~BoosterImpl() {
+        for (auto &e : events) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
+        if (stream) cudaStreamDestroy(stream);
+    }
+
+    // ---------------------------------------------------------------- init helpers
+    void find_cuts_and_bins(const DataSet &ds);
+    void init_base_score();
+    void gradient(int round);
+    void build_tree(int round, int k);
+    void round_metric(int round);
+    size_t full_offset(int level) const { return ((size_t)(1 << level) - 1) * B * 2; }
+};
+
+static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ------------------------------------------------------------------------------------------------
+// Cut points (HistCut::get_cut_points_single, src/thundergbm/hist_cut.cu:205-286) and the bin matrix.
+// Radix sort of (feature, value) keys and DeviceSelect::Unique come from CUB; this runs once, before
+// the boosting loop.  With several ranks every rank contributes its distinct keys and all ranks
+// derive identical cut points from the union, so the bins equal the single-GPU ones.
+void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
+    const size_t nnz = (size_t)ds.row_ptr[N];
+    DevBuf<int> d_row_ptr, d_col;
+    DevBuf<float> d_val;
+    d_row_ptr.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1));
+    TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.row_ptr.data(), sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.col.data(), sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.val.data(), sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
+
+    long long nu = 0;
+    DevBuf<unsigned long long> ukeys;
+    {
+        DevBuf<unsigned long long> keys, keys2;
+        DevBuf<long long> d_nu;
+        keys.alloc(std::max<size_t>(nnz, 1)); keys2.alloc(std::max<size_t>(nnz, 1)); d_nu.alloc(1);
+        auto sort_unique = [&](size_t n) -> long long {  // keys -> keys (sorted distinct), returns the count
+            if (n == 0) return 0;
+            size_t tb = 0;
+            int end_bit = 32;
+            while ((1ll << (end_bit - 32)) < F && end_bit < 64) ++end_bit;
+            cub::DeviceRadixSort::SortKeys(nullptr, tb, keys.p, keys2.p, (long long)n, 0, end_bit, stream);
+            DevBuf<unsigned char> tmp;
+            tmp.alloc(tb);
+            cub::DeviceRadixSort::SortKeys(tmp.p, tb, keys.p, keys2.p, (long long)n, 0, end_bit, stream);
+            size_t tb2 = 0;
+            cub::DeviceSelect::Unique(nullptr, tb2, keys2.p, keys.p, d_nu.p, (long long)n, stream);
+            DevBuf<unsigned char> tmp2;
+            tmp2.alloc(tb2);
+            cub::DeviceSelect::Unique(tmp2.p, tb2, keys2.p, keys.p, d_nu.p, (long long)n, stream);
+            long long r = 0;
+            TGBM_CUDA(cudaMemcpyAsync(&r, d_nu.p, sizeof(long long), cudaMemcpyDeviceToHost, stream));
+            TGBM_CUDA(cudaStreamSynchronize(stream));
+            return r;
+        };
+        if (nnz) k_make_keys<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_val.p, d_col.p, nnz, keys.p);
+        nu = sort_unique(nnz);
+        if (comm && comm->active()) {
+            // union of the ranks' distinct keys: all-gather (padded to the largest rank), then sort + unique again
+            DevBuf<long long> counts;
+            counts.alloc(comm->world);
+            DevBuf<long long> mine;
+            mine.alloc(1);
+            TGBM_CUDA(cudaMemcpyAsync(mine.p, &nu, sizeof(long long), cudaMemcpyHostToDevice, stream));
+            comm->allgather(mine.p, counts.p, 1, Comm::I64, stream);
+            std::vector<long long> hc(comm->world);
+            TGBM_CUDA(cudaMemcpyAsync(hc.data(), counts.p, sizeof(long long) * comm->world, cudaMemcpyDeviceToHost, stream));
+            TGBM_CUDA(cudaStreamSynchronize(stream));
+            const long long mx = std::max<long long>(1, *std::max_element(hc.begin(), hc.end()));
+            DevBuf<unsigned long long> padded, all;
+            padded.alloc(mx); all.alloc((size_t)mx * comm->world);
+            TGBM_CUDA(cudaMemsetAsync(padded.p, 0xff, sizeof(unsigned long long) * mx, stream));
+            if (nu) TGBM_CUDA(cudaMemcpyAsync(padded.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
+            comm->allgather(padded.p, all.p, mx, Comm::I64, stream);
+            long long tot = 0;
+            for (long long c : hc) tot += c;
+            keys.alloc(std::max<long long>(tot, 1)); keys2.alloc(std::max<long long>(tot, 1));
+            long long o = 0;
+            for (int r = 0; r < comm->world; ++r) {
+                if (hc[r]) TGBM_CUDA(cudaMemcpyAsync(keys.p + o, all.p + (size_t)r * mx, sizeof(unsigned long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
+                o += hc[r];
+            }
+            nu = sort_unique(tot);
+        }
+        ukeys.alloc(std::max<long long>(nu, 1));
+        if (nu) TGBM_CUDA(cudaMemcpyAsync(ukeys.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+    }
+    // distinct values per feature -> stride and number of cut points per feature (host, F+1 numbers)
+    DevBuf<long long> ustart;
+    ustart.alloc(F + 1);
+    k_feature_bounds<<<ceil_div(F + 1, 128), 128, 0, stream>>>(ukeys.p, nu, F, ustart.p);
+    std::vector<long long> h_ustart(F + 1);
+    TGBM_CUDA(cudaMemcpyAsync(h_ustart.data(), ustart.p, sizeof(long long) * (F + 1), cudaMemcpyDeviceToHost, stream));
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+    std::vector<int> h_stride(F);
+    h_cut_ptr.assign(F + 1, 0);
+    for (int f = 0; f < F; ++f) {
+        const long long u = h_ustart[f + 1] - h_ustart[f];
+        const long long s = u / p.max_num_bin;
+        h_stride[f] = (int)s;
+        h_cut_ptr[f + 1] = h_cut_ptr[f] + (int)(s == 0 ? u : p.max_num_bin);
+    }
+    B = h_cut_ptr[F];
+    DevBuf<int> d_stride;
+    d_stride.alloc(std::max(F, 1));
+    cut_ptr.alloc(F + 1); cut_val.alloc(std::max(B, 1)); cut_fid.alloc(std::max(B, 1));
+    TGBM_CUDA(cudaMemcpyAsync(d_stride.p, h_stride.data(), sizeof(int) * F, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(cut_ptr.p, h_cut_ptr.data(), sizeof(int) * (F + 1), cudaMemcpyHostToDevice, stream));
+    if (nu) k_select_cuts<<<std::min(ceil_div(nu, 256), num_sms * 16), 256, 0, stream>>>(ukeys.p, nu, ustart.p, d_stride.p, cut_ptr.p,
+                                                                                         p.max_num_bin, cut_val.p, cut_fid.p);
+    h_cut_val.resize(B);
+    TGBM_CUDA(cudaMemcpyAsync(h_cut_val.data(), cut_val.p, sizeof(float) * B, cudaMemcpyDeviceToHost, stream));
+
+    // bin matrix in both layouts
+    bins.alloc((size_t)N * Fpad);
+    binsT.alloc((size_t)F * Npad);
+    TGBM_CUDA(cudaMemsetAsync(bins.p, MISSING_BIN, bins.bytes(), stream));
+    TGBM_CUDA(cudaMemsetAsync(binsT.p, MISSING_BIN, binsT.bytes(), stream));
+    if (N) k_bin_dense<<<ceil_div(N, 128), 128, 0, stream>>>(d_row_ptr.p, d_col.p, d_val.p, N, cut_ptr.p, cut_val.p, Fpad, Npad, bins.p, binsT.p);
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+    TGBM_CUDA(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------------
+Booster::Booster(const GBMParam &param, const Comm *comm) : impl_(new BoosterImpl) {
+    impl_->p = param;
+    impl_->comm = comm;
+}
+Booster::~Booster() = default;
+
+void Booster::init(const DataSet &ds) {
+    BoosterImpl &m = *impl_;
+    GBMParam &p = m.p;
+    m.objective = objective_from_name(p.objective);
+    TGBM_CHECK(m.objective != OBJ_UNKNOWN, "undefined objective " + p.objective);
+    TGBM_CHECK(p.depth >= 1 && p.depth <= 14, "depth must be in [1, 14]");
+    TGBM_CHECK(p.max_num_bin >= 1 && p.max_num_bin <= 255, "max_num_bin must be in [1, 255] (bin ids are bytes, 255 marks a missing value)");
+    TGBM_CHECK(p.quant_bits >= 8 && p.quant_bits <= 21, "quant_bits must be in [8, 21]");
+    TGBM_CHECK(!p.bagging, "bagging is not part of the histogram path implemented here");
+    TGBM_CHECK(p.column_sampling_rate >= 1.0f, "column sampling is not part of the histogram path implemented here");
+    int dev = 0;
+    TGBM_CUDA(cudaGetDevice(&dev));
+    TGBM_CUDA(cudaDeviceGetAttribute(&m.num_sms, cudaDevAttrMultiProcessorCount, dev));
+    TGBM_CUDA(cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking));
+    m.N = ds.n_rows;
+    m.F = ds.n_features;
+    m.depth = p.depth;
+    m.n_nodes = (1 << (p.depth + 1)) - 1;
+    m.label = ds.label;
+
+    // global row count, this rank's row offset, global feature count
+    m.N_global = m.N;
+    m.row_offset = 0;
+    if (m.comm && m.comm->active()) {
+        DevBuf<long long> mine, all;
+        mine.alloc(2); all.alloc(2 * (size_t)m.comm->world);
+        long long h[2] = {m.N, m.F};
+        TGBM_CUDA(cudaMemcpyAsync(mine.p, h, sizeof(h), cudaMemcpyHostToDevice, m.stream));
+        m.comm->allgather(mine.p, all.p, 2, Comm::I64, m.stream);
+        std::vector<long long> ha(2 * (size_t)m.comm->world);
+        TGBM_CUDA(cudaMemcpyAsync(ha.data(), all.p, sizeof(long long) * ha.size(), cudaMemcpyDeviceToHost, m.stream));
+        TGBM_CUDA(cudaStreamSynchronize(m.stream));
+        m.N_global = 0;
+        for (int r = 0; r < m.comm->world; ++r) {
+            if (r < m.comm->rank) m.row_offset += ha[2 * r];
+            m.N_global += ha[2 * r];
+            m.F = std::max<int>(m.F, (int)ha[2 * r + 1]);
+        }
+    }
+    TGBM_CHECK(m.N_global < (1ll << 31), "row count must fit 32 bits");
+    TGBM_CHECK(m.F >= 1, "data set has no features");
+    TGBM_CHECK((long long)m.F * 32 <= (1 << 21), "dense bin matrix supports at most 65536 features; wider data needs the sparse layout");
+    m.Fpad = (m.F + 31) / 32 * 32;
+    m.G = m.Fpad / 32;
+    m.Npad = ((size_t)m.N + 127) / 128 * 128;
+
+    // number of classes / trees per round (src/thundergbm/trainer.cu:26-37)
+    m.K = 1;
+    if (need_group_label(m.objective)) {
+        p.num_class = (int)ds.label.size();
+        if (p.num_class > 2) m.K = p.num_class;
+    } else if (m.objective == REG_LINEAR || m.objective == REG_LOGISTIC) {
+        p.num_class = 1;
+    }
+    p.tree_per_rounds = m.K;
+    m.num_class = p.num_class;
+
+    m.find_cuts_and_bins(ds);
+
+    const int N = m.N, K = m.K, depth = m.depth;
+    const size_t n1 = std::max<size_t>(N, 1);
+    m.y.alloc(n1); m.ypred.alloc(n1 * K); m.gh.alloc(n1 * K); m.ghq.alloc(n1 * K);
+    TGBM_CUDA(cudaMemcpyAsync(m.y.p, ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice, m.stream));
+    m.ypred.zero(m.stream);
+    m.maxbits.alloc(2); m.root_sum.alloc(2 * (size_t)K); m.qinfo.alloc(1);
+    m.qinfo_log.alloc(std::max(p.n_trees, 1) + 1);
+    m.nodes.alloc(m.n_nodes);
+    m.model.alloc((size_t)std::max(p.n_trees, 1) * K * m.n_nodes);
+    m.metric.alloc(std::max(p.n_trees, 1));
+    for (int i = 0; i < 2; ++i) {
+        m.rec_idx[i].alloc(n1); m.rec_gh[i].alloc(n1);
+        m.seg_begin[i].alloc((size_t)1 << depth); m.seg_cnt[i].alloc((size_t)1 << depth);
+        m.seg_begin[i].zero(m.stream); m.seg_cnt[i].zero(m.stream);
+    }
+    m.gcnt.alloc((size_t)1 << depth);
+    m.gcnt.zero(m.stream);
+    m.done_idx.alloc(n1); m.done_nid.alloc(n1);
+    if (p.keep_nid) m.nid_keep.alloc(n1 * K * std::max(p.n_trees, 1));
+    const size_t B1 = std::max(m.B, 1);
+    m.hist_full.alloc((((size_t)1 << depth) - 1) * B1 * 2);
+    m.hist_built.alloc(std::max<size_t>(1, (size_t)1 << std::max(0, depth - 2)) * B1 * 2);
+    const int max_pairs = std::max(1, 1 << std::max(0, depth - 2));
+    m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
+    m.recs.alloc(((size_t)1 << (depth - 1)) * m.F);
+    m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
+    m.tile_node.alloc(m.max_tiles); m.tile_start.alloc(m.max_tiles); m.tile_left.alloc(m.max_tiles);
+    m.node_tile0.alloc(((size_t)1 << depth) + 1); m.node_done_base.alloc((size_t)1 << depth);
+    m.bits.alloc((size_t)m.max_tiles * 32);
+    m.ctl.alloc(1);
+    m.ctl.zero(m.stream);
+    m.metric_partial.alloc(1024); m.metric_sum.alloc(1);
+    m.window_rows = (1 << (31 - p.quant_bits)) - HIST_THREADS;
+    TGBM_CHECK(m.window_rows >= HIST_THREADS, "quant_bits too large for the int32 accumulation window");
+    TGBM_CUDA(cudaFuncSetAttribute(k_hist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 256 * 32 * 4));
+    TGBM_CUDA(cudaFuncSetAttribute(k_hist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 256 * 32 * 4));
+    if (sizeof(TreeNode) * (size_t)m.n_nodes + 4 * (size_t)m.n_nodes > 48 * 1024)
+        TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(52 * (size_t)m.n_nodes)));
+    if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream);
+    m.init_base_score();
+    TGBM_CUDA(cudaStreamSynchronize(m.stream));
+    TGBM_CUDA(cudaGetLastError());
+}
+
+// ------------------------------------------------------------------------------------------------
+void BoosterImpl::gradient(int round) {
+    const int tb = 256;
+    maxbits.zero(stream);
+    root_sum.zero(stream);
+    if (N) {
+        switch (objective) {
+        case REG_LINEAR:
+            k_grad_pointwise<<<ceil_div(N, tb), tb, 0, stream>>>(y.p, ypred.p, N, 0, gh.p, maxbits.p); break;
+        case REG_LOGISTIC: case BINARY_LOGISTIC:
+            k_grad_pointwise<<<ceil_div(N, tb), tb, 0, stream>>>(y.p, ypred.p, N, 1, gh.p, maxbits.p); break;
+        case MULTI_SOFTMAX: case MULTI_SOFTPROB:
+            k_grad_softmax<<<ceil_div(N, tb), tb, 0, stream>>>(y.p, ypred.p, N, K, gh.p, maxbits.p); break;
+        case RANK_PAIRWISE: case RANK_NDCG:
+            rank.gradient(round, p.rank_seed, ypred.p, gh.p, maxbits.p, stream); break;
+        }
+        ++launches;
+    }
+    if (comm && comm->active()) comm->allreduce(maxbits.p, 2, Comm::U32, Comm::MAX, stream);
+    const int blocks = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
+    k_quantize<<<dim3(blocks, K), tb, 0, stream>>>(gh.p, N, maxbits.p, p.quant_bits, ghq.p, root_sum.p, qinfo.p);
+    ++launches;
+    if (comm && comm->active()) comm->allreduce(root_sum.p, 2 * (size_t)K, Comm::I64, Comm::SUM, stream);
+    if (round >= 0 && round < (int)qinfo_log.n)
+        TGBM_CUDA(cudaMemcpyAsync(qinfo_log.p + round, qinfo.p, sizeof(QuantInfo), cudaMemcpyDeviceToDevice, stream));
+}
+
+// Base score (include/thundergbm/objective/regression_obj.h:35-53 and :95-114): gradients at y_pred = 0,
+// w = -sum g / max(sum h, 1e-6) evaluated in double; binary:logistic maps it through sigmoid and logit
+// with the host's libm, as the reference does.
+void BoosterImpl::init_base_score() {
+    base_score = 0;
+    if (!(objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC)) return;
+    gradient(-1);
+    unsigned long long hs[2];
+    QuantInfo q;
+    TGBM_CUDA(cudaMemcpyAsync(hs, root_sum.p, sizeof(hs), cudaMemcpyDeviceToHost, stream));
+    TGBM_CUDA(cudaMemcpyAsync(&q, qinfo.p, sizeof(q), cudaMemcpyDeviceToHost, stream));
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+    const float fg = (float)((double)(long long)hs[0] * q.inv_sg), fh = (float)((double)(long long)hs[1] * q.inv_sh);
+    float w = (float)(-(double)fg / std::fmax((double)fh, 1e-6));
+    if (objective == BINARY_LOGISTIC) {
+        w = 1 / (1 + expf(-w));
+        w = -logf(1.0f / w - 1.0f);
+    }
+    base_score = w;
+    p.base_score = w;
+    if (N) k_fill<<<std::min(ceil_div(N, 256), num_sms * 8), 256, 0, stream>>>(ypred.p, (size_t)N, w);
+}
+
+void BoosterImpl::build_tree(int round, int k) {
+    const int tree_index = round * K + k;
+    const int2 *gq = ghq.p + (size_t)k * N;
+    k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
+                                                            seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
+    ++launches;
+    const int hist_ctas = num_sms * 2;
+    const size_t hist_smem = 2 * 256 * 32 * sizeof(int);
+    for (int level = 0; level < depth; ++level) {
+        const int cur = level & 1, nxt = cur ^ 1;
+        const int nl = 1 << level, pairs = std::max(1, nl / 2);
+        const int *idx_in = level == 0 ? nullptr : rec_idx[cur].p;
+        const int2 *gh_in = level == 0 ? gq : rec_gh[cur].p;
+        // -- histogram of the root / of the smaller child of every pair
+        if (level > 0 && comm && comm->active()) comm->allreduce(gcnt.p, nl, Comm::I32, Comm::SUM, stream);
+        k_hist_plan<<<1, 32, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, gcnt.p, built_right.p, hist_work.p,
+                                          hist_tile_base.p, ctl.p);
+        long long *built = level == 0 ? hist_full.p : hist_built.p;
+        TGBM_CUDA(cudaMemsetAsync(built, 0, sizeof(long long) * 2 * (size_t)B * pairs, stream));
+        TimedEvent ev{};
+        if (profile_on) {
+            cudaEventCreate(&ev.a); cudaEventCreate(&ev.b);
+            ev.kind = level == 0 ? 0 : 1;
+            cudaEventRecord(ev.a, stream);
+        }
+        if (level == 0)
+            k_hist<false><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, nullptr, gh_in, hist_work.p, hist_tile_base.p,
+                                                                                   ctl.p, cut_ptr.p, cut_fid.p, built, B, window_rows);
+        else
+            k_hist<true><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, idx_in, gh_in, hist_work.p, hist_tile_base.p,
+                                                                                  ctl.p, cut_ptr.p, cut_fid.p, built, B, window_rows);
+        if (profile_on) { cudaEventRecord(ev.b, stream); events.push_back(ev); }
+        if (comm && comm->active()) comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
+        // -- split selection and tree update
+        k_eval<<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built,
+                                                  level == 0 ? nullptr : hist_full.p + full_offset(level - 1),
+                                                  hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p);
+        k_best_apply<<<nl, 32, 0, stream>>>(level, F, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda);
+        // -- move the rows
+        TimedEvent pv{};
+        if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
+        k_part_plan<<<1, 256, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, tile_node.p, tile_start.p, node_tile0.p, ctl.p);
+        k_part_count<<<max_tiles, PART_TILE, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, tile_node.p, tile_start.p, ctl.p,
+                                                          idx_in, binsT.p, Npad, bits.p, tile_left.p);
+        k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0.p, tile_left.p,
+                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, node_done_base.p, ctl.p);
+        k_part_scatter<<<max_tiles, PART_TILE, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, tile_node.p, tile_start.p,
+                                                            node_tile0.p, ctl.p, idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p,
+                                                            node_done_base.p, rec_idx[nxt].p, rec_gh[nxt].p, done_idx.p, done_nid.p);
+        if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
+        launches += 8;
+    }
+    k_prune<<<1, 256, 52 * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, p.gamma);
+    if (N) k_predict_update<<<ceil_div(N, 256), 256, 0, stream>>>(nodes.p, done_idx.p, done_nid.p, N, p.learning_rate, ypred.p + (size_t)k * N,
+                                                                  p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr);
+    launches += 2;
+    TGBM_CUDA(cudaMemcpyAsync(model.p + (size_t)tree_index * n_nodes, nodes.p, sizeof(TreeNode) * n_nodes, cudaMemcpyDeviceToDevice, stream));
+}
+
+void BoosterImpl::round_metric(int round) {
+    if (need_group_file(objective)) {
+        rank.metric(objective, ypred.p, metric.p + round, comm, N_global, stream);
+        return;
+    }
+    const int blocks = std::max(1, std::min(ceil_div(N, 256), 1024));
+    k_metric_partial<<<blocks, 256, 0, stream>>>(objective, y.p, ypred.p, N, K, metric_partial.p);
+    k_metric_sum<<<1, 32, 0, stream>>>(metric_partial.p, blocks, metric_sum.p);
+    if (comm && comm->active()) comm->allreduce(metric_sum.p, 1, Comm::F64, Comm::SUM, stream);
+    k_metric_final<<<1, 32, 0, stream>>>(objective, metric_sum.p, N_global, metric.p + round);
+    launches += 3;
+}
+
+void Booster::boost(int n_rounds) {
+    BoosterImpl &m = *impl_;
+    TGBM_CHECK(m.rounds + n_rounds <= m.p.n_trees, "boost() beyond n_trees");
+    for (int i = 0; i < n_rounds; ++i) {
+        const int round = m.rounds;
+        m.gradient(round);
+        for (int k = 0; k < m.K; ++k) m.build_tree(round, k);
+        m.round_metric(round);
+        ++m.rounds;
+    }
+    TGBM_CUDA(cudaGetLastError());
+}
+
+void Booster::sync() {
+    TGBM_CUDA(cudaStreamSynchronize(impl_->stream));
+    TGBM_CUDA(cudaGetLastError());
+}
+
+int Booster::rounds_done() const { return impl_->rounds; }
+int Booster::trees_per_round() const { return impl_->K; }
+int Booster::n_nodes() const { return impl_->n_nodes; }
+int Booster::num_class() const { return impl_->num_class; }
+float Booster::base_score() const { return impl_->base_score; }
+int Booster::n_bins() const { return impl_->B; }
+int Booster::n_features() const { return impl_->F; }
+int Booster::fpad() const { return impl_->Fpad; }
+cudaStream_t Booster::stream() const { return impl_->stream; }
+void Booster::set_profile(bool on) { impl_->profile_on = on; }
+
+HistProfile Booster::profile() {
+    BoosterImpl &m = *impl_;
+    sync();
+    HistProfile r;
+    for (auto &e : m.events) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e.a, e.b);
+        if (e.kind == 2) { r.partition_ms += ms; r.partition_launches += 4; }
+        else {
+            r.hist_ms += ms; r.hist_launches += 1;
+            if (e.kind == 0) { r.hist_root_ms += ms; r.hist_root_launches += 1; }
+        }
+    }
+    TreeCtl c;
+    TGBM_CUDA(cudaMemcpy(&c, m.ctl.p, sizeof(c), cudaMemcpyDeviceToHost));
+    // algorithmic bytes: rows * (F bin bytes + 8 gradient bytes [+ 4 row index]) + histograms * B * 16 written
+    r.hist_root_bytes = (double)c.stat_rows_root * (m.F + 8);
+    r.hist_bytes = r.hist_root_bytes + (double)c.stat_rows_gather * (m.F + 8 + 4) + (double)c.stat_hists * m.B * 16.0;
+    r.partition_bytes = (double)c.stat_part_rows * (4 + 1 + 4);
+    r.kernel_launches = m.launches;
+    return r;
+}
+
+std::vector<std::vector<Tree>> Booster::get_model() {
+    BoosterImpl &m = *impl_;
+    sync();
+    std::vector<TreeNode> h((size_t)m.rounds * m.K * m.n_nodes);
+    if (!h.empty()) TGBM_CUDA(cudaMemcpy(h.data(), m.model.p, sizeof(TreeNode) * h.size(), cudaMemcpyDeviceToHost));
+    std::vector<std::vector<Tree>> out(m.rounds);
+    for (int r = 0; r < m.rounds; ++r) {
+        out[r].resize(m.K);
+        for (int k = 0; k < m.K; ++k) {
+            const TreeNode *src = h.data() + ((size_t)r * m.K + k) * m.n_nodes;
+            out[r][k].nodes.assign(src, src + m.n_nodes);
+        }
+    }
+    return out;
+}
+
+template <typename T>
+static std::vector<T> to_host(const T *p, size_t n) {
+    std::vector<T> h(n);
+    if (n) TGBM_CUDA(cudaMemcpy(h.data(), p, sizeof(T) * n, cudaMemcpyDeviceToHost));
+    return h;
+}
+
+std::vector<float> Booster::get_metrics() { sync(); return to_host(impl_->metric.p, impl_->rounds); }
+std::vector<float> Booster::get_ypred() { sync(); return to_host(impl_->ypred.p, (size_t)impl_->N * impl_->K); }
+std::vector<float> Booster::get_cut_val() const { return impl_->h_cut_val; }
+std::vector<int> Booster::get_cut_ptr() const { return impl_->h_cut_ptr; }
+std::vector<unsigned char> Booster::get_bins() { sync(); return to_host(impl_->bins.p, (size_t)impl_->N * impl_->Fpad); }
+std::vector<int> Booster::get_nid() {
+    sync();
+    if (!impl_->p.keep_nid) return {};
+    return to_host(impl_->nid_keep.p, (size_t)impl_->N * impl_->K * impl_->rounds);
+}
+std::vector<long long> Booster::get_root_hist() { sync(); return to_host(impl_->hist_full.p, (size_t)impl_->B * 2); }
+std::vector<double> Booster::get_quant_scale() {
+    sync();
+    auto q = to_host(impl_->qinfo_log.p, impl_->rounds);
+    std::vector<double> r;
+    for (auto &v : q) { r.push_back(v.sg); r.push_back(v.sh); }
+    return r;
+}
+
+}  // namespace tgbm

@@ -1,0 +1,78 @@
+// Booster: the boosting loop and the per-level tree builder on one GPU (one rank).
+// Counterpart of Booster / TreeBuilder::build_approximate / HistTreeBuilder_single in the reference
+// (include/thundergbm/booster.h:36-93, src/thundergbm/builder/tree_builder.cu:147-194,
+// src/thundergbm/builder/hist_tree_builder_single.cu).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <vector>
+
+#include "tgbm_comm.h"
+#include "tgbm_common.h"
+
+namespace tgbm {
+
+struct BoosterImpl;
+
+struct HistProfile {
+    double hist_ms = 0;          // summed device time of the histogram-build kernels
+    long long hist_launches = 0;
+    double hist_bytes = 0;       // algorithmic bytes they processed
+    double partition_ms = 0;
+    long long partition_launches = 0;
+    double partition_bytes = 0;
+    long long kernel_launches = 0;  // every kernel of this library launched by boost()
+    double hist_root_ms = 0;
+    double hist_root_bytes = 0;
+    long long hist_root_launches = 0;
+};
+
+class Booster {
+public:
+    // `comm` may be null (single GPU).  The booster keeps the pointer, the caller owns it.
+    Booster(const GBMParam &param, const Comm *comm);
+    ~Booster();
+
+    // Host CSR -> device, cut points, bin matrix, labels, base score.  With a communicator each rank passes its
+    // own contiguous block of rows; n_features must then be the global feature count.
+    void init(const DataSet &ds);
+    // rounds [done, done+n) ; asynchronous on the booster's stream
+    void boost(int n_rounds);
+    void sync();
+
+    int rounds_done() const;
+    int trees_per_round() const;
+    int n_nodes() const;
+    int num_class() const;
+    float base_score() const;
+    int n_bins() const;
+    int n_features() const;
+    int fpad() const;
+    cudaStream_t stream() const;
+    void set_profile(bool on);
+    HistProfile profile();  // syncs
+
+    std::vector<std::vector<Tree>> get_model();           // syncs
+    std::vector<float> get_metrics();                     // per finished round; syncs
+    std::vector<float> get_ypred();                       // [K][N] raw scores of the training rows
+    std::vector<float> get_cut_val() const;
+    std::vector<int> get_cut_ptr() const;
+    std::vector<unsigned char> get_bins();                // [N][Fpad] local bin ids, 255 = missing
+    std::vector<int> get_nid();                           // [tree][N] when param.keep_nid
+    std::vector<long long> get_root_hist();               // [B][2] level-0 histogram of the last tree built
+    std::vector<double> get_quant_scale();                // per round: scale_g, scale_h
+
+private:
+    std::unique_ptr<BoosterImpl> impl_;
+};
+
+// batch inference, Predictor::predict_raw (src/thundergbm/predictor.cu:32-189): out[t*N+i]
+void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model, float learning_rate, float base_score,
+                 std::vector<float> &out);
+// ObjectiveFunction::predict_transform on raw scores (in place; may shrink `y`)
+void predict_transform(int objective, int num_class, const std::vector<float> &label, int n_rows, std::vector<float> &y);
+// Metric::get_score on raw scores of `ds`
+float metric_score(int objective, const DataSet &ds, int num_class, const std::vector<float> &raw);
+
+}  // namespace tgbm

@@ -1,0 +1,108 @@
+// Device-side helpers shared by the kernels of the histogram tree builder.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+#include "tgbm_common.h"
+
+namespace tgbm {
+
+#define TGBM_CUDA(call)                                                                                   \
+    do {                                                                                                  \
+        cudaError_t e_ = (call);                                                                          \
+        if (e_ != cudaSuccess)                                                                            \
+            throw ::tgbm::Error(std::string("CUDA error: ") + cudaGetErrorString(e_) + " in " #call " at " __FILE__ ":" + \
+                                std::to_string(__LINE__));                                                \
+    } while (0)
+
+// RAII device buffer; everything is allocated once at init and reused for every tree.
+template <typename T>
+struct DevBuf {
+    T *p = nullptr;
+    size_t n = 0;
+    DevBuf() = default;
+    DevBuf(const DevBuf &) = delete;
+    DevBuf &operator=(const DevBuf &) = delete;
+    ~DevBuf() { release(); }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        n = 0;
+    }
+    void alloc(size_t count) {
+        release();
+        n = count;
+        if (count) TGBM_CUDA(cudaMalloc((void **)&p, sizeof(T) * count));
+    }
+    void zero(cudaStream_t s) {
+        if (n) TGBM_CUDA(cudaMemsetAsync(p, 0, sizeof(T) * n, s));
+    }
+    size_t bytes() const { return sizeof(T) * n; }
+};
+
+// ---- portable expf ------------------------------------------------------------------------
+// Cody-Waite reduction and a degree-5 polynomial written with explicit IEEE fp32 operations
+// only, so that a host restatement of the same lines gives the same bits.  Replaces expf in
+// the reference's losses (include/thundergbm/objective/regression_obj.h:144-154,
+// src/thundergbm/objective/multiclass_obj.cu:22-28).
+__host__ __device__ inline float pow2i(int e) {
+    union { uint32_t u; float f; } c;
+    c.u = (uint32_t)(e + 127) << 23;
+    return c.f;
+}
+__host__ __device__ inline float portable_expf(float x) {
+#ifdef __CUDA_ARCH__
+    if (!(x <= 88.72283f)) return x != x ? x : __int_as_float(0x7f800000);
+    if (x < -103.9f) return 0.0f;
+    float n = rintf(__fmul_rn(x, 1.44269504088896341f));
+    float r = __fmaf_rn(n, -0.693359375f, x);
+    r = __fmaf_rn(n, 2.12194440e-4f, r);
+    float p = 1.9875691500e-4f;
+    p = __fmaf_rn(p, r, 1.3981999507e-3f);
+    p = __fmaf_rn(p, r, 8.3334519073e-3f);
+    p = __fmaf_rn(p, r, 4.1665795894e-2f);
+    p = __fmaf_rn(p, r, 1.6666665459e-1f);
+    p = __fmaf_rn(p, r, 5.0000001201e-1f);
+    float e = __fadd_rn(__fmaf_rn(p, __fmul_rn(r, r), r), 1.0f);
+    int k = (int)n;
+    int k1 = k / 2, k2 = k - k1;
+    return __fmul_rn(__fmul_rn(e, pow2i(k1)), pow2i(k2));
+#else
+    (void)x;
+    return 0.f;
+#endif
+}
+
+// (g,h) quantisation grid of one boosting round: v_q = rn(v * scale), scale a power of two
+struct QuantInfo {
+    double sg, sh;          // 2^s
+    double inv_sg, inv_sh;  // 2^-s
+};
+
+__device__ inline double pow2d(int e) { return __longlong_as_double((long long)(e + 1023) << 52); }
+
+// exponent e with m < 2^e (0 for m == 0); m >= 0 finite
+__device__ inline int exp_above(float m) {
+    if (m == 0.f) return 0;
+    return ilogbf(m) + 1;
+}
+
+__device__ inline float q2f(long long v, double inv_scale) { return __double2float_rn((double)v * inv_scale); }
+
+__device__ inline long long shfl_ll(long long v, int src) {
+    int lo = __shfl_sync(0xffffffffu, (int)(v & 0xffffffffll), src);
+    int hi = __shfl_sync(0xffffffffu, (int)(v >> 32), src);
+    return ((long long)hi << 32) | (unsigned int)lo;
+}
+__device__ inline long long shfl_up_ll(long long v, int d) {
+    int lo = __shfl_up_sync(0xffffffffu, (int)(v & 0xffffffffll), d);
+    int hi = __shfl_up_sync(0xffffffffu, (int)(v >> 32), d);
+    return ((long long)hi << 32) | (unsigned int)lo;
+}
+__device__ inline long long shfl_xor_ll(long long v, int m) {
+    int lo = __shfl_xor_sync(0xffffffffu, (int)(v & 0xffffffffll), m);
+    int hi = __shfl_xor_sync(0xffffffffu, (int)(v >> 32), m);
+    return ((long long)hi << 32) | (unsigned int)lo;
+}
+
+}  // namespace tgbm

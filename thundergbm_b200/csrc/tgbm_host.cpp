@@ -1,0 +1,242 @@
+// Host side of the drop-in boundary: data-set containers, .conf/argv parser,
+// binary model file, logging.  Mirrors the behaviour of the reference's
+// dataset.cpp, parser.cpp and logger configuration for the histogram path.
+#include "tgbm_common.h"
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <sstream>
+
+namespace tgbm {
+
+static int g_verbose = 1;
+void set_verbosity(int v) { g_verbose = v; }
+int verbosity() { return g_verbose; }
+void log_info(const char *fmt, ...) {
+    if (g_verbose < 1) return;
+    va_list ap;
+    va_start(ap, fmt);
+    vfprintf(stdout, fmt, ap);
+    va_end(ap);
+    fputc('\n', stdout);
+    fflush(stdout);
+}
+
+// src/thundergbm/dataset.cpp:20-69.  The CSR arrays are copied; n_features = max column + 1;
+// classification objectives regroup the labels; ranking objectives take the query group sizes.
+void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *ci, const float *yy, const int *grp,
+                               int num_group, GBMParam &param) {
+    TGBM_CHECK(n >= 0 && rp != nullptr, "bad CSR input");
+    const long long nnz = rp[n];
+    TGBM_CHECK(nnz >= 0, "bad CSR row_ptr");
+    n_rows = n;
+    row_ptr.assign(rp, rp + n + 1);
+    col.assign(ci, ci + nnz);
+    val.assign(v, v + nnz);
+    y.assign(n, 0.f);
+    if (yy) y.assign(yy, yy + n);
+    label.clear();
+    group.clear();
+    int mx = 0;
+    for (long long i = 0; i < nnz; ++i) mx = std::max(mx, ci[i]);
+    n_features = mx + 1;
+    const int o = objective_from_name(param.objective);
+    if (yy && need_group_label(o)) {
+        group_label();
+        param.num_class = (int)label.size();
+    }
+    if (need_group_file(o))
+        for (int i = 0; i < num_group; ++i) group.push_back(grp[i]);
+}
+
+// src/thundergbm/dataset.cpp:83-101: labels cast to int, sorted, uniqued; y -> index of its value
+void DataSet::group_label() {
+    std::vector<int> t(y.begin(), y.end());
+    std::sort(t.begin(), t.end());
+    t.erase(std::unique(t.begin(), t.end()), t.end());
+    std::map<float, int> m;
+    label.clear();
+    for (int v : t) {
+        m[(float)v] = (int)label.size();
+        label.push_back((float)v);
+    }
+    for (auto &v : y) {
+        auto it = m.find(v);
+        v = it == m.end() ? 0.f : (float)it->second;
+    }
+}
+
+// src/thundergbm/dataset.cpp:71-81
+void DataSet::load_group_file(const std::string &file) {
+    std::ifstream ifs(file);
+    TGBM_CHECK(ifs.is_open(), "ranking objective needs a group file, not found: " + file);
+    group.clear();
+    int g;
+    while (ifs >> g) group.push_back(g);
+    log_info("#groups = %zu", group.size());
+}
+
+// src/thundergbm/dataset.cpp:106-320: LibSVM text, `label idx:val ...`, 1-based idx, '#' comments.
+void DataSet::load_from_file(const std::string &file, GBMParam &param) {
+    std::ifstream ifs(file, std::ifstream::binary);
+    TGBM_CHECK(ifs.is_open(), "file not found: " + file);
+    std::stringstream ss;
+    ss << ifs.rdbuf();
+    const std::string buf = ss.str();
+    row_ptr.assign(1, 0);
+    col.clear(); val.clear(); y.clear(); label.clear(); group.clear();
+    int maxf = 0;
+    const char *p = buf.data(), *end = p + buf.size();
+    auto is_num = [](char c) { return (c >= '0' && c <= '9') || c == '+' || c == '-' || c == '.' || c == 'e' || c == 'E'; };
+    while (p < end) {
+        const char *le = p;
+        while (le < end && *le != '\n' && *le != '\r' && *le != '\0') ++le;
+        const char *q = p;
+        const char *stop = le;
+        for (const char *c = p; c < le; ++c) if (*c == '#') { stop = c; break; }
+        while (q < stop && !is_num(*q)) ++q;
+        if (q < stop) {
+            y.push_back((float)atof(q));
+            while (q < stop && is_num(*q)) ++q;
+            while (q < stop) {
+                while (q < stop && !is_num(*q)) ++q;
+                if (q >= stop) break;
+                const char *a = q;
+                while (q < stop && is_num(*q)) ++q;
+                const char *c = q;
+                while (c < stop && (*c == ' ' || *c == '\t')) ++c;
+                if (c < stop && *c == ':') {
+                    const int fid = atoi(a);
+                    q = c + 1;
+                    while (q < stop && !is_num(*q)) ++q;
+                    const float fv = (float)atof(q);
+                    while (q < stop && is_num(*q)) ++q;
+                    col.push_back(fid - 1);
+                    val.push_back(fv);
+                    maxf = std::max(maxf, fid);
+                }
+            }
+            row_ptr.push_back((int)col.size());
+        }
+        p = le + 1;
+    }
+    n_rows = (int)y.size();
+    n_features = maxf;
+    log_info("#instances = %d, #features = %d", n_rows, n_features);
+    const int o = objective_from_name(param.objective);
+    if (need_group_file(o)) load_group_file(file + ".group");
+    if (need_group_label(o)) {
+        group_label();
+        param.num_class = (int)label.size();
+    }
+}
+
+// src/thundergbm/parser.cpp:9-100: defaults, then `key=value` lines of the conf file, then argv.
+void parse_param(GBMParam &mp, int argc, char **argv) {
+    mp = GBMParam();
+    auto parse_value = [&](const char *name_val) {
+        char name[256], val[256];
+        if (sscanf(name_val, "%255[^=]=%255s", name, val) != 2) return;
+        const std::string k(name);
+        if (k == "max_depth" || k == "depth") mp.depth = atoi(val);
+        else if (k == "num_round" || k == "n_trees") mp.n_trees = atoi(val);
+        else if (k == "n_gpus") mp.n_device = atoi(val);
+        else if (k == "verbosity" || k == "verbose") mp.verbose = atoi(val);
+        else if (k == "profiling") mp.profiling = atoi(val);
+        else if (k == "data") mp.path = val;
+        else if (k == "max_bin" || k == "max_num_bin") mp.max_num_bin = atoi(val);
+        else if (k == "colsample" || k == "column_sampling_rate") mp.column_sampling_rate = (float)atof(val);
+        else if (k == "bagging") mp.bagging = atoi(val);
+        else if (k == "num_parallel_tree" || k == "n_parallel_trees") mp.n_parallel_trees = atoi(val);
+        else if (k == "eta" || k == "learning_rate") mp.learning_rate = (float)atof(val);
+        else if (k == "objective") mp.objective = val;
+        else if (k == "num_class") mp.num_class = atoi(val);
+        else if (k == "min_child_weight") mp.min_child_weight = (float)atoi(val);  // atoi, as in the reference
+        else if (k == "lambda" || k == "lambda_tgbm") mp.lambda = (float)atof(val);
+        else if (k == "gamma" || k == "min_split_loss") mp.gamma = (float)atof(val);
+        else if (k == "tree_method") mp.tree_method = val;
+        else if (k == "quant_bits") mp.quant_bits = atoi(val);
+        else log_info("\"%s\" is unknown option!", name);
+    };
+    if (argc >= 2) {
+        std::ifstream conf(argv[1]);
+        std::string line;
+        while (std::getline(conf, line)) parse_value(line.c_str());
+    }
+    for (int i = 0; i < argc; ++i) parse_value(argv[i]);
+}
+
+// src/thundergbm/parser.cpp:146-171 -- little-endian native dump:
+// i32 len, objective, f32 lr, i32 num_class, i32 n_trees, f32 base_score, i32 n_label, f32 label[],
+// i32 n_rounds, { i32 n_k, { u64 n_nodes, TreeNode[n_nodes] } x n_k } x n_rounds
+void save_model(const std::string &path, const GBMParam &p, const std::vector<std::vector<Tree>> &model,
+                const std::vector<float> &label) {
+    std::ofstream out(path, std::ios::binary);
+    TGBM_CHECK(out.is_open(), "cannot write model file " + path);
+    const int len = (int)p.objective.size();
+    out.write((const char *)&len, 4);
+    out.write(p.objective.data(), len);
+    out.write((const char *)&p.learning_rate, 4);
+    out.write((const char *)&p.num_class, 4);
+    out.write((const char *)&p.n_trees, 4);
+    out.write((const char *)&p.base_score, 4);
+    const int nl = (int)label.size();
+    out.write((const char *)&nl, 4);
+    out.write((const char *)label.data(), 4 * (size_t)nl);
+    const int nr = (int)model.size();
+    out.write((const char *)&nr, 4);
+    for (const auto &round : model) {
+        const int nk = (int)round.size();
+        out.write((const char *)&nk, 4);
+        for (const auto &t : round) {
+            const uint64_t nn = t.nodes.size();
+            out.write((const char *)&nn, 8);
+            out.write((const char *)t.nodes.data(), sizeof(TreeNode) * nn);
+        }
+    }
+}
+
+// src/thundergbm/parser.cpp:102-145
+void load_model(const std::string &path, GBMParam &p, std::vector<std::vector<Tree>> &model, std::vector<float> &label) {
+    std::ifstream in(path, std::ios::binary);
+    TGBM_CHECK(in.is_open(), "cannot read model file " + path);
+    int len = 0;
+    in.read((char *)&len, 4);
+    TGBM_CHECK(len >= 0 && len < 4096, "corrupt model file");
+    std::string obj(len, '\0');
+    in.read(&obj[0], len);
+    p.objective = obj;
+    in.read((char *)&p.learning_rate, 4);
+    in.read((char *)&p.num_class, 4);
+    in.read((char *)&p.n_trees, 4);
+    in.read((char *)&p.base_score, 4);
+    int nl = 0;
+    in.read((char *)&nl, 4);
+    TGBM_CHECK(nl >= 0 && nl < (1 << 24), "corrupt model file");
+    label.resize(nl);
+    in.read((char *)label.data(), 4 * (size_t)nl);
+    int nr = 0;
+    in.read((char *)&nr, 4);
+    TGBM_CHECK(nr >= 0 && nr < (1 << 24), "corrupt model file");
+    model.clear();
+    for (int r = 0; r < nr; ++r) {
+        int nk = 0;
+        in.read((char *)&nk, 4);
+        TGBM_CHECK(nk >= 0 && nk < (1 << 20), "corrupt model file");
+        std::vector<Tree> v(nk);
+        for (auto &t : v) {
+            uint64_t nn = 0;
+            in.read((char *)&nn, 8);
+            TGBM_CHECK(nn < (1ull << 28), "corrupt model file");
+            t.nodes.resize(nn);
+            in.read((char *)t.nodes.data(), sizeof(TreeNode) * nn);
+        }
+        model.push_back(std::move(v));
+    }
+    TGBM_CHECK(bool(in), "truncated model file " + path);
+}
+
+}  // namespace tgbm

@@ -1,0 +1,837 @@
+// CUDA kernels of the histogram tree builder (sm_100a).
+//
+// Data layout in HBM (one rank = one contiguous block of rows):
+//   bins   uint8 [N][Fpad]   row-major local bin ids, Fpad = F rounded up to 32, 255 = missing.
+//                            One 32-byte sector holds 32 features of one row.
+//   binsT  uint8 [F][Npad]   the same matrix column-major; read by the partition step, which
+//                            needs one feature of many rows.
+//   gh     float2 [K][N]     gradient pairs of the round, class-major like the reference.
+//   ghq    int2   [K][N]     the same on the round's fixed-point grid.
+//   rec_idx/rec_gh [2][N]    per-level record lists: rows grouped by tree node, ascending row id
+//                            inside a node (stable partition), ping-pong between levels.
+//   hist   int64 [node][B][2] per-node histograms on the fixed-point grid.
+//
+// All sums on the fixed-point grid are integer sums, so they do not depend on the order of
+// the atomics, on the CTA count or on the number of ranks.
+#pragma once
+#include "tgbm_device.cuh"
+
+namespace tgbm {
+
+constexpr int HIST_THREADS = 512;
+constexpr int PART_TILE = 1024;
+constexpr int MISSING_BIN = 255;
+
+struct HistWork {  // one histogram to build at a level
+    int begin, count, slab, pad;
+};
+
+struct TreeCtl {  // device-side scalars of the tree being built
+    int done_count;
+    int n_hist_tiles;
+    int n_hist_work;
+    int n_part_tiles;
+    int n_records;  // records alive at the current level
+    int pad_;
+    unsigned long long stat_rows_root, stat_rows_gather, stat_hists, stat_part_rows;
+};
+
+struct SplitRec {  // best candidate of one (node, feature)
+    float gain;     // signed like the reference: negative = missing goes right
+    int bin;        // local bin of the candidate, -1 = none
+    float lg, lh;   // left sum without missing
+    float mg, mh;   // missing sum of the feature in this node
+};
+
+// ------------------------------------------------------------------ cut points
+// key = feature id in the high word, order-preserving image of the float in the low word
+__global__ void k_make_keys(const float *__restrict__ val, const int *__restrict__ col, size_t nnz,
+                            unsigned long long *__restrict__ keys) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nnz; i += (size_t)gridDim.x * blockDim.x) {
+        unsigned u = __float_as_uint(val[i]);
+        if (u == 0x80000000u) u = 0;  // -0.0f == 0.0f
+        u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+        keys[i] = ((unsigned long long)(unsigned)col[i] << 32) | u;
+    }
+}
+
+__device__ inline float key_to_float(unsigned long long k) {
+    unsigned u = (unsigned)(k & 0xffffffffull);
+    u = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+    return __uint_as_float(u);
+}
+
+// ustart[f] = number of unique (feature,value) keys with feature < f
+__global__ void k_feature_bounds(const unsigned long long *__restrict__ ukeys, long long nu, int F, long long *__restrict__ ustart) {
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f > F) return;
+    const unsigned long long target = (unsigned long long)(unsigned)f << 32;
+    long long lo = 0, hi = nu;
+    while (lo < hi) {
+        const long long mid = lo + (hi - lo) / 2;
+        if (ukeys[mid] < target) lo = mid + 1; else hi = mid;
+    }
+    ustart[f] = lo;
+}
+
+// HistCut::get_cut_points_single (src/thundergbm/hist_cut.cu:232-286): stride s = u / max_bin;
+// s == 0 keeps every distinct value, else positions 0, s, ..., (max_bin-1) s
+__global__ void k_select_cuts(const unsigned long long *__restrict__ ukeys, long long nu, const long long *__restrict__ ustart,
+                              const int *__restrict__ stride, const int *__restrict__ cut_ptr, int max_bin,
+                              float *__restrict__ cut_val, int *__restrict__ cut_fid) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nu; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long k = ukeys[i];
+        const int f = (int)(k >> 32);
+        const long long t = i - ustart[f];
+        const int s = stride[f];
+        long long pos;
+        if (s == 0) pos = t;
+        else if (t % s == 0 && t / s < max_bin) pos = t / s;
+        else continue;
+        cut_val[cut_ptr[f] + pos] = key_to_float(k);
+        cut_fid[cut_ptr[f] + pos] = f;
+    }
+}
+
+// HistTreeBuilder_single::get_bin_ids (hist_tree_builder_single.cu:81-119): clamped upper bound,
+// bin = min(#cuts <= v, n_cuts - 1); stored as the feature-local id in both layouts
+__global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val,
+                            int n_rows, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val, int Fpad,
+                            size_t Npad, unsigned char *__restrict__ bins, unsigned char *__restrict__ binsT) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= n_rows) return;
+    for (int j = row_ptr[r]; j < row_ptr[r + 1]; ++j) {
+        const int f = col[j];
+        const float v = val[j];
+        const int b0 = cut_ptr[f];
+        int lo = b0, hi = cut_ptr[f + 1] - 1;
+        if (hi < lo) continue;
+        while (lo < hi) {
+            const int mid = lo + (hi - lo) / 2;
+            if (cut_val[mid] <= v) lo = mid + 1; else hi = mid;
+        }
+        const unsigned char b = (unsigned char)(lo - b0);
+        bins[(size_t)r * Fpad + f] = b;
+        binsT[(size_t)f * Npad + r] = b;
+    }
+}
+
+// ------------------------------------------------------------------ objectives
+__device__ inline void track_max(float ag, float h, unsigned *maxbits) {
+    // non-negative floats order like their bit patterns
+    unsigned a = __float_as_uint(ag), b = __float_as_uint(h);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
+        b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+    }
+    if ((threadIdx.x & 31) == 0) {
+        atomicMax(maxbits, a);
+        atomicMax(maxbits + 1, b);
+    }
+}
+
+// SquareLoss / LogisticLoss gradients (include/thundergbm/objective/regression_obj.h:129-154)
+__global__ void k_grad_pointwise(const float *__restrict__ y, const float *__restrict__ yp, int n, int logistic,
+                                 float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    float g = 0.f, h = 0.f;
+    if (i < n) {
+        if (logistic) {
+            const float p = __fdiv_rn(1.0f, __fadd_rn(1.0f, portable_expf(-yp[i])));
+            g = __fsub_rn(p, y[i]);
+            h = fmaxf(__fmul_rn(p, __fsub_rn(1.0f, p)), 1e-16f);
+        } else {
+            g = __fsub_rn(yp[i], y[i]);
+            h = 1.0f;
+        }
+        gh[i] = make_float2(g, h);
+    }
+    track_max(fabsf(g), h, maxbits);
+}
+
+// Softmax::get_gradient (src/thundergbm/objective/multiclass_obj.cu:7-35), class-major gh[k*N+i]
+__global__ void k_grad_softmax(const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
+                               float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    float mg = 0.f, mh = 0.f;
+    if (i < n) {
+        float mx = yp[i];
+        for (int k = 1; k < K; ++k) mx = fmaxf(mx, yp[(size_t)k * n + i]);
+        float sum = 0.f;
+        for (int k = 0; k < K; ++k) sum = __fadd_rn(sum, portable_expf(__fsub_rn(yp[(size_t)k * n + i], mx)));
+        const float yi = y[i];
+        for (int k = 0; k < K; ++k) {
+            const float p = __fdiv_rn(portable_expf(__fsub_rn(yp[(size_t)k * n + i], mx)), sum);
+            const float g = ((float)k == yi) ? __fsub_rn(p, 1.0f) : p;
+            const float h = fmaxf(__fmul_rn(__fmul_rn(2.0f, p), __fsub_rn(1.0f, p)), 1e-16f);
+            gh[(size_t)k * n + i] = make_float2(g, h);
+            mg = fmaxf(mg, fabsf(g));
+            mh = fmaxf(mh, h);
+        }
+    }
+    track_max(mg, mh, maxbits);
+}
+
+// Round the round's gradients to the fixed-point grid and sum them per class (root node sums,
+// Tree::init2, src/thundergbm/tree.cu:31).  grid = (blocks, K)
+__global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned *__restrict__ maxbits, int quant_bits,
+                           int2 *__restrict__ ghq, unsigned long long *__restrict__ root_sum, QuantInfo *__restrict__ qinfo) {
+    const int k = blockIdx.y;
+    const int eg = exp_above(__uint_as_float(maxbits[0])), eh = exp_above(__uint_as_float(maxbits[1]));
+    const double sg = pow2d(quant_bits - eg), sh = pow2d(quant_bits - eh);
+    if (blockIdx.x == 0 && k == 0 && threadIdx.x == 0) {
+        qinfo->sg = sg; qinfo->sh = sh;
+        qinfo->inv_sg = pow2d(eg - quant_bits); qinfo->inv_sh = pow2d(eh - quant_bits);
+    }
+    long long tg = 0, th = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float2 v = gh[(size_t)k * n + i];
+        const int qg = (int)__double2ll_rn((double)v.x * sg), qh = (int)__double2ll_rn((double)v.y * sh);
+        ghq[(size_t)k * n + i] = make_int2(qg, qh);
+        tg += qg; th += qh;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { tg += shfl_xor_ll(tg, o); th += shfl_xor_ll(th, o); }
+    if ((threadIdx.x & 31) == 0) {
+        atomicAdd(root_sum + 2 * k, (unsigned long long)tg);
+        atomicAdd(root_sum + 2 * k + 1, (unsigned long long)th);
+    }
+}
+
+// ------------------------------------------------------------------ tree set-up
+// Tree::init2 (src/thundergbm/tree.cu:8-39)
+__global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, const unsigned long long *__restrict__ root_sum,
+                            const QuantInfo *__restrict__ q, float lambda, int n_rows, int *__restrict__ seg_begin,
+                            int *__restrict__ seg_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_nodes) return;
+    TreeNode t;
+    memset(&t, 0, sizeof(t));
+    t.final_id = i;
+    t.split_feature_id = -1;
+    t.parent_index = i == 0 ? -1 : (i - 1) / 2;
+    if (i < n_nodes / 2) { t.is_leaf = 0; t.lch_index = 2 * i + 1; t.rch_index = 2 * i + 2; }
+    else { t.is_leaf = 1; t.lch_index = -1; t.rch_index = -1; }
+    if (i == 0) {
+        t.sum_g = q2f((long long)root_sum[0], q->inv_sg);
+        t.sum_h = q2f((long long)root_sum[1], q->inv_sh);
+        t.is_valid = 1;
+        t.base_weight = __fdiv_rn(-t.sum_g, __fadd_rn(t.sum_h, lambda));
+        seg_begin[0] = 0; seg_cnt[0] = n_rows; gcnt[0] = n_rows;
+        ctl->done_count = 0; ctl->n_records = n_rows;
+    }
+    nodes[i] = t;
+}
+
+// ------------------------------------------------------------------ histogram build
+// Which sibling to build (the one with fewer rows over all ranks, ties -> left:
+// hist_tree_builder_single.cu:466) and the work list of the level.  One block.
+__global__ void k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+                            const int *__restrict__ gcnt, int *__restrict__ built_right, HistWork *__restrict__ work,
+                            int *__restrict__ tile_base, TreeCtl *__restrict__ ctl) {
+    if (threadIdx.x != 0) return;
+    int nw = 0, tiles = 0;
+    unsigned long long rows = 0;
+    if (level == 0) {
+        work[0] = HistWork{0, seg_cnt[0], 0, 0};
+        tile_base[0] = 0;
+        tiles = (seg_cnt[0] + HIST_THREADS - 1) / HIST_THREADS;
+        tile_base[1] = tiles;
+        nw = 1;
+        built_right[0] = 0;
+        ctl->stat_rows_root += seg_cnt[0];
+        ctl->stat_hists += 1;
+    } else {
+        const int pairs = 1 << (level - 1);
+        for (int j = 0; j < pairs; ++j) {
+            const int gl = gcnt[2 * j], gr = gcnt[2 * j + 1];
+            if (max(gl, gr) == 0) { built_right[j] = -1; continue; }
+            const int right = gl > gr;
+            built_right[j] = right;
+            const int c = 2 * j + right;
+            work[nw] = HistWork{seg_begin[c], seg_cnt[c], j, 0};
+            tile_base[nw] = tiles;
+            tiles += (seg_cnt[c] + HIST_THREADS - 1) / HIST_THREADS;
+            rows += seg_cnt[c];
+            ++nw;
+        }
+        tile_base[nw] = tiles;
+        ctl->stat_rows_gather += rows;
+        ctl->stat_hists += nw;
+    }
+    ctl->n_hist_work = nw;
+    ctl->n_hist_tiles = tiles;
+}
+
+// Rotate the 32 bin bytes of a row left by L bytes (L = lane id): afterwards byte j of the
+// register array is the bin of feature (j + L) mod 32, so at step j the 32 lanes of a warp
+// address 32 different features.
+__device__ __forceinline__ void rotate_row(uint32_t (&w)[8], int L) {
+    const int a = L >> 2, b = L & 3;
+#pragma unroll
+    for (int s = 4; s >= 1; s >>= 1) {
+        uint32_t t[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) t[i] = (a & s) ? w[(i + s) & 7] : w[i];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w[i] = t[i];
+    }
+    uint32_t t[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t[i] = __funnelshift_r(w[i], w[(i + 1) & 7], 8 * b);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) w[i] = t[i];
+}
+
+// Histogram build of one level (root: hist_tree_builder_single.cu:203-216, deeper levels: :485-505).
+// Persistent CTAs; grid = (ctas, feature groups of 32).  Each CTA owns a contiguous range of
+// 512-row tiles of the level's work list.  One lane = one row; the shared-memory histogram is laid
+// out [bin][32 features] so that the bank is the feature index: with the rotated feature order
+// every shared atomic of a warp hits 32 different banks.  Accumulators are int32; they are flushed
+// to the int64 histogram in global memory when the node changes or before they could overflow
+// (`window_rows` rows of at most 2^quant_bits each).
+template <bool GATHER>
+__global__ void __launch_bounds__(HIST_THREADS, 2)
+k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__restrict__ rec_idx,
+       const int2 *__restrict__ rec_gh, const HistWork *__restrict__ work, const int *__restrict__ tile_base,
+       const TreeCtl *__restrict__ ctl, const int *__restrict__ cut_ptr, const int *__restrict__ cut_fid,
+       long long *__restrict__ slab, int B, int window_rows) {
+    extern __shared__ __align__(16) int sh_hist[];  // g: [256][32], h: [256][32]
+    int *hg = sh_hist, *hh = sh_hist + 256 * 32;
+    for (int i = threadIdx.x; i < 2 * 256 * 32; i += HIST_THREADS) sh_hist[i] = 0;
+    __syncthreads();
+
+    const int group = blockIdx.y;
+    const int f0 = group * 32;
+    const int nf = min(32, F - f0);
+    const int bin_lo = cut_ptr[f0], bin_hi = cut_ptr[f0 + nf];
+    const int lane = threadIdx.x & 31;
+    const int total = ctl->n_hist_tiles, nwork = ctl->n_hist_work;
+    const int per = (total + gridDim.x - 1) / gridDim.x;
+    const int t_begin = min(total, (int)blockIdx.x * per), t_end = min(total, t_begin + per);
+    if (t_begin >= t_end) return;
+
+    auto flush = [&](int slab_idx) {
+        __syncthreads();
+        long long *dst = slab + (size_t)slab_idx * B * 2;
+        for (int b = bin_lo + threadIdx.x; b < bin_hi; b += HIST_THREADS) {
+            const int f = cut_fid[b];
+            const int s = (b - cut_ptr[f]) * 32 + (f - f0);
+            const int vg = hg[s], vh = hh[s];
+            if (vg) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b), (unsigned long long)(long long)vg); hg[s] = 0; }
+            if (vh) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b + 1), (unsigned long long)(long long)vh); hh[s] = 0; }
+        }
+        __syncthreads();
+    };
+
+    // locate the work item of a tile; w is a cursor that only moves forward
+    auto locate = [&](int t, int &w) -> long long {
+        while (w + 1 < nwork && t >= tile_base[w + 1]) ++w;
+        const HistWork it = work[w];
+        const long long p = (long long)(t - tile_base[w]) * HIST_THREADS + threadIdx.x;
+        return p < it.count ? it.begin + p : -1;
+    };
+    int w_cur = 0;
+    {  // binary search for the first item
+        int lo = 0, hi = nwork - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) / 2;
+            if (tile_base[mid] <= t_begin) lo = mid; else hi = mid - 1;
+        }
+        w_cur = lo;
+    }
+    int w_next = w_cur;
+    uint4 na = make_uint4(0, 0, 0, 0), nb = na;
+    int2 nv = make_int2(0, 0);
+    bool nok = false;
+    auto load = [&](int t, int &w) {
+        const long long p = locate(t, w);
+        nok = p >= 0;
+        if (nok) {
+            const int r = GATHER ? rec_idx[p] : (int)p;
+            const uint4 *src = reinterpret_cast<const uint4 *>(bins + (size_t)r * Fpad + f0);
+            na = src[0]; nb = src[1];
+            nv = rec_gh[p];
+        }
+    };
+    load(t_begin, w_next);
+    int slab_cur = work[w_cur].slab;
+    int since = 0;
+    for (int t = t_begin; t < t_end; ++t) {
+        const uint4 a = na, b = nb;
+        const int2 v = nv;
+        const bool ok = nok;
+        const int w_this = w_next;
+        if (t + 1 < t_end) load(t + 1, w_next);
+        if (w_this != w_cur) {  // the tile belongs to the next node: hand the finished one over
+            flush(slab_cur);
+            w_cur = w_this;
+            slab_cur = work[w_cur].slab;
+            since = 0;
+        } else if (since + HIST_THREADS > window_rows) {
+            flush(slab_cur);
+            since = 0;
+        }
+        since += HIST_THREADS;
+        if (ok) {
+            uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            rotate_row(w, lane);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const int f = (j + lane) & 31;
+                const uint32_t bin = (w[j >> 2] >> (8 * (j & 3))) & 255u;
+                if (f < nf && bin != MISSING_BIN) {
+                    const int o = bin * 32 + f;
+                    atomicAdd(hg + o, v.x);
+                    atomicAdd(hh + o, v.y);
+                }
+            }
+        }
+    }
+    flush(slab_cur);
+}
+
+// ------------------------------------------------------------------ split evaluation
+__device__ __forceinline__ float split_gain(float pg, float ph, float lg, float lh, float rg, float rh, float mcw, float lam) {
+    // compute_gain, hist_tree_builder_single.cu:279-286 (no fused multiply-add: products feed divisions)
+    if (lh >= mcw && rh >= mcw)
+        return __fsub_rn(__fadd_rn(__fdiv_rn(__fmul_rn(lg, lg), __fadd_rn(lh, lam)), __fdiv_rn(__fmul_rn(rg, rg), __fadd_rn(rh, lam))),
+                         __fdiv_rn(__fmul_rn(pg, pg), __fadd_rn(ph, lam)));
+    return 0.f;
+}
+
+// Sibling subtraction, per-feature prefix scan, missing sums, gains and per-feature argmax
+// (hist_tree_builder_single.cu:257-347 for the root, :538-540 and :614-704 for sibling pairs).
+// grid = (F, pairs); block = 64: warp 0 evaluates the left child, warp 1 the right child.
+__global__ void __launch_bounds__(64)
+k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode *__restrict__ nodes,
+       const int *__restrict__ built_right, const long long *__restrict__ built, const long long *__restrict__ parent,
+       long long *__restrict__ full, const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs) {
+    __shared__ long long sg[2][256], sh[2][256];
+    const int f = blockIdx.x, j = blockIdx.y;
+    const int b0 = cut_ptr[f], nb = cut_ptr[f + 1] - b0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_children = level == 0 ? 1 : 2;
+    const int node_local = level == 0 ? 0 : 2 * j + warp;
+    const int off = (1 << level) - 1;
+    SplitRec none = {0.f, -1, 0.f, 0.f, 0.f, 0.f};
+    const int br = built_right[j];
+    if (nb == 0 || br < 0) {
+        if (lane == 0 && warp < n_children) recs[(size_t)node_local * F + f] = none;
+        return;
+    }
+    if (level == 0) {
+        for (int i = threadIdx.x; i < nb; i += 64) { sg[0][i] = built[2 * (b0 + i)]; sh[0][i] = built[2 * (b0 + i) + 1]; }
+    } else {
+        const long long *bp = built + (size_t)j * B * 2, *pp = parent + (size_t)j * B * 2;
+        long long *fb = full + (size_t)(2 * j + br) * B * 2, *fo = full + (size_t)(2 * j + 1 - br) * B * 2;
+        for (int i = threadIdx.x; i < nb; i += 64) {
+            const long long cg = bp[2 * (b0 + i)], ch = bp[2 * (b0 + i) + 1];
+            const long long og = pp[2 * (b0 + i)] - cg, oh = pp[2 * (b0 + i) + 1] - ch;
+            sg[br][i] = cg; sh[br][i] = ch;
+            sg[1 - br][i] = og; sh[1 - br][i] = oh;
+            fb[2 * (b0 + i)] = cg; fb[2 * (b0 + i) + 1] = ch;
+            fo[2 * (b0 + i)] = og; fo[2 * (b0 + i) + 1] = oh;
+        }
+    }
+    __syncthreads();
+    if (warp >= n_children) return;
+    const TreeNode nd = nodes[off + node_local];
+    if (!nd.is_valid) {
+        if (lane == 0) recs[(size_t)node_local * F + f] = none;
+        return;
+    }
+    // each lane owns 8 consecutive bins
+    long long lg8[8], lh8[8];
+    long long tg = 0, th = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int b = lane * 8 + i;
+        lg8[i] = tg; lh8[i] = th;  // exclusive prefix inside the lane
+        if (b < nb) { tg += sg[warp][b]; th += sh[warp][b]; }
+    }
+    long long ig = tg, ih = th;  // inclusive scan of the lane totals
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const long long ug = shfl_up_ll(ig, o), uh = shfl_up_ll(ih, o);
+        if (lane >= o) { ig += ug; ih += uh; }
+    }
+    const long long base_g = ig - tg, base_h = ih - th;
+    const long long tot_g = shfl_ll(ig, 31), tot_h = shfl_ll(ih, 31);
+    const float pg = nd.sum_g, ph = nd.sum_h;
+    const float mg = __fsub_rn(pg, q2f(tot_g, q->inv_sg)), mh = __fsub_rn(ph, q2f(tot_h, q->inv_sh));
+    float best = 0.f, best_lg = 0.f, best_lh = 0.f;
+    int best_bin = -1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int b = lane * 8 + i;
+        if (b < nb) {
+            const float lg = q2f(base_g + lg8[i], q->inv_sg), lh = q2f(base_h + lh8[i], q->inv_sh);
+            const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
+            const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
+            const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
+            const float gn = gl > gr ? gl : -gr;
+            if (best_bin < 0 || fabsf(gn) > fabsf(best)) { best = gn; best_bin = b; best_lg = lg; best_lh = lh; }
+        }
+    }
+    // warp arg-abs-max, ties -> smaller bin (hist_tree_builder_single.cu:330-335)
+    unsigned long long key = best_bin < 0 ? 0ull
+                                          : (((unsigned long long)__float_as_uint(fabsf(best)) << 32) | (unsigned)(0x7fffffff - best_bin));
+    unsigned long long mk = key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = (unsigned long long)shfl_xor_ll((long long)mk, o);
+        mk = other > mk ? other : mk;
+    }
+    const unsigned win = __ballot_sync(0xffffffffu, key == mk && best_bin >= 0);
+    const int src = __ffs(win) - 1;
+    best = __shfl_sync(0xffffffffu, best, src);
+    best_bin = __shfl_sync(0xffffffffu, best_bin, src);
+    best_lg = __shfl_sync(0xffffffffu, best_lg, src);
+    best_lh = __shfl_sync(0xffffffffu, best_lh, src);
+    if (lane == 0) recs[(size_t)node_local * F + f] = SplitRec{best, best_bin, best_lg, best_lh, mg, mh};
+}
+
+// Per-node argmax over the features, SplitPoint decode and update_tree
+// (hist_tree_builder_single.cu:365-389 and :847-902).  One warp per node of the level.
+__global__ void __launch_bounds__(32)
+k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
+             const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam) {
+    const int n = blockIdx.x, lane = threadIdx.x;
+    const int nid = (1 << level) - 1 + n;
+    if (!nodes[nid].is_valid) return;
+    unsigned long long key = 0;
+    for (int f = lane; f < F; f += 32) {
+        const SplitRec r = recs[(size_t)n * F + f];
+        if (r.bin < 0) continue;
+        const unsigned long long k = ((unsigned long long)__float_as_uint(fabsf(r.gain)) << 32) | (unsigned)(0x7fffffff - f);
+        if (k > key) key = k;
+    }
+    // a record with gain 0 still has key == 0x7fffffff - f > 0, so 0 means "no record"
+    unsigned long long mk = key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = (unsigned long long)shfl_xor_ll((long long)mk, o);
+        mk = other > mk ? other : mk;
+    }
+    if (lane != 0) return;
+    TreeNode &nd = nodes[nid];
+    if (mk == 0) {  // no feature has a cut point: nothing to split on
+        nd.is_leaf = 1;
+        nodes[nd.lch_index].is_valid = 0;
+        nodes[nd.rch_index].is_valid = 0;
+        return;
+    }
+    const int f = 0x7fffffff - (int)(mk & 0xffffffffull);
+    const SplitRec r = recs[(size_t)n * F + f];
+    const float gain = fabsf(r.gain);
+    if (gain > rt_eps) {
+        const bool default_right = r.gain < 0.f;
+        const int b0 = cut_ptr[f];
+        nd.gain = gain;
+        nd.split_feature_id = f;
+        nd.split_bid = (unsigned char)r.bin;
+        if (r.bin == 0) {
+            const float c = cut_val[b0];
+            nd.split_value = (float)((double)__fsub_rn(c, fabsf(c)) - 1e-5);
+        } else {
+            nd.split_value = cut_val[b0 + r.bin - 1];
+        }
+        TreeNode &l = nodes[nd.lch_index], &rc = nodes[nd.rch_index];
+        l.is_valid = 1; rc.is_valid = 1;
+        float lgs = r.lg, lhs = r.lh;
+        if (!default_right) { lgs = __fadd_rn(lgs, r.mg); lhs = __fadd_rn(lhs, r.mh); nd.default_right = 0; }
+        else nd.default_right = 1;
+        l.sum_g = lgs; l.sum_h = lhs;
+        rc.sum_g = __fsub_rn(nd.sum_g, lgs); rc.sum_h = __fsub_rn(nd.sum_h, lhs);
+        l.base_weight = __fdiv_rn(-l.sum_g, __fadd_rn(l.sum_h, lam));
+        rc.base_weight = __fdiv_rn(-rc.sum_g, __fadd_rn(rc.sum_h, lam));
+    } else {
+        nd.is_leaf = 1;
+        nodes[nd.lch_index].is_valid = 0;
+        nodes[nd.rch_index].is_valid = 0;
+    }
+}
+
+// ------------------------------------------------------------------ instance partition
+// (replaces update_ins2node_id + the per-level radix sort, hist_tree_builder_single.cu:908-1020, :397-415)
+// Tile table: every node of the level that holds records gets ceil(count / 1024) tiles.
+__global__ void k_part_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+                            int *__restrict__ tile_node, int *__restrict__ tile_start, int *__restrict__ node_tile0,
+                            TreeCtl *__restrict__ ctl) {
+    __shared__ int total;
+    const int nl = 1 << level;
+    if (threadIdx.x == 0) {
+        int t = 0;
+        unsigned long long rows = 0;
+        for (int n = 0; n < nl; ++n) {
+            node_tile0[n] = t;
+            t += (seg_cnt[n] + PART_TILE - 1) / PART_TILE;
+            rows += seg_cnt[n];
+        }
+        node_tile0[nl] = t;
+        total = t;
+        ctl->n_part_tiles = t;
+        ctl->stat_part_rows += rows;
+    }
+    __syncthreads();
+    for (int n = threadIdx.x; n < nl; n += blockDim.x) {
+        const int t0 = node_tile0[n], t1 = node_tile0[n + 1];
+        for (int t = t0; t < t1; ++t) { tile_node[t] = n; tile_start[t] = seg_begin[n] + (t - t0) * PART_TILE; }
+    }
+}
+
+// Direction of every record of a splittable node: left unless (missing and default right) or
+// bin >= split_bid (hist_tree_builder_single.cu:1003-1012).  One bit per record, one count per tile.
+__global__ void __launch_bounds__(PART_TILE)
+k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+             const int *__restrict__ tile_node, const int *__restrict__ tile_start, const TreeCtl *__restrict__ ctl,
+             const int *__restrict__ rec_idx, const unsigned char *__restrict__ binsT, size_t Npad,
+             unsigned *__restrict__ bits, int *__restrict__ tile_left) {
+    const int t = blockIdx.x;
+    if (t >= ctl->n_part_tiles) return;
+    __shared__ int wsum[32];
+    const int n = tile_node[t];
+    const TreeNode nd = nodes[(1 << level) - 1 + n];
+    const bool splittable = nd.is_valid && !nd.is_leaf;
+    if (!splittable) { if (threadIdx.x == 0) tile_left[t] = 0; return; }
+    const int p = tile_start[t] + threadIdx.x;
+    const int end = seg_begin[n] + seg_cnt[n];
+    bool left = false;
+    if (p < end) {
+        const int r = rec_idx ? rec_idx[p] : p;
+        const unsigned char b = binsT[(size_t)nd.split_feature_id * Npad + r];
+        left = (b == MISSING_BIN) ? !nd.default_right : (b < nd.split_bid);
+    }
+    const unsigned m = __ballot_sync(0xffffffffu, left);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { bits[(size_t)t * 32 + warp] = m; wsum[warp] = __popc(m); }
+    __syncthreads();
+    if (warp == 0) {
+        int v = wsum[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) tile_left[t] = v;
+    }
+}
+
+// Prefix of the left counts over the tiles of every node, child segment table of the next level,
+// done-list offsets of finished nodes.  One block of 1024 threads.
+__global__ void __launch_bounds__(1024)
+k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
+            const int *__restrict__ seg_cnt, const int *__restrict__ node_tile0, int *__restrict__ tile_left,
+            int *__restrict__ next_begin, int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base,
+            TreeCtl *__restrict__ ctl) {
+    __shared__ int wsum[32];
+    __shared__ int carry;
+    const int nt = ctl->n_part_tiles, nl = 1 << level;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) carry = 0;
+    __syncthreads();
+    // inclusive scan of tile_left over all tiles (in place)
+    for (int base = 0; base < nt; base += 1024) {
+        const int i = base + threadIdx.x;
+        int v = i < nt ? tile_left[i] : 0;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+        if (lane == 31) wsum[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            int s = wsum[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, s, o); if (lane >= o) s += u; }
+            wsum[lane] = s;
+        }
+        __syncthreads();
+        v += (warp ? wsum[warp - 1] : 0) + carry;
+        if (i < nt) tile_left[i] = v;
+        __syncthreads();
+        if (threadIdx.x == 1023) carry = v;
+        __syncthreads();
+    }
+    // per node: children counts
+    const bool last = level == depth - 1;
+    for (int n = threadIdx.x; n < nl; n += 1024) {
+        const TreeNode nd = nodes[nl - 1 + n];
+        const bool splittable = nd.is_valid && !nd.is_leaf;
+        int cl = 0, cr = 0;
+        if (splittable && seg_cnt[n] > 0) {
+            const int t0 = node_tile0[n], t1 = node_tile0[n + 1];
+            cl = tile_left[t1 - 1] - (t0 > 0 ? tile_left[t0 - 1] : 0);
+            cr = seg_cnt[n] - cl;
+        }
+        next_cnt[2 * n] = cl; next_cnt[2 * n + 1] = cr;
+        gcnt[2 * n] = cl; gcnt[2 * n + 1] = cr;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        // exclusive scans in node order (at most 2^depth entries)
+        int pos = 0, done = ctl->done_count;
+        for (int n = 0; n < nl; ++n) {
+            const TreeNode nd = nodes[nl - 1 + n];
+            const bool splittable = nd.is_valid && !nd.is_leaf;
+            next_begin[2 * n] = pos; pos += next_cnt[2 * n];
+            next_begin[2 * n + 1] = pos; pos += next_cnt[2 * n + 1];
+            node_done_base[n] = done;
+            if (!splittable || last) done += seg_cnt[n];
+        }
+        ctl->done_count = done;
+        ctl->n_records = last ? 0 : pos;
+    }
+}
+
+// Stable scatter of the records into the child segments (or, for nodes that stopped splitting and
+// at the last level, into the done list with the id of the node the row ended in).
+__global__ void __launch_bounds__(PART_TILE)
+k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
+               const int *__restrict__ seg_cnt, const int *__restrict__ tile_node, const int *__restrict__ tile_start,
+               const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
+               const int2 *__restrict__ rec_gh, const unsigned *__restrict__ bits, const int *__restrict__ tile_left,
+               const int *__restrict__ next_begin, const int *__restrict__ node_done_base, int *__restrict__ out_idx,
+               int2 *__restrict__ out_gh, int *__restrict__ done_idx, int *__restrict__ done_nid) {
+    const int t = blockIdx.x;
+    if (t >= ctl->n_part_tiles) return;
+    __shared__ int wpre[32];
+    const int n = tile_node[t];
+    const int nid = (1 << level) - 1 + n;
+    const TreeNode nd = nodes[nid];
+    const bool splittable = nd.is_valid && !nd.is_leaf;
+    const bool last = level == depth - 1;
+    const int p0 = tile_start[t];
+    const int p = p0 + threadIdx.x;
+    const int b = seg_begin[n], end = b + seg_cnt[n];
+    const bool ok = p < end;
+    const int r = ok ? (rec_idx ? rec_idx[p] : p) : 0;
+    if (!splittable) {
+        if (ok) { const int d = node_done_base[n] + (p - b); done_idx[d] = r; done_nid[d] = nid; }
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned m = bits[(size_t)t * 32 + warp];
+    if (lane == 0) wpre[warp] = __popc(m);
+    __syncthreads();
+    if (warp == 0) {
+        int v = wpre[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+        wpre[lane] = v - __popc(bits[(size_t)t * 32 + lane]);  // exclusive
+    }
+    __syncthreads();
+    if (!ok) return;
+    const bool left = (m >> lane) & 1u;
+    const int t0 = node_tile0[n];
+    const int lefts_before_tile = (t > 0 ? tile_left[t - 1] : 0) - (t0 > 0 ? tile_left[t0 - 1] : 0);
+    const int lefts_before = lefts_before_tile + wpre[warp] + __popc(m & ((1u << lane) - 1u));
+    const int t1 = node_tile0[n + 1];
+    const int n_left = tile_left[t1 - 1] - (t0 > 0 ? tile_left[t0 - 1] : 0);
+    const int rank = left ? lefts_before : (p - b) - lefts_before;
+    if (last) {
+        const int d = node_done_base[n] + (left ? rank : n_left + rank);
+        done_idx[d] = r;
+        done_nid[d] = left ? nd.lch_index : nd.rch_index;
+    } else {
+        const int d = (left ? next_begin[2 * n] : next_begin[2 * n + 1]) + rank;
+        out_idx[d] = r;
+        out_gh[d] = rec_gh[p];
+    }
+}
+
+// ------------------------------------------------------------------ end of tree
+// Tree::prune_self / try_prune_leaf / reorder_nid (src/thundergbm/tree.cu:85-128); the node table is
+// staged in shared memory and walked by one thread in the reference's order.
+__global__ void k_prune(TreeNode *__restrict__ nodes, int n_nodes, float gamma) {
+    extern __shared__ __align__(16) unsigned char sm[];
+    TreeNode *sn = reinterpret_cast<TreeNode *>(sm);
+    int *cnt = reinterpret_cast<int *>(sm + sizeof(TreeNode) * (size_t)n_nodes);
+    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) { sn[i] = nodes[i]; cnt[i] = 0; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < n_nodes; ++i) {
+            if (!(sn[i].is_leaf && sn[i].is_valid)) continue;
+            int n = i;
+            while (true) {
+                const int p = sn[n].parent_index;
+                if (p == -1) break;
+                cnt[p]++;
+                if (cnt[p] >= 2 && sn[p].gain < gamma) {
+                    sn[sn[p].lch_index].is_pruned = 1;
+                    sn[sn[p].rch_index].is_pruned = 1;
+                    sn[p].is_leaf = 1;
+                    n = p;
+                } else break;
+            }
+        }
+        int id = 0;
+        for (int i = 0; i < n_nodes; ++i) if (sn[i].is_valid && !sn[i].is_pruned) sn[i].final_id = id++;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) nodes[i] = sn[i];
+}
+
+// TreeBuilder::predict_in_training (src/thundergbm/builder/tree_builder.cu:62-74); nvcc contracts the
+// reference's `y += lr * w` into one fused multiply-add, written out here
+__global__ void k_predict_update(const TreeNode *__restrict__ nodes, const int *__restrict__ done_idx,
+                                 const int *__restrict__ done_nid, int n, float lr, float *__restrict__ yp,
+                                 int *__restrict__ nid_out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = done_idx[i];
+    int nid = done_nid[i];
+    if (nid_out) nid_out[r] = nid;
+    while (nid != -1 && nodes[nid].is_pruned) nid = nodes[nid].parent_index;
+    yp[r] = __fmaf_rn(lr, nodes[nid].base_weight, yp[r]);
+}
+
+// ------------------------------------------------------------------ metrics
+// per-block partial sums in a fixed order: RMSE (pointwise_metric.cu:8-22), binary error and
+// multi-class accuracy (multiclass_metric.cu:9-46)
+__global__ void k_metric_partial(int objective, const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
+                                 double *__restrict__ partial) {
+    __shared__ double ws[32];
+    double s = 0;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        if (objective == REG_LINEAR || objective == REG_LOGISTIC) {
+            const float e = __fsub_rn(yp[i], y[i]);
+            s += (double)__fmul_rn(e, e);
+        } else if (objective == BINARY_LOGISTIC) {
+            const int k = (1.0 / (1.0 + exp(-(double)yp[i])) > 0.5) ? 1 : 0;
+            s += ((float)k == y[i]) ? 1.0 : 0.0;
+        } else {
+            int mk = 0;
+            float mp = yp[i];
+            for (int k = 1; k < K; ++k) { const float v = yp[(size_t)k * n + i]; if (v > mp) { mp = v; mk = k; } }
+            s += ((float)mk == y[i]) ? 1.0 : 0.0;
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0;
+        for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += ws[w];
+        partial[blockIdx.x] = t;
+    }
+}
+__global__ void k_metric_sum(const double *__restrict__ partial, int nb, double *__restrict__ out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        double t = 0;
+        for (int i = 0; i < nb; ++i) t += partial[i];
+        *out = t;
+    }
+}
+__global__ void k_metric_final(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const double s = *sum;
+        if (objective == REG_LINEAR || objective == REG_LOGISTIC) *out = sqrtf((float)s / (float)n_total);
+        else if (objective == BINARY_LOGISTIC) *out = 1.0f - (float)(long long)s / (float)n_total;
+        else *out = (float)(long long)s / (float)n_total;
+    }
+}
+
+__global__ void k_fill(float *p, size_t n, float v) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
+}
+
+}  // namespace tgbm

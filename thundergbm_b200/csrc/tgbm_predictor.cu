@@ -1,0 +1,214 @@
+// Batch inference: Predictor::predict_raw (src/thundergbm/predictor.cu:32-189), the objectives'
+// predict_transform and the metric the predict CLI logs.
+#include <algorithm>
+#include <cmath>
+
+#include "tgbm_booster.h"
+#include "tgbm_kernels.cuh"
+#include "tgbm_rank.cuh"
+
+namespace tgbm {
+
+// 16-byte traversal record (the 48-byte model record carries training-only fields)
+struct PNode {
+    float v;     // split value, or leaf weight
+    int fid;     // feature id; bit 31 = leaf, bit 30 = default right
+    int lch, rch;
+};
+
+constexpr int PRED_ROWS = 128;
+
+// Rows of a tile are densified in shared memory (INFINITY = missing), one thread walks every tree of
+// every class for its row.  The reference takes this path when F*128*4 <= 48 KB and accumulates in
+// double from base_score, adding the result to a zeroed float (predictor.cu:88-134).
+__global__ void __launch_bounds__(PRED_ROWS)
+k_predict_dense(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F,
+                const PNode *__restrict__ model, int n_rounds, int K, int n_nodes, float lr, float base_score,
+                float *__restrict__ out) {
+    extern __shared__ float dense[];  // [F][PRED_ROWS]
+    const int i = blockIdx.x * PRED_ROWS + threadIdx.x;
+    for (int f = 0; f < F; ++f) dense[f * PRED_ROWS + threadIdx.x] = INFINITY;
+    if (i < n_rows)
+        for (int j = row_ptr[i]; j < row_ptr[i + 1]; ++j) {
+            const int c = col[j];
+            if (c < F) dense[c * PRED_ROWS + threadIdx.x] = val[j];
+        }
+    if (i >= n_rows) return;
+    for (int t = 0; t < K; ++t) {
+        double sum = base_score;
+        for (int r = 0; r < n_rounds; ++r) {
+            const PNode *nd = model + ((size_t)r * K + t) * n_nodes;
+            PNode cur = nd[0];
+            while (!(cur.fid & 0x80000000)) {
+                const int f = cur.fid & 0x3fffffff;
+                const float fv = f < F ? dense[f * PRED_ROWS + threadIdx.x] : INFINITY;
+                int nx;
+                if (fv < INFINITY) nx = fv < cur.v ? cur.lch : cur.rch;
+                else nx = (cur.fid & 0x40000000) ? cur.rch : cur.lch;
+                cur = nd[nx];
+            }
+            sum += (double)__fmul_rn(lr, cur.v);
+        }
+        out[(size_t)t * n_rows + i] = (float)(0.0 + sum);
+    }
+}
+
+// CSR path with a binary search per visited node; float accumulator, `sum += lr * w` is one fused
+// multiply-add in the reference's compiled code (predictor.cu:137-187)
+__global__ void k_predict_csr(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows,
+                              const PNode *__restrict__ model, int n_rounds, int K, int n_nodes, float lr, float base_score,
+                              float *__restrict__ out) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_rows) return;
+    const int *ci = col + row_ptr[i];
+    const float *vi = val + row_ptr[i];
+    const int len = row_ptr[i + 1] - row_ptr[i];
+    for (int t = 0; t < K; ++t) {
+        float sum = base_score;
+        for (int r = 0; r < n_rounds; ++r) {
+            const PNode *nd = model + ((size_t)r * K + t) * n_nodes;
+            PNode cur = nd[0];
+            while (!(cur.fid & 0x80000000)) {
+                const int f = cur.fid & 0x3fffffff;
+                int lo = 0, hi = len;
+                bool found = false;
+                float fv = 0.f;
+                while (lo != hi) {
+                    const int mid = lo + (hi - lo) / 2;
+                    const int c = ci[mid];
+                    if (c == f) { found = true; fv = vi[mid]; break; }
+                    if (c > f) hi = mid; else lo = mid + 1;
+                }
+                int nx;
+                if (found) nx = fv < cur.v ? cur.lch : cur.rch;
+                else nx = (cur.fid & 0x40000000) ? cur.rch : cur.lch;
+                cur = nd[nx];
+            }
+            sum = __fmaf_rn(lr, cur.v, sum);
+        }
+        out[(size_t)t * n_rows + i] = sum;
+    }
+}
+
+void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model, float learning_rate, float base_score,
+                 std::vector<float> &out) {
+    const int N = ds.n_rows;
+    const int n_rounds = (int)model.size();
+    TGBM_CHECK(n_rounds > 0 && !model[0].empty(), "empty model");
+    const int K = (int)model[0].size();
+    const int n_nodes = (int)model[0][0].nodes.size();
+    out.assign((size_t)N * K, 0.f);
+    if (N == 0) return;
+    if (K > 1) base_score = 0;  // predictor.cu:81-83
+    std::vector<PNode> flat((size_t)n_rounds * K * n_nodes);
+    for (int r = 0; r < n_rounds; ++r)
+        for (int t = 0; t < K; ++t) {
+            TGBM_CHECK((int)model[r].size() == K && (int)model[r][t].nodes.size() == n_nodes, "ragged model");
+            for (int n = 0; n < n_nodes; ++n) {
+                const TreeNode &s = model[r][t].nodes[n];
+                PNode &d = flat[((size_t)r * K + t) * n_nodes + n];
+                d.lch = s.lch_index; d.rch = s.rch_index;
+                if (s.is_leaf) { d.v = s.base_weight; d.fid = (int)0x80000000; }
+                else { d.v = s.split_value; d.fid = (s.split_feature_id & 0x3fffffff) | (s.default_right ? 0x40000000 : 0); }
+            }
+        }
+    cudaStream_t st;
+    TGBM_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    const size_t nnz = (size_t)ds.row_ptr[N];
+    DevBuf<int> d_rp, d_col;
+    DevBuf<float> d_val, d_out;
+    DevBuf<PNode> d_model;
+    d_rp.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1)); d_out.alloc((size_t)N * K);
+    d_model.alloc(flat.size());
+    TGBM_CUDA(cudaMemcpyAsync(d_rp.p, ds.row_ptr.data(), sizeof(int) * (N + 1), cudaMemcpyHostToDevice, st));
+    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.col.data(), sizeof(int) * nnz, cudaMemcpyHostToDevice, st));
+    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.val.data(), sizeof(float) * nnz, cudaMemcpyHostToDevice, st));
+    TGBM_CUDA(cudaMemcpyAsync(d_model.p, flat.data(), sizeof(PNode) * flat.size(), cudaMemcpyHostToDevice, st));
+    const int F = ds.n_features;
+    const size_t smem = (size_t)F * PRED_ROWS * sizeof(float);
+    if (smem <= 48 * 1024) {
+        k_predict_dense<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds, K,
+                                                                                n_nodes, learning_rate, base_score, d_out.p);
+    } else {
+        k_predict_csr<<<(N + 127) / 128, 128, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, d_model.p, n_rounds, K, n_nodes, learning_rate,
+                                                       base_score, d_out.p);
+    }
+    TGBM_CUDA(cudaGetLastError());
+    TGBM_CUDA(cudaMemcpyAsync(out.data(), d_out.p, sizeof(float) * out.size(), cudaMemcpyDeviceToHost, st));
+    TGBM_CUDA(cudaStreamSynchronize(st));
+    cudaStreamDestroy(st);
+}
+
+// ---- predict_transform -------------------------------------------------------------------------
+// regression_obj.h:27-32 (identity / sigmoid), :76-92 (binary: label[y > 0]),
+// multiclass_obj.cu:44-89 (softmax: label of the arg max; softprob: probabilities, class-major)
+__global__ void k_transform(int objective, int K, int n, const float *__restrict__ label, float *__restrict__ y) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (objective == REG_LOGISTIC) {
+        y[i] = __fdiv_rn(1.0f, __fadd_rn(1.0f, portable_expf(-y[i])));
+    } else if (objective == BINARY_LOGISTIC) {
+        y[i] = label[y[i] > 0.f ? 1 : 0];
+    } else if (objective == MULTI_SOFTMAX) {
+        int mk = 0;
+        float mp = y[i];
+        for (int k = 1; k < K; ++k) if (mp < y[(size_t)k * n + i]) { mp = y[(size_t)k * n + i]; mk = k; }
+        y[i] = label[mk];
+    } else if (objective == MULTI_SOFTPROB) {
+        float mx = y[i];
+        for (int k = 1; k < K; ++k) mx = fmaxf(mx, y[(size_t)k * n + i]);
+        float sum = 0.f;
+        for (int k = 0; k < K; ++k) {
+            const float e = portable_expf(__fsub_rn(y[(size_t)k * n + i], mx));
+            y[(size_t)k * n + i] = e;
+            sum = __fadd_rn(sum, e);
+        }
+        for (int k = 0; k < K; ++k) y[(size_t)k * n + i] = __fdiv_rn(y[(size_t)k * n + i], sum);
+    }
+}
+
+void predict_transform(int objective, int num_class, const std::vector<float> &label, int n_rows, std::vector<float> &y) {
+    if (objective == REG_LINEAR || objective == RANK_PAIRWISE || objective == RANK_NDCG || n_rows == 0) return;
+    int K = (int)(y.size() / (size_t)n_rows);
+    if (objective == BINARY_LOGISTIC) TGBM_CHECK(label.size() >= 2, "binary:logistic needs two class labels");
+    if (objective == MULTI_SOFTMAX) TGBM_CHECK((int)label.size() >= K, "multi:softmax needs one label per class");
+    (void)num_class;
+    DevBuf<float> d_y, d_label;
+    d_y.alloc(y.size()); d_label.alloc(std::max<size_t>(label.size(), 1));
+    TGBM_CUDA(cudaMemcpy(d_y.p, y.data(), sizeof(float) * y.size(), cudaMemcpyHostToDevice));
+    if (!label.empty()) TGBM_CUDA(cudaMemcpy(d_label.p, label.data(), sizeof(float) * label.size(), cudaMemcpyHostToDevice));
+    k_transform<<<(n_rows + 255) / 256, 256>>>(objective, K, n_rows, d_label.p, d_y.p);
+    TGBM_CUDA(cudaGetLastError());
+    if (objective == MULTI_SOFTMAX) y.resize(n_rows);
+    TGBM_CUDA(cudaMemcpy(y.data(), d_y.p, sizeof(float) * y.size(), cudaMemcpyDeviceToHost));
+}
+
+// ---- metric on raw scores (Predictor::predict logs it, predictor.cu:20-24) ---------------------
+float metric_score(int objective, const DataSet &ds, int num_class, const std::vector<float> &raw) {
+    const int N = ds.n_rows;
+    if (N == 0) return 0.f;
+    const int K = (int)(raw.size() / (size_t)N);
+    (void)num_class;
+    DevBuf<float> d_y, d_raw, d_out;
+    d_y.alloc(N); d_raw.alloc(raw.size()); d_out.alloc(1);
+    TGBM_CUDA(cudaMemcpy(d_y.p, ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice));
+    TGBM_CUDA(cudaMemcpy(d_raw.p, raw.data(), sizeof(float) * raw.size(), cudaMemcpyHostToDevice));
+    if (need_group_file(objective)) {
+        RankState rs;
+        rs.init(ds, objective, N, nullptr);
+        rs.metric(objective, d_raw.p, d_out.p, nullptr, N, nullptr);
+    } else {
+        DevBuf<double> partial, sum;
+        const int blocks = std::max(1, std::min((N + 255) / 256, 1024));
+        partial.alloc(blocks); sum.alloc(1);
+        k_metric_partial<<<blocks, 256>>>(objective, d_y.p, d_raw.p, N, K, partial.p);
+        k_metric_sum<<<1, 32>>>(partial.p, blocks, sum.p);
+        k_metric_final<<<1, 32>>>(objective, sum.p, N, d_out.p);
+    }
+    TGBM_CUDA(cudaGetLastError());
+    float r = 0;
+    TGBM_CUDA(cudaMemcpy(&r, d_out.p, sizeof(float), cudaMemcpyDeviceToHost));
+    return r;
+}
+
+}  // namespace tgbm
