@@ -106,6 +106,10 @@ TgbmBooster *tgbm_booster_create(int n_rows, const float *val, const int *row_pt
 /* Booster::boost x n_rounds; queues the work on the booster's stream and returns */
 int tgbm_booster_boost(TgbmBooster *b, int n_rounds);
 int tgbm_booster_sync(TgbmBooster *b);
+/* boost + sync, bracketed by CUDA events on the booster's stream: device time of the n_rounds in ms */
+int tgbm_booster_boost_timed(TgbmBooster *b, int n_rounds, float *elapsed_ms);
+/* switch the per-kernel CUDA-event timing of the histogram and partition kernels on or off */
+int tgbm_booster_set_profile(TgbmBooster *b, int on);
 int tgbm_booster_info(TgbmBooster *b, TgbmInfo *out);
 int tgbm_booster_profile(TgbmBooster *b, TgbmProfile *out);
 /* rounds_done * trees_per_round * n_nodes records of 48 bytes */

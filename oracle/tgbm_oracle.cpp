@@ -129,6 +129,8 @@ struct Ctx {
     std::vector<float> idcg;
     std::vector<float> hist_dump;  // level histograms of the first tree (tests): see tgo_first_tree_hist
     std::vector<double> quant_scale;  // per round: 2^s_g, 2^s_h
+    std::vector<double> round_seconds;
+    std::vector<float> gain2;  // [tree][n_nodes]: runner-up |gain| at every evaluated node (how decisive the split was)
     double train_seconds = 0, init_seconds = 0;
     float expf_(float x) const { return p.portable_exp ? portable_expf(x) : expf(x); }
 };
@@ -323,7 +325,17 @@ void get_gradient(const Ctx &c, int round, const float *yp, GH *gh) {
 }
 
 // ---------------------------------------------------------------- histogram arithmetic
-struct Quant { double sg = 1, sh = 1; };  // scales 2^s
+struct Quant { double sg = 1, sh = 1; uint32_t round = 0, k = 0; };  // scales 2^s, dither stream
+
+// Rounding to the grid is dithered: q = floor(v * scale + u) with u in [0,1) a hash of (round, class, row).
+// Plain round-to-nearest would shift every row with the same gradient the same way (all rows share one
+// gradient value per class in the first round), and the shifts would add up coherently in the sums.
+inline double dither(uint32_t round, uint32_t k, uint32_t row, uint32_t which) {
+    return (double)mix32(0x9E3779B9u + which, round, k, row) * (1.0 / 4294967296.0);
+}
+inline double quantize(float v, double scale, uint32_t round, uint32_t k, uint32_t row, uint32_t which) {
+    return floor((double)v * scale + dither(round, k, row, which));
+}
 
 // exponent e with |m| < 2^e
 inline int exp_above(float m) { int e; frexpf(m, &e); return m == 0 ? 0 : e; }
@@ -355,7 +367,7 @@ struct Builder {
     Builder(Ctx &c_, const GH *gh_, Quant q_) : c(c_), gh(gh_), q(q_) {}
 
     inline void qrow(int r, double &g, double &h) const {
-        if (c.p.hist_mode == 1) { g = nearbyint((double)gh[r].g * q.sg); h = nearbyint((double)gh[r].h * q.sh); }
+        if (c.p.hist_mode == 1) { g = quantize(gh[r].g, q.sg, q.round, q.k, (uint32_t)r, 0); h = quantize(gh[r].h, q.sh, q.round, q.k, (uint32_t)r, 1); }
         else { g = gh[r].g; h = gh[r].h; }
     }
     inline float to_f(double v, double s) const { return c.p.hist_mode == 1 ? (float)(v / s) : (float)v; }
@@ -424,7 +436,8 @@ struct Builder {
         nodes[0].base_weight = -nodes[0].sum_g / (nodes[0].sum_h + c.p.lambda);
     }
 
-    struct Split { float gain = 0, miss_g = 0, miss_h = 0, l_g = 0, l_h = 0, fval = 0; bool default_right = false;
+    std::vector<float> gain2;
+    struct Split { float gain = 0, gain2 = 0, miss_g = 0, miss_h = 0, l_g = 0, l_h = 0, fval = 0; bool default_right = false;
                    int nid = -1, fea = -1; unsigned char bid = 0; };
 
     static inline float gainf(float pg, float ph, float lg, float lh, float rg, float rh, float mcw, float lam) {
@@ -440,7 +453,7 @@ struct Builder {
         if (!nd.is_valid) return sp;  // nid stays -1
         const int B = (int)c.cut_val.size();
         const float pg = nd.sum_g, ph = nd.sum_h, mcw = c.p.min_child_weight, lam = c.p.lambda;
-        float best = 0; int besti = -1; bool have = false;
+        float best = 0, second = 0; int besti = -1; bool have = false;
         std::vector<float> Pg(B), Ph(B);
         for (int f = 0; f < c.F; ++f) {
             const int b0 = c.cut_ptr[f], b1 = c.cut_ptr[f + 1];
@@ -461,7 +474,8 @@ struct Builder {
                 const float gl = fmaxf(0.f, gainf(pg, ph, lg2, lh2, pg - lg2, ph - lh2, mcw, lam));
                 const float gn = gl > gr ? gl : -gr;
                 // arg abs max, ties -> smaller index (:330-335)
-                if (!have || fabsf(gn) > fabsf(best)) { best = gn; besti = i; have = true; }
+                if (!have || fabsf(gn) > fabsf(best)) { if (have) second = fmaxf(second, fabsf(best)); best = gn; besti = i; have = true; }
+                else second = fmaxf(second, fabsf(gn));
             }
         }
         sp.nid = node_id;
@@ -470,6 +484,7 @@ struct Builder {
         // recompute the winner's record (:365-389)
         sp.fea = f;
         sp.gain = fabsf(best);
+        sp.gain2 = second;
         sp.bid = (unsigned char)(besti - b0);
         sp.default_right = best < 0;
         // prefix of the winning feature again (Pg/Ph hold the last computed values for all features)
@@ -568,6 +583,7 @@ struct Builder {
         const int d = c.p.depth;
         nid.assign(c.N, 0);
         init_tree();
+        gain2.assign(nodes.size(), 0.f);
         level_hist.assign(d, {});
         for (int level = 0; level < d; ++level) {
             const int n_level = 1 << level, off = n_level - 1;
@@ -593,7 +609,7 @@ struct Builder {
                 }
             }
             for (int n = 0; n < n_level; ++n)
-                if (!LH[n].g.empty()) sps[n] = evaluate(LH[n], off + n);
+                if (!LH[n].g.empty()) { sps[n] = evaluate(LH[n], off + n); gain2[off + n] = sps[n].gain2; }
             if (dump_hist) {
                 const int B = (int)c.cut_val.size();
                 for (int n = 0; n < n_level; ++n)
@@ -620,7 +636,7 @@ void init_base_score(Ctx &c, std::vector<GH> &gh) {
     double sg = 0, sh = 0;
     if (c.p.hist_mode == 1) {
         Quant q = choose_quant(c, gh.data(), c.N);
-        for (int i = 0; i < c.N; ++i) { sg += nearbyint((double)gh[i].g * q.sg); sh += nearbyint((double)gh[i].h * q.sh); }
+        for (int i = 0; i < c.N; ++i) { sg += quantize(gh[i].g, q.sg, 0xffffffffu, 0, (uint32_t)i, 0); sh += quantize(gh[i].h, q.sh, 0xffffffffu, 0, (uint32_t)i, 1); }
         sg /= q.sg; sh /= q.sh;
     } else {
         for (int i = 0; i < c.N; ++i) { sg += gh[i].g; sh += gh[i].h; }
@@ -719,18 +735,22 @@ void train(Ctx &c) {
     c.init_seconds = now_s() - t_init;
     const double t0 = now_s();
     for (int r = 0; r < c.p.n_trees; ++r) {  // src/thundergbm/trainer.cu:44-47, include/thundergbm/booster.h:76-93
+        const double tr0 = now_s();
         get_gradient(c, r, c.ypred.data(), gh.data());
         Quant q;
         if (c.p.hist_mode == 1) q = choose_quant(c, gh.data(), (size_t)K * N);
         c.quant_scale.push_back(q.sg); c.quant_scale.push_back(q.sh);
         for (int k = 0; k < K; ++k) {
+            q.round = (uint32_t)r; q.k = (uint32_t)k;
             Builder b(c, gh.data() + (size_t)k * N, q);
             b.build(r == 0 && k == 0 && c.p.keep_nid);
             predict_in_training(c, b, c.ypred.data() + (size_t)k * N);
             c.trees.insert(c.trees.end(), b.nodes.begin(), b.nodes.end());
+            c.gain2.insert(c.gain2.end(), b.gain2.begin(), b.gain2.end());
             if (c.p.keep_nid) c.nid_keep.insert(c.nid_keep.end(), b.nid.begin(), b.nid.end());
         }
         c.metric.push_back(metric(c, c.ypred.data()));
+        c.round_seconds.push_back(now_s() - tr0);
     }
     c.train_seconds = now_s() - t0;
 }
@@ -777,6 +797,8 @@ const float *tgo_ypred(void *h) { return ((Ctx *)h)->ypred.data(); }
 const float *tgo_labels(void *h) { return ((Ctx *)h)->label.data(); }
 const int *tgo_nid(void *h) { return ((Ctx *)h)->nid_keep.data(); }
 const double *tgo_quant_scale(void *h) { return ((Ctx *)h)->quant_scale.data(); }
+const float *tgo_gain2(void *h) { return ((Ctx *)h)->gain2.data(); }
+const double *tgo_round_seconds(void *h) { return ((Ctx *)h)->round_seconds.data(); }
 long tgo_hist_dump_size(void *h) { return (long)((Ctx *)h)->hist_dump.size(); }
 const float *tgo_hist_dump(void *h) { return ((Ctx *)h)->hist_dump.data(); }
 

@@ -57,7 +57,7 @@ def lib():
         l.tgo_train_seconds.argtypes = [vp]; l.tgo_train_seconds.restype = C.c_double
         l.tgo_init_seconds.argtypes = [vp]; l.tgo_init_seconds.restype = C.c_double
         l.tgo_hist_dump_size.argtypes = [vp]; l.tgo_hist_dump_size.restype = C.c_long
-        for n in ('cut_val', 'cut_ptr', 'bins', 'trees', 'metric', 'ypred', 'labels', 'nid', 'quant_scale', 'hist_dump'):
+        for n in ('cut_val', 'cut_ptr', 'bins', 'trees', 'metric', 'ypred', 'labels', 'nid', 'quant_scale', 'hist_dump', 'round_seconds', 'gain2'):
             getattr(l, 'tgo_' + n).argtypes = [vp]
             getattr(l, 'tgo_' + n).restype = vp
         l.tgo_predict_raw.argtypes = [C.c_int, vp, vp, vp, C.c_int, vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, vp]
@@ -110,6 +110,8 @@ def train(data, objective='reg:linear', depth=6, n_trees=40, max_num_bin=255, le
         r.ypred = _view(l.tgo_ypred(h), (K, data.n_rows), np.float32)
         r.labels = _view(l.tgo_labels(h), (l.tgo_n_labels(h),), np.float32)
         r.quant_scale = _view(l.tgo_quant_scale(h), (n_trees, 2), np.float64)
+        r.gain2 = _view(l.tgo_gain2(h), (n_trees, K, nn), np.float32)
+        r.round_seconds = _view(l.tgo_round_seconds(h), (n_trees,), np.float64)
         if keep_nid:
             r.nid = _view(l.tgo_nid(h), (n_trees * K, data.n_rows), np.int32)
             r.hist_dump = _view(l.tgo_hist_dump(h), (l.tgo_hist_dump_size(h),), np.float32)

@@ -1,0 +1,158 @@
+"""The reference's own extern "C" surface (what its Python wrapper binds), through ctypes."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _vp(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _train(lib, d, objective, depth=5, n_trees=4, lr=0.3, max_bin=64, num_class=1):
+    val = np.ascontiguousarray(d.val, np.float32); rp = np.ascontiguousarray(d.row_ptr, np.int32)
+    col = np.ascontiguousarray(d.col, np.int32); y = np.ascontiguousarray(d.y, np.float32)
+    grp = np.ascontiguousarray(d.group, np.int32)
+    model = C.c_void_p(None)
+    nc = C.c_int(num_class); per = C.c_int(0)
+    gl = (C.c_float * 64)()
+    lib.sparse_train_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(y), depth, n_trees, 1, 1.0, 1.0, 1.0, max_bin, 0,
+                            1.0, 0, 1, lr, objective.encode(), C.byref(nc), b'hist', C.byref(model), C.byref(per), gl,
+                            _vp(grp) if grp.size else None, int(grp.size))
+    assert model.value, lib.tgbm_last_error().decode()
+    return model, nc.value, per.value, np.array(gl[:max(nc.value, 1)], np.float32)
+
+
+def _predict(lib, d, model, n_trees, per, objective, nc, lr, gl, n_out):
+    val = np.ascontiguousarray(d.val, np.float32); rp = np.ascontiguousarray(d.row_ptr, np.int32)
+    col = np.ascontiguousarray(d.col, np.int32)
+    out = np.zeros(n_out, np.float32)
+    glc = (C.c_float * len(gl))(*gl)
+    lib.sparse_predict_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(out), C.byref(model), n_trees, per,
+                              objective.encode(), nc, lr, glc, None, 0, 0)
+    return out
+
+
+def test_train_predict_save_load_roundtrip(gpu, orc, cases, tmp_path):
+    from thundergbm_b200 import _lib
+    lib = _lib.lib()
+    d, _ = cases('fixture_bin')
+    model, nc, per, gl = _train(lib, d, 'binary:logistic')
+    assert nc == 2 and per == 1 and gl.tolist() == [-1.0, 1.0]
+    n_nodes = np.zeros(4, np.int32)
+    lib.get_n_nodes(C.byref(model), _vp(n_nodes), 4, 1)
+    assert (n_nodes == 63).all()
+    arrs = [np.zeros(63, np.int32) for _ in range(4)] + [np.zeros(63, np.float32) for _ in range(3)]
+    lib.get_a_tree(C.byref(model), 0, 63, *[_vp(a) for a in arrs])
+    left, right, default, feat, thr, val, w = arrs
+    o = orc.train(d, objective='binary:logistic', depth=5, n_trees=4, learning_rate=0.3, max_num_bin=64, hist_mode=1)
+    t0 = o.trees[0, 0]
+    leaf = t0['is_leaf'] == 1
+    assert np.array_equal(feat, t0['split_feature_id']) and np.array_equal(thr, t0['split_value'])
+    assert np.array_equal(left[~leaf], t0['lch_index'][~leaf]) and (left[leaf] == -1).all()
+    assert np.array_equal(val[leaf], t0['base_weight'][leaf]) and np.array_equal(w, t0['sum_h'])
+    pred = _predict(lib, d, model, 4, per, 'binary:logistic', nc, 0.3, gl, d.n_rows)
+    assert set(np.unique(pred)) <= {-1.0, 1.0}
+    # the scikit predict path does not apply the base score (src/thundergbm/scikit_tgbm.cpp:87-90)
+    raw = orc.predict_raw(d, o.trees, 0.3, 0.0, n_features=d.n_cols)[0]
+    assert np.array_equal(pred, np.where(raw > 0, 1.0, -1.0).astype(np.float32))
+    # save -> load -> identical predictions, and the file has the reference's layout
+    path = str(tmp_path / 'm.model').encode()
+    glc = (C.c_float * 2)(*gl)
+    lib.save(path, b'binary:logistic', 0.3, nc, 4, per, C.byref(model), glc)
+    lr2 = C.c_float(0); nc2 = C.c_int(0); nt2 = C.c_int(0); per2 = C.c_int(0); model2 = C.c_void_p(None)
+    lib.load_model(path, C.byref(lr2), C.byref(nc2), C.byref(nt2), C.byref(per2), C.byref(model2))
+    assert model2.value and (round(lr2.value, 6), nc2.value, nt2.value, per2.value) == (0.3, 2, 4, 1)
+    gl2 = (C.c_float * 2)()
+    lib.load_config(path, gl2)
+    assert list(gl2) == [-1.0, 1.0]
+    pred2 = _predict(lib, d, model2, 4, 1, 'binary:logistic', 2, 0.3, gl, d.n_rows)
+    assert np.array_equal(pred, pred2)
+    raw_file = open(path.decode(), 'rb').read()
+    assert raw_file[:4] == (15).to_bytes(4, 'little') and raw_file[4:19] == b'binary:logistic'
+    assert len(raw_file) == 4 + 15 + 16 + 4 + 8 + 4 + 4 * (4 + 8 + 63 * 48)
+    lib.model_free(C.byref(model)); lib.model_free(C.byref(model2))
+    assert model.value is None
+
+
+def test_multiclass_and_softprob(gpu, orc, cases):
+    from thundergbm_b200 import _lib
+    lib = _lib.lib()
+    d, _ = cases('c3_covtype_small')
+    d = d.rows(0, 5000)
+    for obj in ('multi:softmax', 'multi:softprob'):
+        model, nc, per, gl = _train(lib, d, obj, depth=4, n_trees=2, lr=0.5)
+        assert nc == 7 and per == 7
+        n_out = d.n_rows * (7 if obj == 'multi:softprob' else 1)
+        pred = _predict(lib, d, model, 2, per, obj, nc, 0.5, gl, n_out)
+        if obj == 'multi:softprob':
+            p = pred.reshape(7, d.n_rows)  # class-major, as the reference lays it out
+            assert np.allclose(p.sum(axis=0), 1.0, atol=1e-5)
+        else:
+            assert set(np.unique(pred)) <= set(gl.tolist())
+            assert (pred == d.y).mean() > 0.3
+        lib.model_free(C.byref(model))
+
+
+def test_errors_leave_model_null(gpu, cases):
+    from thundergbm_b200 import _lib
+    lib = _lib.lib()
+    d, _ = cases('fixture_reg')
+    val = np.ascontiguousarray(d.val, np.float32); rp = np.ascontiguousarray(d.row_ptr, np.int32)
+    col = np.ascontiguousarray(d.col, np.int32); y = np.ascontiguousarray(d.y, np.float32)
+    model = C.c_void_p(123)
+    nc = C.c_int(1); per = C.c_int(0); gl = (C.c_float * 4)()
+    lib.sparse_train_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(y), 5, 2, 1, 1.0, 1.0, 1.0, 64, 0, 1.0, 0, 1, 0.3,
+                            b'reg:linear', C.byref(nc), b'exact', C.byref(model), C.byref(per), gl, None, 0)
+    assert model.value is None and b'hist' in lib.tgbm_last_error()
+
+
+def test_python_mirror_classes(gpu, cases):
+    from thundergbm_b200.thundergbm import TGBMClassifier, TGBMRegressor
+    import scipy.sparse as sp
+    d, _ = cases('c1_dense_reg')
+    X = sp.csr_matrix((d.val, d.col, d.row_ptr), shape=(d.n_rows, d.n_cols))
+    reg = TGBMRegressor(depth=5, n_trees=10, learning_rate=0.5, verbose=0)
+    reg.fit(X, d.y)
+    p = reg.predict(X)
+    # the scikit predict path drops the base score, exactly like the reference's wrapper
+    assert np.sqrt(np.mean((p + reg_base(d) - d.y) ** 2)) < np.std(d.y) * 0.6
+    d2, _ = cases('fixture_bin')
+    X2 = sp.csr_matrix((d2.val, d2.col, d2.row_ptr), shape=(d2.n_rows, d2.n_cols))
+    clf = TGBMClassifier(depth=5, n_trees=6, learning_rate=0.5, verbose=0, objective='binary:logistic')
+    clf.fit(X2, d2.y)
+    assert (clf.predict(X2) == d2.y).mean() > 0.8
+    with pytest.raises(RuntimeError, match='binary:logistic'):
+        TGBMClassifier(depth=3, n_trees=1, verbose=0).fit(X2, d2.y)  # multi:softmax with two labels
+
+
+def reg_base(d):
+    return float(np.mean(d.y))
+
+
+def test_cli_train_and_predict(gpu, tmp_path):
+    """thundergbm-train <conf> writes ./tgbm.model; thundergbm-predict <conf> reads it and logs the metric."""
+    import subprocess
+    from thundergbm_b200 import synth
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d = synth.dense_regression(2000, 8, seed=5)
+    data = tmp_path / 'train.txt'
+    with open(data, 'w') as fh:
+        for i in range(d.n_rows):
+            a, b = d.row_ptr[i], d.row_ptr[i + 1]
+            fh.write(f'{d.y[i]:.9g} ' + ' '.join(f'{c + 1}:{v:.9g}' for c, v in zip(d.col[a:b], d.val[a:b])) + '\n')
+    conf = tmp_path / 'run.conf'
+    conf.write_text(f'data={data}\ndepth=4\nn_trees=5\nlearning_rate=0.5\nobjective=reg:linear\n')
+    out = subprocess.run([os.path.join(root, 'thundergbm_b200', 'bin', 'thundergbm-train'), str(conf)], cwd=tmp_path,
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert '[5/5] RMSE = ' in out.stdout and os.path.exists(tmp_path / 'tgbm.model')
+    rmse_train = float(out.stdout.split('[5/5] RMSE = ')[1].split()[0])
+    out2 = subprocess.run([os.path.join(root, 'thundergbm_b200', 'bin', 'thundergbm-predict'), str(conf)], cwd=tmp_path,
+                          capture_output=True, text=True, timeout=300)
+    assert out2.returncode == 0, out2.stderr
+    rmse_pred = float(out2.stdout.split('RMSE = ')[1].split()[0])
+    assert abs(rmse_pred - rmse_train) < 1e-4

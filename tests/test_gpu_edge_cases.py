@@ -1,0 +1,131 @@
+"""Edge cases of the inputs: ragged and empty rows, constant and absent features, tiny data, extreme parameters."""
+import numpy as np
+import pytest
+
+from thundergbm_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _pair(orc, d, **p):
+    from thundergbm_b200.booster import Booster
+    o = orc.train(d, hist_mode=1, keep_nid=1, **p)
+    b = Booster(d, keep_nid=1, **p)
+    b.boost(p['n_trees'])
+    return o, b
+
+
+def _rand_csr(n, f, density, seed, n_values=None):
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, f)).astype(np.float32)
+    if n_values:
+        x = np.round(x * n_values / 4).astype(np.float32)
+    x[rng.random((n, f)) > density] = 0
+    y = (x[:, 0] - x[:, 1 % f] + 0.3 * rng.standard_normal(n)).astype(np.float32)
+    return synth.dense_to_csr(x, y)
+
+
+@pytest.mark.parametrize('n,f,density', [(1, 3, 1.0), (2, 1, 1.0), (33, 5, 0.5), (1000, 40, 0.3), (5000, 70, 0.9),
+                                         (1023, 33, 0.7), (1025, 31, 1.0)])
+def test_ragged_shapes(gpu, orc, n, f, density):
+    d = _rand_csr(n, f, density, seed=n + f)
+    if d.nnz == 0:
+        d = _rand_csr(n, f, 1.0, seed=n + f + 1)
+    p = dict(objective='reg:linear', depth=4, n_trees=3, max_num_bin=255, learning_rate=0.5)
+    o, b = _pair(orc, d, **p)
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid) and np.array_equal(b.ypred(), o.ypred)
+    b.close()
+
+
+def test_empty_rows_and_absent_features(gpu, orc):
+    d = _rand_csr(3000, 12, 0.4, seed=7)
+    # rows 10..19 empty, feature 5 never present, feature 11 constant
+    x = np.zeros((3000, 12), np.float32)
+    rows = np.repeat(np.arange(3000), np.diff(d.row_ptr))
+    x[rows, d.col] = d.val
+    x[10:20] = 0
+    x[:, 5] = 0
+    x[:, 11] = 3.5
+    d2 = synth.dense_to_csr(x, d.y)
+    p = dict(objective='reg:linear', depth=5, n_trees=4, max_num_bin=255, learning_rate=0.3)
+    o, b = _pair(orc, d2, **p)
+    assert b.trees().tobytes() == o.trees.tobytes() and np.array_equal(b.ypred(), o.ypred)
+    cp = b.cuts()[1]
+    assert cp[6] - cp[5] == 0 and cp[12] - cp[11] == 1
+    b.close()
+
+
+@pytest.mark.parametrize('max_bin', [2, 16, 64, 255])
+def test_small_bin_budgets(gpu, orc, max_bin):
+    d = _rand_csr(4000, 9, 1.0, seed=max_bin)
+    p = dict(objective='reg:linear', depth=5, n_trees=3, max_num_bin=max_bin, learning_rate=0.5)
+    o, b = _pair(orc, d, **p)
+    assert b.info.n_bins == o.n_bins
+    assert b.trees().tobytes() == o.trees.tobytes()
+    b.close()
+
+
+def test_low_cardinality_collisions(gpu, orc):
+    """Few distinct values per feature: many rows hit the same bins (shared-memory atomics on one address)."""
+    d = _rand_csr(20000, 8, 1.0, seed=3, n_values=3)
+    p = dict(objective='binary:logistic', depth=6, n_trees=4, max_num_bin=255, learning_rate=0.3)
+    d.y = (d.y > 0).astype(np.float32)
+    o, b = _pair(orc, d, **p)
+    assert b.trees().tobytes() == o.trees.tobytes() and np.array_equal(b.nid(), o.nid)
+    b.close()
+
+
+@pytest.mark.parametrize('depth', [1, 2, 10])
+def test_depth_extremes(gpu, orc, depth):
+    d = _rand_csr(6000, 6, 1.0, seed=depth)
+    p = dict(objective='reg:linear', depth=depth, n_trees=2, max_num_bin=64, learning_rate=0.5, gamma=0.0)
+    o, b = _pair(orc, d, **p)
+    assert b.trees().tobytes() == o.trees.tobytes() and np.array_equal(b.ypred(), o.ypred)
+    b.close()
+
+
+def test_accumulator_window_flush(gpu, orc):
+    """More rows per CTA than one int32 accumulation window holds (quant_bits 21 -> 512-row windows)."""
+    d = synth.higgs_like(300_000, seed=5)
+    p = dict(objective='binary:logistic', depth=3, n_trees=2, max_num_bin=255, learning_rate=0.1, quant_bits=21)
+    o, b = _pair(orc, d, **p)
+    assert b.trees().tobytes() == o.trees.tobytes()
+    b.close()
+
+
+def test_rejects_what_is_out_of_scope(gpu):
+    from thundergbm_b200.booster import Booster
+    d = _rand_csr(100, 4, 1.0, seed=1)
+    with pytest.raises(RuntimeError, match='max_num_bin'):
+        Booster(d, objective='reg:linear', depth=3, n_trees=1, max_num_bin=300)
+    with pytest.raises(RuntimeError, match='objective'):
+        Booster(d, objective='reg:nope', depth=3, n_trees=1)
+    with pytest.raises(RuntimeError, match='depth'):
+        Booster(d, objective='reg:linear', depth=0, n_trees=1)
+
+
+def test_full_size_properties(gpu):
+    """Size-independent properties at a multi-million-row size: every feature's root histogram sums to the root
+    total, every row ends in exactly one valid leaf, the error rate falls."""
+    from thundergbm_b200.booster import Booster
+    d = synth.higgs_like(2_000_000, seed=9)
+    b = Booster(d, objective='binary:logistic', depth=8, n_trees=4, max_num_bin=255, learning_rate=0.1, keep_nid=1)
+    b.boost(4)
+    t = b.trees()
+    nid = b.nid()
+    for r in range(4):
+        nodes = t[r, 0]
+        leaf = nodes[nid[r]]
+        assert (leaf['is_valid'] == 1).all() and (leaf['is_leaf'] == 1).all()
+        # row counts per leaf add up
+        assert np.bincount(nid[r], minlength=len(nodes)).sum() == d.n_rows
+        # children sums add up to the parent within float rounding
+        inner = np.nonzero((nodes['is_valid'] == 1) & (nodes['lch_index'] > 0) & (nodes['gain'] > 0) & (nodes['split_feature_id'] >= 0))[0]
+        for i in inner[:50]:
+            l, rr = nodes[nodes[i]['lch_index']], nodes[nodes[i]['rch_index']]
+            if l['is_valid'] and rr['is_valid']:
+                assert abs((l['sum_h'] + rr['sum_h']) - nodes[i]['sum_h']) <= 1e-5 * nodes[i]['sum_h'] + 1e-3
+    m = b.metrics()
+    assert m[-1] < m[0] + 1e-6
+    b.close()

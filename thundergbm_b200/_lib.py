@@ -46,6 +46,8 @@ def load() -> C.CDLL:
     lib.tgbm_booster_create.argtypes = [C.c_int, vp, vp, vp, vp, vp, C.c_int, P(TgbmParam), vp]
     lib.tgbm_booster_boost.argtypes = [vp, C.c_int]
     lib.tgbm_booster_sync.argtypes = [vp]
+    lib.tgbm_booster_set_profile.argtypes = [vp, C.c_int]
+    lib.tgbm_booster_boost_timed.argtypes = [vp, C.c_int, fp]
     lib.tgbm_booster_info.argtypes = [vp, P(TgbmInfo)]
     lib.tgbm_booster_profile.argtypes = [vp, P(TgbmProfile)]
     for name in ('get_trees', 'get_metrics', 'get_ypred', 'get_bins', 'get_nid', 'get_root_hist', 'get_quant_scale',

@@ -78,6 +78,15 @@ class Booster:
     def boost(self, n_rounds: int):
         _lib.check(self._lib.tgbm_booster_boost(self.handle, n_rounds))
 
+    def boost_timed(self, n_rounds: int) -> float:
+        """boost(n_rounds) + sync; returns the device time in milliseconds (CUDA events on the booster's stream)."""
+        ms = C.c_float(0)
+        _lib.check(self._lib.tgbm_booster_boost_timed(self.handle, n_rounds, C.byref(ms)))
+        return ms.value
+
+    def set_profile(self, on: bool):
+        _lib.check(self._lib.tgbm_booster_set_profile(self.handle, int(on)))
+
     def sync(self):
         _lib.check(self._lib.tgbm_booster_sync(self.handle))
 

@@ -248,6 +248,9 @@ void Booster::init(const DataSet &ds) {
         p.num_class = 1;
     }
     p.tree_per_rounds = m.K;
+    // with two labels the reference's Softmax::get_gradient aborts on a size check (multiclass_obj.cu:9); binary:logistic is the 2-class objective
+    TGBM_CHECK(!((m.objective == MULTI_SOFTMAX || m.objective == MULTI_SOFTPROB) && p.num_class <= 2),
+               "multi:softmax / multi:softprob need more than two classes; use binary:logistic for two");
     m.num_class = p.num_class;
 
     m.find_cuts_and_bins(ds);
@@ -316,7 +319,7 @@ void BoosterImpl::gradient(int round) {
     }
     if (comm && comm->active()) comm->allreduce(maxbits.p, 2, Comm::U32, Comm::MAX, stream);
     const int blocks = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
-    k_quantize<<<dim3(blocks, K), tb, 0, stream>>>(gh.p, N, maxbits.p, p.quant_bits, ghq.p, root_sum.p, qinfo.p);
+    k_quantize<<<dim3(blocks, K), tb, 0, stream>>>(gh.p, N, maxbits.p, p.quant_bits, (uint32_t)round, (uint32_t)row_offset, ghq.p, root_sum.p, qinfo.p);
     ++launches;
     if (comm && comm->active()) comm->allreduce(root_sum.p, 2 * (size_t)K, Comm::I64, Comm::SUM, stream);
     if (round >= 0 && round < (int)qinfo_log.n)

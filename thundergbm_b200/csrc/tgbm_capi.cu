@@ -317,6 +317,22 @@ TgbmBooster *tgbm_booster_create(int n_rows, const float *val, const int *row_pt
 
 int tgbm_booster_boost(TgbmBooster *b, int n_rounds) { return guard([&] { b->b->boost(n_rounds); }); }
 int tgbm_booster_sync(TgbmBooster *b) { return guard([&] { b->b->sync(); }); }
+int tgbm_booster_set_profile(TgbmBooster *b, int on) { return guard([&] { b->b->set_profile(on != 0); }); }
+int tgbm_booster_boost_timed(TgbmBooster *b, int n_rounds, float *elapsed_ms) {
+    return guard([&] {
+        cudaEvent_t e0, e1;
+        TGBM_CUDA(cudaEventCreate(&e0));
+        TGBM_CUDA(cudaEventCreate(&e1));
+        b->b->sync();
+        TGBM_CUDA(cudaEventRecord(e0, b->b->stream()));
+        b->b->boost(n_rounds);
+        TGBM_CUDA(cudaEventRecord(e1, b->b->stream()));
+        b->b->sync();
+        TGBM_CUDA(cudaEventElapsedTime(elapsed_ms, e0, e1));
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+    });
+}
 int tgbm_booster_info(TgbmBooster *b, TgbmInfo *o) {
     return guard([&] {
         o->n_rows = b->n_rows; o->n_features = b->b->n_features(); o->fpad = b->b->fpad(); o->n_bins = b->b->n_bins();

@@ -50,8 +50,7 @@ __host__ __device__ inline float pow2i(int e) {
     c.u = (uint32_t)(e + 127) << 23;
     return c.f;
 }
-__host__ __device__ inline float portable_expf(float x) {
-#ifdef __CUDA_ARCH__
+__device__ inline float portable_expf(float x) {
     if (!(x <= 88.72283f)) return x != x ? x : __int_as_float(0x7f800000);
     if (x < -103.9f) return 0.0f;
     float n = rintf(__fmul_rn(x, 1.44269504088896341f));
@@ -67,13 +66,18 @@ __host__ __device__ inline float portable_expf(float x) {
     int k = (int)n;
     int k1 = k / 2, k2 = k - k1;
     return __fmul_rn(__fmul_rn(e, pow2i(k1)), pow2i(k2));
-#else
-    (void)x;
-    return 0.f;
-#endif
 }
 
-// (g,h) quantisation grid of one boosting round: v_q = rn(v * scale), scale a power of two
+// counter-based hash: LambdaRank partner sampling and the dither of the gradient quantisation
+__host__ __device__ inline uint32_t mix32(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    uint64_t z = ((uint64_t)a << 32 | b) * 0x9E3779B97F4A7C15ull + ((uint64_t)c << 32 | d);
+    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull;
+    z ^= z >> 27; z *= 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return (uint32_t)(z >> 32);
+}
+
+// (g,h) quantisation grid of one boosting round: v_q = floor(v * scale + dither), scale a power of two
 struct QuantInfo {
     double sg, sh;          // 2^s
     double inv_sg, inv_sh;  // 2^-s

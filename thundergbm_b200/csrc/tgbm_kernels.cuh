@@ -45,7 +45,7 @@ struct SplitRec {  // best candidate of one (node, feature)
 
 // ------------------------------------------------------------------ cut points
 // key = feature id in the high word, order-preserving image of the float in the low word
-__global__ void k_make_keys(const float *__restrict__ val, const int *__restrict__ col, size_t nnz,
+static __global__ void k_make_keys(const float *__restrict__ val, const int *__restrict__ col, size_t nnz,
                             unsigned long long *__restrict__ keys) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nnz; i += (size_t)gridDim.x * blockDim.x) {
         unsigned u = __float_as_uint(val[i]);
@@ -62,7 +62,7 @@ __device__ inline float key_to_float(unsigned long long k) {
 }
 
 // ustart[f] = number of unique (feature,value) keys with feature < f
-__global__ void k_feature_bounds(const unsigned long long *__restrict__ ukeys, long long nu, int F, long long *__restrict__ ustart) {
+static __global__ void k_feature_bounds(const unsigned long long *__restrict__ ukeys, long long nu, int F, long long *__restrict__ ustart) {
     const int f = blockIdx.x * blockDim.x + threadIdx.x;
     if (f > F) return;
     const unsigned long long target = (unsigned long long)(unsigned)f << 32;
@@ -76,7 +76,7 @@ __global__ void k_feature_bounds(const unsigned long long *__restrict__ ukeys, l
 
 // HistCut::get_cut_points_single (src/thundergbm/hist_cut.cu:232-286): stride s = u / max_bin;
 // s == 0 keeps every distinct value, else positions 0, s, ..., (max_bin-1) s
-__global__ void k_select_cuts(const unsigned long long *__restrict__ ukeys, long long nu, const long long *__restrict__ ustart,
+static __global__ void k_select_cuts(const unsigned long long *__restrict__ ukeys, long long nu, const long long *__restrict__ ustart,
                               const int *__restrict__ stride, const int *__restrict__ cut_ptr, int max_bin,
                               float *__restrict__ cut_val, int *__restrict__ cut_fid) {
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nu; i += (long long)gridDim.x * blockDim.x) {
@@ -95,7 +95,7 @@ __global__ void k_select_cuts(const unsigned long long *__restrict__ ukeys, long
 
 // HistTreeBuilder_single::get_bin_ids (hist_tree_builder_single.cu:81-119): clamped upper bound,
 // bin = min(#cuts <= v, n_cuts - 1); stored as the feature-local id in both layouts
-__global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val,
+static __global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val,
                             int n_rows, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val, int Fpad,
                             size_t Npad, unsigned char *__restrict__ bins, unsigned char *__restrict__ binsT) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
@@ -132,7 +132,7 @@ __device__ inline void track_max(float ag, float h, unsigned *maxbits) {
 }
 
 // SquareLoss / LogisticLoss gradients (include/thundergbm/objective/regression_obj.h:129-154)
-__global__ void k_grad_pointwise(const float *__restrict__ y, const float *__restrict__ yp, int n, int logistic,
+static __global__ void k_grad_pointwise(const float *__restrict__ y, const float *__restrict__ yp, int n, int logistic,
                                  float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     float g = 0.f, h = 0.f;
@@ -151,7 +151,7 @@ __global__ void k_grad_pointwise(const float *__restrict__ y, const float *__res
 }
 
 // Softmax::get_gradient (src/thundergbm/objective/multiclass_obj.cu:7-35), class-major gh[k*N+i]
-__global__ void k_grad_softmax(const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
+static __global__ void k_grad_softmax(const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
                                float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     float mg = 0.f, mh = 0.f;
@@ -175,8 +175,13 @@ __global__ void k_grad_softmax(const float *__restrict__ y, const float *__restr
 
 // Round the round's gradients to the fixed-point grid and sum them per class (root node sums,
 // Tree::init2, src/thundergbm/tree.cu:31).  grid = (blocks, K)
-__global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned *__restrict__ maxbits, int quant_bits,
-                           int2 *__restrict__ ghq, unsigned long long *__restrict__ root_sum, QuantInfo *__restrict__ qinfo) {
+//
+// The rounding is dithered, q = floor(v * scale + u) with u in [0,1) a hash of (round, class, global row):
+// round-to-nearest would move every row that carries the same gradient the same way (in the first round all rows
+// of a class do), and those shifts would add up coherently in the histogram sums.
+static __global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned *__restrict__ maxbits, int quant_bits,
+                           uint32_t round, uint32_t row_offset, int2 *__restrict__ ghq,
+                           unsigned long long *__restrict__ root_sum, QuantInfo *__restrict__ qinfo) {
     const int k = blockIdx.y;
     const int eg = exp_above(__uint_as_float(maxbits[0])), eh = exp_above(__uint_as_float(maxbits[1]));
     const double sg = pow2d(quant_bits - eg), sh = pow2d(quant_bits - eh);
@@ -187,7 +192,10 @@ __global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned 
     long long tg = 0, th = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         const float2 v = gh[(size_t)k * n + i];
-        const int qg = (int)__double2ll_rn((double)v.x * sg), qh = (int)__double2ll_rn((double)v.y * sh);
+        const uint32_t row = row_offset + (uint32_t)i;
+        const double ug = (double)mix32(0x9E3779B9u, round, (uint32_t)k, row) * (1.0 / 4294967296.0);
+        const double uh = (double)mix32(0x9E3779B9u + 1u, round, (uint32_t)k, row) * (1.0 / 4294967296.0);
+        const int qg = (int)__double2ll_rd((double)v.x * sg + ug), qh = (int)__double2ll_rd((double)v.y * sh + uh);
         ghq[(size_t)k * n + i] = make_int2(qg, qh);
         tg += qg; th += qh;
     }
@@ -201,7 +209,7 @@ __global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned 
 
 // ------------------------------------------------------------------ tree set-up
 // Tree::init2 (src/thundergbm/tree.cu:8-39)
-__global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, const unsigned long long *__restrict__ root_sum,
+static __global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, const unsigned long long *__restrict__ root_sum,
                             const QuantInfo *__restrict__ q, float lambda, int n_rows, int *__restrict__ seg_begin,
                             int *__restrict__ seg_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -227,7 +235,7 @@ __global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, const uns
 // ------------------------------------------------------------------ histogram build
 // Which sibling to build (the one with fewer rows over all ranks, ties -> left:
 // hist_tree_builder_single.cu:466) and the work list of the level.  One block.
-__global__ void k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+static __global__ void k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
                             const int *__restrict__ gcnt, int *__restrict__ built_right, HistWork *__restrict__ work,
                             int *__restrict__ tile_base, TreeCtl *__restrict__ ctl) {
     if (threadIdx.x != 0) return;
@@ -292,7 +300,7 @@ __device__ __forceinline__ void rotate_row(uint32_t (&w)[8], int L) {
 // to the int64 histogram in global memory when the node changes or before they could overflow
 // (`window_rows` rows of at most 2^quant_bits each).
 template <bool GATHER>
-__global__ void __launch_bounds__(HIST_THREADS, 2)
+static __global__ void __launch_bounds__(HIST_THREADS, 2)
 k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__restrict__ rec_idx,
        const int2 *__restrict__ rec_gh, const HistWork *__restrict__ work, const int *__restrict__ tile_base,
        const TreeCtl *__restrict__ ctl, const int *__restrict__ cut_ptr, const int *__restrict__ cut_fid,
@@ -404,7 +412,7 @@ __device__ __forceinline__ float split_gain(float pg, float ph, float lg, float 
 // Sibling subtraction, per-feature prefix scan, missing sums, gains and per-feature argmax
 // (hist_tree_builder_single.cu:257-347 for the root, :538-540 and :614-704 for sibling pairs).
 // grid = (F, pairs); block = 64: warp 0 evaluates the left child, warp 1 the right child.
-__global__ void __launch_bounds__(64)
+static __global__ void __launch_bounds__(64)
 k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode *__restrict__ nodes,
        const int *__restrict__ built_right, const long long *__restrict__ built, const long long *__restrict__ parent,
        long long *__restrict__ full, const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs) {
@@ -495,7 +503,7 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode 
 
 // Per-node argmax over the features, SplitPoint decode and update_tree
 // (hist_tree_builder_single.cu:365-389 and :847-902).  One warp per node of the level.
-__global__ void __launch_bounds__(32)
+static __global__ void __launch_bounds__(32)
 k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
              const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam) {
     const int n = blockIdx.x, lane = threadIdx.x;
@@ -557,7 +565,7 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
 // ------------------------------------------------------------------ instance partition
 // (replaces update_ins2node_id + the per-level radix sort, hist_tree_builder_single.cu:908-1020, :397-415)
 // Tile table: every node of the level that holds records gets ceil(count / 1024) tiles.
-__global__ void k_part_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+static __global__ void k_part_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
                             int *__restrict__ tile_node, int *__restrict__ tile_start, int *__restrict__ node_tile0,
                             TreeCtl *__restrict__ ctl) {
     __shared__ int total;
@@ -584,7 +592,7 @@ __global__ void k_part_plan(int level, const int *__restrict__ seg_begin, const 
 
 // Direction of every record of a splittable node: left unless (missing and default right) or
 // bin >= split_bid (hist_tree_builder_single.cu:1003-1012).  One bit per record, one count per tile.
-__global__ void __launch_bounds__(PART_TILE)
+static __global__ void __launch_bounds__(PART_TILE)
 k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
              const int *__restrict__ tile_node, const int *__restrict__ tile_start, const TreeCtl *__restrict__ ctl,
              const int *__restrict__ rec_idx, const unsigned char *__restrict__ binsT, size_t Npad,
@@ -618,7 +626,7 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
 
 // Prefix of the left counts over the tiles of every node, child segment table of the next level,
 // done-list offsets of finished nodes.  One block of 1024 threads.
-__global__ void __launch_bounds__(1024)
+static __global__ void __launch_bounds__(1024)
 k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
             const int *__restrict__ seg_cnt, const int *__restrict__ node_tile0, int *__restrict__ tile_left,
             int *__restrict__ next_begin, int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base,
@@ -683,7 +691,7 @@ k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int 
 
 // Stable scatter of the records into the child segments (or, for nodes that stopped splitting and
 // at the last level, into the done list with the id of the node the row ended in).
-__global__ void __launch_bounds__(PART_TILE)
+static __global__ void __launch_bounds__(PART_TILE)
 k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
                const int *__restrict__ seg_cnt, const int *__restrict__ tile_node, const int *__restrict__ tile_start,
                const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
@@ -740,7 +748,7 @@ k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const i
 // ------------------------------------------------------------------ end of tree
 // Tree::prune_self / try_prune_leaf / reorder_nid (src/thundergbm/tree.cu:85-128); the node table is
 // staged in shared memory and walked by one thread in the reference's order.
-__global__ void k_prune(TreeNode *__restrict__ nodes, int n_nodes, float gamma) {
+static __global__ void k_prune(TreeNode *__restrict__ nodes, int n_nodes, float gamma) {
     extern __shared__ __align__(16) unsigned char sm[];
     TreeNode *sn = reinterpret_cast<TreeNode *>(sm);
     int *cnt = reinterpret_cast<int *>(sm + sizeof(TreeNode) * (size_t)n_nodes);
@@ -771,7 +779,7 @@ __global__ void k_prune(TreeNode *__restrict__ nodes, int n_nodes, float gamma) 
 
 // TreeBuilder::predict_in_training (src/thundergbm/builder/tree_builder.cu:62-74); nvcc contracts the
 // reference's `y += lr * w` into one fused multiply-add, written out here
-__global__ void k_predict_update(const TreeNode *__restrict__ nodes, const int *__restrict__ done_idx,
+static __global__ void k_predict_update(const TreeNode *__restrict__ nodes, const int *__restrict__ done_idx,
                                  const int *__restrict__ done_nid, int n, float lr, float *__restrict__ yp,
                                  int *__restrict__ nid_out) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -786,7 +794,7 @@ __global__ void k_predict_update(const TreeNode *__restrict__ nodes, const int *
 // ------------------------------------------------------------------ metrics
 // per-block partial sums in a fixed order: RMSE (pointwise_metric.cu:8-22), binary error and
 // multi-class accuracy (multiclass_metric.cu:9-46)
-__global__ void k_metric_partial(int objective, const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
+static __global__ void k_metric_partial(int objective, const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
                                  double *__restrict__ partial) {
     __shared__ double ws[32];
     double s = 0;
@@ -814,14 +822,14 @@ __global__ void k_metric_partial(int objective, const float *__restrict__ y, con
         partial[blockIdx.x] = t;
     }
 }
-__global__ void k_metric_sum(const double *__restrict__ partial, int nb, double *__restrict__ out) {
+static __global__ void k_metric_sum(const double *__restrict__ partial, int nb, double *__restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         double t = 0;
         for (int i = 0; i < nb; ++i) t += partial[i];
         *out = t;
     }
 }
-__global__ void k_metric_final(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ out) {
+static __global__ void k_metric_final(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         const double s = *sum;
         if (objective == REG_LINEAR || objective == REG_LOGISTIC) *out = sqrtf((float)s / (float)n_total);
@@ -830,7 +838,7 @@ __global__ void k_metric_final(int objective, const double *__restrict__ sum, lo
     }
 }
 
-__global__ void k_fill(float *p, size_t n, float v) {
+static __global__ void k_fill(float *p, size_t n, float v) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
 }
 

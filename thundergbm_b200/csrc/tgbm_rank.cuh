@@ -16,14 +16,6 @@ namespace tgbm {
 
 constexpr int RANK_MAX_GROUP = 4096;
 
-__host__ __device__ inline uint32_t mix32(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    uint64_t z = ((uint64_t)a << 32 | b) * 0x9E3779B97F4A7C15ull + ((uint64_t)c << 32 | d);
-    z ^= z >> 30; z *= 0xBF58476D1CE4E5B9ull;
-    z ^= z >> 27; z *= 0x94D049BB133111EBull;
-    z ^= z >> 31;
-    return (uint32_t)(z >> 32);
-}
-
 __device__ inline uint32_t desc_key(float v) {  // larger float -> smaller key
     uint32_t u = __float_as_uint(v);
     if (u == 0x80000000u) u = 0;  // -0.0f == 0.0f
@@ -59,7 +51,7 @@ __device__ inline float disc_gain(int label, int rank, const float *__restrict__
 }
 
 // LambdaRank::get_gradient for one query group per CTA
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 k_lambdarank(const int *__restrict__ gptr, const float *__restrict__ y, const float *__restrict__ yp, const float *__restrict__ idcg,
              const float *__restrict__ log2tab, int ndcg, uint32_t seed, uint32_t round, uint32_t group_offset,
              float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
@@ -137,7 +129,7 @@ k_lambdarank(const int *__restrict__ gptr, const float *__restrict__ y, const fl
 
 // NDCG / MAP of one query group per CTA (src/thundergbm/metric/rank_metric.cpp:42-100):
 // documents ordered by score descending (ties by row), sequential sums in rank order
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 k_rank_metric(const int *__restrict__ gptr, const float *__restrict__ y, const float *__restrict__ yp, const float *__restrict__ idcg,
               const float *__restrict__ log2tab, int ndcg, float *__restrict__ group_score) {
     extern __shared__ __align__(16) unsigned char sm[];
@@ -166,14 +158,14 @@ k_rank_metric(const int *__restrict__ gptr, const float *__restrict__ y, const f
     }
 }
 
-__global__ void k_rank_metric_sum(const float *__restrict__ group_score, int n_group, double *__restrict__ out) {
+static __global__ void k_rank_metric_sum(const float *__restrict__ group_score, int n_group, double *__restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
         double s = 0;
         for (int i = 0; i < n_group; ++i) s += (double)group_score[i];
         *out = s;
     }
 }
-__global__ void k_rank_metric_final(const double *__restrict__ sum, long long n_group_total, float *__restrict__ out) {
+static __global__ void k_rank_metric_final(const double *__restrict__ sum, long long n_group_total, float *__restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) *out = (float)(*sum / (double)n_group_total);
 }
 

@@ -61,22 +61,25 @@ def dense_regression(n=10_000, f=32, seed=0) -> CsrData:
     return dense_to_csr(x, y.astype(np.float32))
 
 
-def higgs_like(n=10_500_000, seed=1, chunk=1_000_000) -> CsrData:
+def higgs_like(n=10_500_000, seed=1, rows=None, chunk=262_144) -> CsrData:
     """Config 2: 28 dense float32 features; 0-20 N(0,1) or |N(0,1)|, 21-27 LogNormal(0,0.5);
     y ~ Bernoulli(sigmoid(s)), s = sparse linear term over 8 features + 4 pairwise products,
-    shifted to give ~53 % positives."""
+    shifted to give ~53 % positives.
+
+    Rows are generated in fixed chunks with one random stream per chunk, so `rows=(lo, hi)` yields
+    exactly the rows [lo, hi) of the full data set without generating the rest (row sharding)."""
     f = 28
-    rng = np.random.default_rng(seed)
-    absf = rng.random(21) < 0.5
-    lin_idx = rng.choice(f, 8, replace=False)
-    lin_w = rng.standard_normal(8).astype(np.float32)
-    pairs = rng.choice(f, (4, 2))
-    pair_w = rng.standard_normal(4).astype(np.float32) * 0.5
-    x = np.empty((n, f), np.float32)
-    y = np.empty(n, np.float32)
-    for lo in range(0, n, chunk):
-        hi = min(n, lo + chunk)
-        m = hi - lo
+    lo, hi = (0, n) if rows is None else rows
+    head = np.random.default_rng([seed, 0xC0FFEE])
+    absf = head.random(21) < 0.5
+    lin_idx = head.choice(f, 8, replace=False)
+    lin_w = head.standard_normal(8).astype(np.float32)
+    pairs = head.choice(f, (4, 2))
+    pair_w = head.standard_normal(4).astype(np.float32) * 0.5
+
+    def gen(c):  # chunk c -> (x, raw score, uniform draws)
+        rng = np.random.default_rng([seed, c])
+        m = min(chunk, n - c * chunk)
         a = rng.standard_normal((m, 21), dtype=np.float32)
         a[:, absf] = np.abs(a[:, absf])
         b = np.exp(0.5 * rng.standard_normal((m, 7), dtype=np.float32))
@@ -84,17 +87,24 @@ def higgs_like(n=10_500_000, seed=1, chunk=1_000_000) -> CsrData:
         s = xb[:, lin_idx] @ lin_w
         for (i, j), w in zip(pairs, pair_w):
             s += w * xb[:, i] * xb[:, j]
-        x[lo:hi] = xb
-        y[lo:hi] = s
-    shift = np.quantile(y[: min(n, 200_000)], 0.47)
-    p = 1.0 / (1.0 + np.exp(-(y - shift)))
-    y = (rng.random(n, dtype=np.float32) < p).astype(np.float32)
+        return xb, s, rng.random(m, dtype=np.float32)
+
+    shift = np.quantile(gen(0)[1], 0.47)  # from chunk 0, the same on every shard
+    m = hi - lo
+    x = np.empty((m, f), np.float32)
+    y = np.empty(m, np.float32)
+    for c in range(lo // chunk, (hi + chunk - 1) // chunk):
+        xb, s, u = gen(c)
+        a, b = max(lo, c * chunk), min(hi, c * chunk + xb.shape[0])
+        sl = slice(a - c * chunk, b - c * chunk)
+        x[a - lo:b - lo] = xb[sl]
+        y[a - lo:b - lo] = u[sl] < 1.0 / (1.0 + np.exp(-(s[sl] - shift)))
     # continuous features contain no exact zeros, so the CSR is fully dense
-    row_ptr = (np.arange(n + 1, dtype=np.int64) * f)
+    row_ptr = (np.arange(m + 1, dtype=np.int64) * f)
     assert row_ptr[-1] < 2 ** 31
     x[x == 0] = np.float32(1e-30)
-    col = np.tile(np.arange(f, dtype=np.int32), n)
-    return CsrData(n, f, row_ptr.astype(np.int32), col, x.reshape(-1), y)
+    col = np.tile(np.arange(f, dtype=np.int32), m)
+    return CsrData(m, f, row_ptr.astype(np.int32), col, x.reshape(-1), y)
 
 
 def covtype_like(n=581_012, seed=2) -> CsrData:
