@@ -86,9 +86,9 @@ def test_depth_extremes(gpu, orc, depth):
 
 
 def test_accumulator_window_flush(gpu, orc):
-    """More rows per CTA than one int32 accumulation window holds (quant_bits 21 -> 512-row windows)."""
+    """More rows per CTA than one int32 accumulation window holds (quant_bits 20 -> a window of one 1024-row tile)."""
     d = synth.higgs_like(300_000, seed=5)
-    p = dict(objective='binary:logistic', depth=3, n_trees=2, max_num_bin=255, learning_rate=0.1, quant_bits=21)
+    p = dict(objective='binary:logistic', depth=3, n_trees=2, max_num_bin=255, learning_rate=0.1, quant_bits=20)
     o, b = _pair(orc, d, **p)
     assert b.trees().tobytes() == o.trees.tobytes()
     b.close()

@@ -51,11 +51,12 @@ struct BoosterImpl {
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     DevBuf<SplitRec> recs;
-    DevBuf<int> tile_node, tile_start, node_tile0, tile_left, node_done_base;
+    DevBuf<int> node_tile0, tile_left, node_done_base;
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
     DevBuf<double> metric_partial, metric_sum;
     int max_tiles = 0;
+    int hist_smem = 0;
     RankState rank;
 
     struct TimedEvent { cudaEvent_t a, b; int kind; };
@@ -200,7 +201,7 @@ void Booster::init(const DataSet &ds) {
     TGBM_CHECK(m.objective != OBJ_UNKNOWN, "undefined objective " + p.objective);
     TGBM_CHECK(p.depth >= 1 && p.depth <= 14, "depth must be in [1, 14]");
     TGBM_CHECK(p.max_num_bin >= 1 && p.max_num_bin <= 255, "max_num_bin must be in [1, 255] (bin ids are bytes, 255 marks a missing value)");
-    TGBM_CHECK(p.quant_bits >= 8 && p.quant_bits <= 21, "quant_bits must be in [8, 21]");
+    TGBM_CHECK(p.quant_bits >= 8 && p.quant_bits <= 20, "quant_bits must be in [8, 20]");
     TGBM_CHECK(!p.bagging, "bagging is not part of the histogram path implemented here");
     TGBM_CHECK(p.column_sampling_rate >= 1.0f, "column sampling is not part of the histogram path implemented here");
     int dev = 0;
@@ -281,18 +282,19 @@ void Booster::init(const DataSet &ds) {
     m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
     m.recs.alloc(((size_t)1 << (depth - 1)) * m.F);
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
-    m.tile_node.alloc(m.max_tiles); m.tile_start.alloc(m.max_tiles); m.tile_left.alloc(m.max_tiles);
+    m.tile_left.alloc(m.max_tiles);
     m.node_tile0.alloc(((size_t)1 << depth) + 1); m.node_done_base.alloc((size_t)1 << depth);
-    m.bits.alloc((size_t)m.max_tiles * 32);
+    m.bits.alloc((size_t)m.max_tiles * (PART_TILE / 32));
     m.ctl.alloc(1);
     m.ctl.zero(m.stream);
     m.metric_partial.alloc(1024); m.metric_sum.alloc(1);
     m.window_rows = (1 << (31 - p.quant_bits)) - HIST_THREADS;
     TGBM_CHECK(m.window_rows >= HIST_THREADS, "quant_bits too large for the int32 accumulation window");
-    TGBM_CUDA(cudaFuncSetAttribute(k_hist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 256 * 32 * 4));
-    TGBM_CUDA(cudaFuncSetAttribute(k_hist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 256 * 32 * 4));
-    if (sizeof(TreeNode) * (size_t)m.n_nodes + 4 * (size_t)m.n_nodes > 48 * 1024)
-        TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(52 * (size_t)m.n_nodes)));
+    m.hist_smem = 2 * 256 * 32 * 4 + 2 * 256 * 32 * 8;  // int32 accumulators + int64 totals, both [2][256 bins][32 features]
+    TGBM_CUDA(cudaFuncSetAttribute(k_hist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
+    TGBM_CUDA(cudaFuncSetAttribute(k_hist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
+    if (sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
+        TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(TreeNode) * (size_t)m.n_nodes)));
     if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream);
     m.init_base_score();
     TGBM_CUDA(cudaStreamSynchronize(m.stream));
@@ -305,13 +307,14 @@ void BoosterImpl::gradient(int round) {
     maxbits.zero(stream);
     root_sum.zero(stream);
     if (N) {
+        const int gb = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
         switch (objective) {
         case REG_LINEAR:
-            k_grad_pointwise<<<ceil_div(N, tb), tb, 0, stream>>>(y.p, ypred.p, N, 0, gh.p, maxbits.p); break;
+            k_grad_pointwise<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, 0, gh.p, maxbits.p); break;
         case REG_LOGISTIC: case BINARY_LOGISTIC:
-            k_grad_pointwise<<<ceil_div(N, tb), tb, 0, stream>>>(y.p, ypred.p, N, 1, gh.p, maxbits.p); break;
+            k_grad_pointwise<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, 1, gh.p, maxbits.p); break;
         case MULTI_SOFTMAX: case MULTI_SOFTPROB:
-            k_grad_softmax<<<ceil_div(N, tb), tb, 0, stream>>>(y.p, ypred.p, N, K, gh.p, maxbits.p); break;
+            k_grad_softmax<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, K, gh.p, maxbits.p); break;
         case RANK_PAIRWISE: case RANK_NDCG:
             rank.gradient(round, p.rank_seed, ypred.p, gh.p, maxbits.p, stream); break;
         }
@@ -355,8 +358,8 @@ void BoosterImpl::build_tree(int round, int k) {
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
     ++launches;
-    const int hist_ctas = num_sms * 2;
-    const size_t hist_smem = 2 * 256 * 32 * sizeof(int);
+    const int hist_ctas = num_sms;
+    const int part_ctas = std::max(1, std::min(max_tiles, num_sms * 2));
     for (int level = 0; level < depth; ++level) {
         const int cur = level & 1, nxt = cur ^ 1;
         const int nl = 1 << level, pairs = std::max(1, nl / 2);
@@ -364,7 +367,7 @@ void BoosterImpl::build_tree(int round, int k) {
         const int2 *gh_in = level == 0 ? gq : rec_gh[cur].p;
         // -- histogram of the root / of the smaller child of every pair
         if (level > 0 && comm && comm->active()) comm->allreduce(gcnt.p, nl, Comm::I32, Comm::SUM, stream);
-        k_hist_plan<<<1, 32, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, gcnt.p, built_right.p, hist_work.p,
+        k_hist_plan<<<1, 1024, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, gcnt.p, built_right.p, hist_work.p,
                                           hist_tile_base.p, ctl.p);
         long long *built = level == 0 ? hist_full.p : hist_built.p;
         TGBM_CUDA(cudaMemsetAsync(built, 0, sizeof(long long) * 2 * (size_t)B * pairs, stream));
@@ -390,18 +393,18 @@ void BoosterImpl::build_tree(int round, int k) {
         // -- move the rows
         TimedEvent pv{};
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
-        k_part_plan<<<1, 256, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, tile_node.p, tile_start.p, node_tile0.p, ctl.p);
-        k_part_count<<<max_tiles, PART_TILE, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, tile_node.p, tile_start.p, ctl.p,
-                                                          idx_in, binsT.p, Npad, bits.p, tile_left.p);
-        k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0.p, tile_left.p,
+        k_part_plan<<<1, 1024, 0, stream>>>(level, seg_cnt[cur].p, node_tile0.p, ctl.p);
+        k_part_count<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0.p, ctl.p,
+                                                             idx_in, binsT.p, Npad, bits.p, tile_left.p);
+        k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_cnt[cur].p, node_tile0.p, tile_left.p,
                                             seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, node_done_base.p, ctl.p);
-        k_part_scatter<<<max_tiles, PART_TILE, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, tile_node.p, tile_start.p,
-                                                            node_tile0.p, ctl.p, idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p,
-                                                            node_done_base.p, rec_idx[nxt].p, rec_gh[nxt].p, done_idx.p, done_nid.p);
+        k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0.p, ctl.p,
+                                                               idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p, node_done_base.p,
+                                                               rec_idx[nxt].p, rec_gh[nxt].p, done_idx.p, done_nid.p);
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
         launches += 8;
     }
-    k_prune<<<1, 256, 52 * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, p.gamma);
+    k_prune<<<1, 1024, sizeof(TreeNode) * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, depth, p.gamma);
     if (N) k_predict_update<<<ceil_div(N, 256), 256, 0, stream>>>(nodes.p, done_idx.p, done_nid.p, N, p.learning_rate, ypred.p + (size_t)k * N,
                                                                   p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr);
     launches += 2;

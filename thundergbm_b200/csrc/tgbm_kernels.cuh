@@ -18,8 +18,10 @@
 
 namespace tgbm {
 
-constexpr int HIST_THREADS = 512;
-constexpr int PART_TILE = 1024;
+constexpr int HIST_THREADS = 1024;  // one CTA per SM: 64 KB of int32 accumulators + up to 128 KB of int64 totals
+constexpr int PART_THREADS = 1024;
+constexpr int PART_RPT = 4;         // records per thread
+constexpr int PART_TILE = PART_THREADS * PART_RPT;
 constexpr int MISSING_BIN = 255;
 
 struct HistWork {  // one histogram to build at a level
@@ -117,26 +119,37 @@ static __global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *_
 }
 
 // ------------------------------------------------------------------ objectives
+// block-wide maximum of |g| and h, then one atomic pair per block (every thread of the block must call it)
 __device__ inline void track_max(float ag, float h, unsigned *maxbits) {
     // non-negative floats order like their bit patterns
+    __shared__ unsigned smax[2][32];
     unsigned a = __float_as_uint(ag), b = __float_as_uint(h);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
         b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
     }
-    if ((threadIdx.x & 31) == 0) {
-        atomicMax(maxbits, a);
-        atomicMax(maxbits + 1, b);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) { smax[0][warp] = a; smax[1][warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+        a = lane < nw ? smax[0][lane] : 0u;
+        b = lane < nw ? smax[1][lane] : 0u;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            a = max(a, __shfl_xor_sync(0xffffffffu, a, o));
+            b = max(b, __shfl_xor_sync(0xffffffffu, b, o));
+        }
+        if (lane == 0) { atomicMax(maxbits, a); atomicMax(maxbits + 1, b); }
     }
 }
 
 // SquareLoss / LogisticLoss gradients (include/thundergbm/objective/regression_obj.h:129-154)
 static __global__ void k_grad_pointwise(const float *__restrict__ y, const float *__restrict__ yp, int n, int logistic,
                                  float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    float g = 0.f, h = 0.f;
-    if (i < n) {
+    float mg = 0.f, mh = 0.f;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        float g, h;
         if (logistic) {
             const float p = __fdiv_rn(1.0f, __fadd_rn(1.0f, portable_expf(-yp[i])));
             g = __fsub_rn(p, y[i]);
@@ -146,16 +159,16 @@ static __global__ void k_grad_pointwise(const float *__restrict__ y, const float
             h = 1.0f;
         }
         gh[i] = make_float2(g, h);
+        mg = fmaxf(mg, fabsf(g)); mh = fmaxf(mh, h);
     }
-    track_max(fabsf(g), h, maxbits);
+    track_max(mg, mh, maxbits);
 }
 
 // Softmax::get_gradient (src/thundergbm/objective/multiclass_obj.cu:7-35), class-major gh[k*N+i]
 static __global__ void k_grad_softmax(const float *__restrict__ y, const float *__restrict__ yp, int n, int K,
                                float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
     float mg = 0.f, mh = 0.f;
-    if (i < n) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
         float mx = yp[i];
         for (int k = 1; k < K; ++k) mx = fmaxf(mx, yp[(size_t)k * n + i]);
         float sum = 0.f;
@@ -233,167 +246,236 @@ static __global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, co
 }
 
 // ------------------------------------------------------------------ histogram build
-// Which sibling to build (the one with fewer rows over all ranks, ties -> left:
-// hist_tree_builder_single.cu:466) and the work list of the level.  One block.
-static __global__ void k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
-                            const int *__restrict__ gcnt, int *__restrict__ built_right, HistWork *__restrict__ work,
-                            int *__restrict__ tile_base, TreeCtl *__restrict__ ctl) {
-    if (threadIdx.x != 0) return;
-    int nw = 0, tiles = 0;
-    unsigned long long rows = 0;
-    if (level == 0) {
-        work[0] = HistWork{0, seg_cnt[0], 0, 0};
-        tile_base[0] = 0;
-        tiles = (seg_cnt[0] + HIST_THREADS - 1) / HIST_THREADS;
-        tile_base[1] = tiles;
-        nw = 1;
-        built_right[0] = 0;
-        ctl->stat_rows_root += seg_cnt[0];
-        ctl->stat_hists += 1;
-    } else {
-        const int pairs = 1 << (level - 1);
-        for (int j = 0; j < pairs; ++j) {
-            const int gl = gcnt[2 * j], gr = gcnt[2 * j + 1];
-            if (max(gl, gr) == 0) { built_right[j] = -1; continue; }
-            const int right = gl > gr;
-            built_right[j] = right;
-            const int c = 2 * j + right;
-            work[nw] = HistWork{seg_begin[c], seg_cnt[c], j, 0};
-            tile_base[nw] = tiles;
-            tiles += (seg_cnt[c] + HIST_THREADS - 1) / HIST_THREADS;
-            rows += seg_cnt[c];
-            ++nw;
+// Exclusive prefix sums over n values inside one block of 1024 threads: out(i, prefix before i); returns the total.
+// `scratch` holds 33 ints of shared memory.  Every thread of the block must call it.
+template <typename In, typename Out>
+__device__ inline int block_scan_excl(int n, In in, Out out, int *scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int carry = 0;
+    for (int base = 0; base < n; base += 1024) {
+        const int i = base + threadIdx.x;
+        const int x = i < n ? in(i) : 0;
+        int v = x;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+        __syncthreads();
+        if (lane == 31) scratch[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            int t = scratch[lane];
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, t, o); if (lane >= o) t += u; }
+            scratch[lane] = t;
         }
+        __syncthreads();
+        const int incl = v + (warp ? scratch[warp - 1] : 0) + carry;
+        if (i < n) out(i, incl - x);
+        carry += scratch[31];
+    }
+    __syncthreads();
+    return carry;
+}
+
+// Which sibling to build (the one with fewer rows over all ranks, ties -> left:
+// hist_tree_builder_single.cu:466) and the work list of the level.  One block of 1024 threads.
+static __global__ void __launch_bounds__(1024)
+k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+            const int *__restrict__ gcnt, int *__restrict__ built_right, HistWork *__restrict__ work,
+            int *__restrict__ tile_base, TreeCtl *__restrict__ ctl) {
+    __shared__ int scratch[33];
+    __shared__ unsigned long long rows;
+    if (level == 0) {
+        if (threadIdx.x == 0) {
+            work[0] = HistWork{0, seg_cnt[0], 0, 0};
+            tile_base[0] = 0;
+            tile_base[1] = (seg_cnt[0] + HIST_THREADS - 1) / HIST_THREADS;
+            built_right[0] = 0;
+            ctl->stat_rows_root += seg_cnt[0];
+            ctl->stat_hists += 1;
+            ctl->n_hist_work = 1;
+            ctl->n_hist_tiles = tile_base[1];
+        }
+        return;
+    }
+    const int pairs = 1 << (level - 1);
+    if (threadIdx.x == 0) rows = 0;
+    __syncthreads();
+    auto right_of = [&](int j) {  // -1: nothing to do, else which child is built
+        const int gl = gcnt[2 * j], gr = gcnt[2 * j + 1];
+        return max(gl, gr) == 0 ? -1 : (gl > gr ? 1 : 0);
+    };
+    // compacted position of every active pair in the work list
+    const int nw = block_scan_excl(pairs, [&](int j) { return right_of(j) >= 0 ? 1 : 0; },
+                                   [&](int j, int pos) {
+                                       const int r = right_of(j);
+                                       built_right[j] = r;
+                                       if (r >= 0) {
+                                           const int c = 2 * j + r;
+                                           work[pos] = HistWork{seg_begin[c], seg_cnt[c], j, 0};
+                                           atomicAdd(&rows, (unsigned long long)seg_cnt[c]);
+                                       }
+                                   }, scratch);
+    const int tiles = block_scan_excl(nw, [&](int w) { return (work[w].count + HIST_THREADS - 1) / HIST_THREADS; },
+                                      [&](int w, int base) { tile_base[w] = base; }, scratch);
+    if (threadIdx.x == 0) {
         tile_base[nw] = tiles;
         ctl->stat_rows_gather += rows;
         ctl->stat_hists += nw;
+        ctl->n_hist_work = nw;
+        ctl->n_hist_tiles = tiles;
     }
-    ctl->n_hist_work = nw;
-    ctl->n_hist_tiles = tiles;
 }
 
-// Rotate the 32 bin bytes of a row left by L bytes (L = lane id): afterwards byte j of the
-// register array is the bin of feature (j + L) mod 32, so at step j the 32 lanes of a warp
-// address 32 different features.
-__device__ __forceinline__ void rotate_row(uint32_t (&w)[8], int L) {
-    const int a = L >> 2, b = L & 3;
+// Permute the 32 bin bytes of a row so that byte j of the register array is the bin of feature (j XOR lane):
+// at step j the 32 lanes of a warp then address 32 different features.  Lane bits 0-1 permute the bytes inside
+// every word (one PRMT each), bits 2-4 exchange whole words.
+__device__ __forceinline__ void xor_permute_row(uint32_t (&w)[8], int lane) {
+    const uint32_t sel = (lane & 2) ? ((lane & 1) ? 0x0123u : 0x1032u) : ((lane & 1) ? 0x2301u : 0x3210u);
 #pragma unroll
-    for (int s = 4; s >= 1; s >>= 1) {
+    for (int i = 0; i < 8; ++i) w[i] = __byte_perm(w[i], 0u, sel);
+    const int hi = lane >> 2;
+#pragma unroll
+    for (int s = 1; s <= 4; s <<= 1) {
         uint32_t t[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = (a & s) ? w[(i + s) & 7] : w[i];
+        for (int i = 0; i < 8; ++i) t[i] = (hi & s) ? w[i ^ s] : w[i];
 #pragma unroll
         for (int i = 0; i < 8; ++i) w[i] = t[i];
     }
-    uint32_t t[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) t[i] = __funnelshift_r(w[i], w[(i + 1) & 7], 8 * b);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = t[i];
 }
 
 // Histogram build of one level (root: hist_tree_builder_single.cu:203-216, deeper levels: :485-505).
-// Persistent CTAs; grid = (ctas, feature groups of 32).  Each CTA owns a contiguous range of
-// 512-row tiles of the level's work list.  One lane = one row; the shared-memory histogram is laid
-// out [bin][32 features] so that the bank is the feature index: with the rotated feature order
-// every shared atomic of a warp hits 32 different banks.  Accumulators are int32; they are flushed
-// to the int64 histogram in global memory when the node changes or before they could overflow
-// (`window_rows` rows of at most 2^quant_bits each).
+// Persistent CTAs, one per SM; grid = (ctas, feature groups of 32).  Each CTA owns a contiguous range of
+// 1024-row tiles of the level's work list.  One lane = one row; the shared-memory accumulators are laid out
+// [bin][32 features] so that the bank is the feature index: lane l handles feature j^l at step j, so every
+// shared atomic of a warp hits 32 different banks.  Accumulators are int32.  Before they could overflow
+// (`window_rows` rows of at most 2^quant_bits each) they are drained into int64 totals, also in shared
+// memory; the totals go to the node's int64 histogram in global memory when the CTA moves on to another
+// node and at the end.
 template <bool GATHER>
-static __global__ void __launch_bounds__(HIST_THREADS, 2)
+static __global__ void __launch_bounds__(HIST_THREADS, 1)
 k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__restrict__ rec_idx,
        const int2 *__restrict__ rec_gh, const HistWork *__restrict__ work, const int *__restrict__ tile_base,
        const TreeCtl *__restrict__ ctl, const int *__restrict__ cut_ptr, const int *__restrict__ cut_fid,
        long long *__restrict__ slab, int B, int window_rows) {
-    extern __shared__ __align__(16) int sh_hist[];  // g: [256][32], h: [256][32]
-    int *hg = sh_hist, *hh = sh_hist + 256 * 32;
-    for (int i = threadIdx.x; i < 2 * 256 * 32; i += HIST_THREADS) sh_hist[i] = 0;
-    __syncthreads();
+    extern __shared__ __align__(16) int sh_hist[];  // int32 g,h: [2][256][32]; int64 totals g,h: [2][256][32]
+    int *acc = sh_hist;
+    int *hg = acc, *hh = acc + 256 * 32;
+    long long *tot = reinterpret_cast<long long *>(sh_hist + 2 * 256 * 32);
 
     const int group = blockIdx.y;
     const int f0 = group * 32;
     const int nf = min(32, F - f0);
     const int bin_lo = cut_ptr[f0], bin_hi = cut_ptr[f0 + nf];
     const int lane = threadIdx.x & 31;
+    const uint32_t lane4 = 4u * lane;
     const int total = ctl->n_hist_tiles, nwork = ctl->n_hist_work;
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int t_begin = min(total, (int)blockIdx.x * per), t_end = min(total, t_begin + per);
     if (t_begin >= t_end) return;
+    for (int i = threadIdx.x; i < 2 * 256 * 32; i += HIST_THREADS) { acc[i] = 0; tot[i] = 0; }
+    __syncthreads();
 
-    auto flush = [&](int slab_idx) {
+    auto drain = [&]() {  // int32 window -> int64 totals, same [bin][feature] layout
         __syncthreads();
+#pragma unroll 4
+        for (int i = threadIdx.x; i < 2 * 256 * 32; i += HIST_THREADS) {
+            const int v = acc[i];
+            if (v) { tot[i] += v; acc[i] = 0; }
+        }
+        __syncthreads();
+    };
+    auto flush = [&](int slab_idx) {  // totals -> the node's histogram (global bin order)
+        drain();
         long long *dst = slab + (size_t)slab_idx * B * 2;
         for (int b = bin_lo + threadIdx.x; b < bin_hi; b += HIST_THREADS) {
             const int f = cut_fid[b];
             const int s = (b - cut_ptr[f]) * 32 + (f - f0);
-            const int vg = hg[s], vh = hh[s];
-            if (vg) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b), (unsigned long long)(long long)vg); hg[s] = 0; }
-            if (vh) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b + 1), (unsigned long long)(long long)vh); hh[s] = 0; }
+            const long long vg = tot[s], vh = tot[256 * 32 + s];
+            if (vg) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b), (unsigned long long)vg); tot[s] = 0; }
+            if (vh) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b + 1), (unsigned long long)vh); tot[256 * 32 + s] = 0; }
         }
         __syncthreads();
     };
 
-    // locate the work item of a tile; w is a cursor that only moves forward
+    // Software pipeline over tiles: while tile t is accumulated, the bin rows of tile t+1 are in flight and the
+    // row index of tile t+2 is being fetched, so that no load waits for another inside an iteration.
+    // locate(): record position of this thread in tile t; w is a cursor over the work list that only moves forward
     auto locate = [&](int t, int &w) -> long long {
+        if (t >= t_end) return -1;
         while (w + 1 < nwork && t >= tile_base[w + 1]) ++w;
         const HistWork it = work[w];
         const long long p = (long long)(t - tile_base[w]) * HIST_THREADS + threadIdx.x;
         return p < it.count ? it.begin + p : -1;
     };
-    int w_cur = 0;
+    int w0 = 0;
     {  // binary search for the first item
         int lo = 0, hi = nwork - 1;
         while (lo < hi) {
             const int mid = (lo + hi + 1) / 2;
             if (tile_base[mid] <= t_begin) lo = mid; else hi = mid - 1;
         }
-        w_cur = lo;
+        w0 = lo;
     }
-    int w_next = w_cur;
+    // stage 2 (tile t+2): position + row id; stage 1 (tile t+1): bin row + gradients; stage 0: being accumulated
+    int w_cur = w0, w1 = w0, w2 = w0;
+    long long p1 = locate(t_begin, w1);
+    int r1 = p1 >= 0 ? (GATHER ? rec_idx[p1] : (int)p1) : 0;
+    w2 = w1;
+    long long p2 = locate(t_begin + 1, w2);
+    int r2 = p2 >= 0 ? (GATHER ? rec_idx[p2] : (int)p2) : 0;
     uint4 na = make_uint4(0, 0, 0, 0), nb = na;
     int2 nv = make_int2(0, 0);
-    bool nok = false;
-    auto load = [&](int t, int &w) {
-        const long long p = locate(t, w);
-        nok = p >= 0;
-        if (nok) {
-            const int r = GATHER ? rec_idx[p] : (int)p;
-            const uint4 *src = reinterpret_cast<const uint4 *>(bins + (size_t)r * Fpad + f0);
-            na = src[0]; nb = src[1];
-            nv = rec_gh[p];
-        }
-    };
-    load(t_begin, w_next);
+    if (p1 >= 0) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(bins + (size_t)r1 * Fpad + f0);
+        na = src[0]; nb = src[1];
+        nv = rec_gh[p1];
+    }
+    bool nok = p1 >= 0;
+    int w_of_next = w1;
     int slab_cur = work[w_cur].slab;
     int since = 0;
     for (int t = t_begin; t < t_end; ++t) {
         const uint4 a = na, b = nb;
         const int2 v = nv;
         const bool ok = nok;
-        const int w_this = w_next;
-        if (t + 1 < t_end) load(t + 1, w_next);
+        const int w_this = w_of_next;
+        // tile t+1: its row id arrived during the previous iteration
+        nok = p2 >= 0;
+        w_of_next = w2;
+        if (nok) {
+            const uint4 *src = reinterpret_cast<const uint4 *>(bins + (size_t)r2 * Fpad + f0);
+            na = src[0]; nb = src[1];
+            nv = rec_gh[p2];
+        }
+        // tile t+2: position and row id
+        p2 = locate(t + 2, w2);
+        r2 = p2 >= 0 ? (GATHER ? rec_idx[p2] : (int)p2) : 0;
         if (w_this != w_cur) {  // the tile belongs to the next node: hand the finished one over
             flush(slab_cur);
             w_cur = w_this;
             slab_cur = work[w_cur].slab;
             since = 0;
         } else if (since + HIST_THREADS > window_rows) {
-            flush(slab_cur);
+            drain();
             since = 0;
         }
         since += HIST_THREADS;
         if (ok) {
             uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            rotate_row(w, lane);
+            xor_permute_row(w, lane);
+            // Step j adds the row to (bin of feature j^lane, feature j^lane).  Byte offset of the accumulator:
+            // bin * 128 | feature * 4 -- the bin field comes straight out of the packed word with one shift and
+            // one mask.  No test for missing values: bin 255 (missing, and the padding columns beyond F) lands in
+            // row 255 of the table, which no feature ever reads back.
+            char *const gbase = reinterpret_cast<char *>(hg);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-                const int f = (j + lane) & 31;
-                const uint32_t bin = (w[j >> 2] >> (8 * (j & 3))) & 255u;
-                if (f < nf && bin != MISSING_BIN) {
-                    const int o = bin * 32 + f;
-                    atomicAdd(hg + o, v.x);
-                    atomicAdd(hh + o, v.y);
-                }
+                const uint32_t word = w[j >> 2];
+                const uint32_t binoff = ((j & 3) == 0 ? (word << 7) : (word >> (8 * (j & 3) - 7))) & 0x7f80u;
+                const uint32_t off = binoff | (lane4 ^ (4u * j));
+                atomicAdd(reinterpret_cast<int *>(gbase + off), v.x);
+                atomicAdd(reinterpret_cast<int *>(gbase + off + 256 * 32 * 4), v.y);
             }
         }
     }
@@ -564,107 +646,99 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
 
 // ------------------------------------------------------------------ instance partition
 // (replaces update_ins2node_id + the per-level radix sort, hist_tree_builder_single.cu:908-1020, :397-415)
-// Tile table: every node of the level that holds records gets ceil(count / 1024) tiles.
-static __global__ void k_part_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
-                            int *__restrict__ tile_node, int *__restrict__ tile_start, int *__restrict__ node_tile0,
-                            TreeCtl *__restrict__ ctl) {
-    __shared__ int total;
+// Every node of the level that holds records gets ceil(count / PART_TILE) tiles of 4096 records;
+// node_tile0[n] is the first tile of node n.  One block.
+static __global__ void __launch_bounds__(1024)
+k_part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl) {
+    __shared__ int scratch[33];
+    __shared__ unsigned long long rows;
     const int nl = 1 << level;
+    if (threadIdx.x == 0) rows = 0;
+    __syncthreads();
+    const int total = block_scan_excl(nl, [&](int n) { return (seg_cnt[n] + PART_TILE - 1) / PART_TILE; },
+                                      [&](int n, int t0) {
+                                          node_tile0[n] = t0;
+                                          if (seg_cnt[n]) atomicAdd(&rows, (unsigned long long)seg_cnt[n]);
+                                      }, scratch);
     if (threadIdx.x == 0) {
-        int t = 0;
-        unsigned long long rows = 0;
-        for (int n = 0; n < nl; ++n) {
-            node_tile0[n] = t;
-            t += (seg_cnt[n] + PART_TILE - 1) / PART_TILE;
-            rows += seg_cnt[n];
-        }
-        node_tile0[nl] = t;
-        total = t;
-        ctl->n_part_tiles = t;
+        node_tile0[nl] = total;
+        ctl->n_part_tiles = total;
         ctl->stat_part_rows += rows;
     }
-    __syncthreads();
-    for (int n = threadIdx.x; n < nl; n += blockDim.x) {
-        const int t0 = node_tile0[n], t1 = node_tile0[n + 1];
-        for (int t = t0; t < t1; ++t) { tile_node[t] = n; tile_start[t] = seg_begin[n] + (t - t0) * PART_TILE; }
+}
+
+// node that owns tile t: the n with node_tile0[n] <= t < node_tile0[n + 1]
+__device__ inline int tile_owner(const int *__restrict__ node_tile0, int nl, int t) {
+    int lo = 0, hi = nl;  // first n with node_tile0[n] > t
+    while (lo < hi) {
+        const int mid = (lo + hi) / 2;
+        if (node_tile0[mid] > t) hi = mid; else lo = mid + 1;
     }
+    return lo - 1;
 }
 
 // Direction of every record of a splittable node: left unless (missing and default right) or
 // bin >= split_bid (hist_tree_builder_single.cu:1003-1012).  One bit per record, one count per tile.
-static __global__ void __launch_bounds__(PART_TILE)
+// Persistent blocks; a thread handles PART_RPT records of a tile so that their loads overlap.
+static __global__ void __launch_bounds__(PART_THREADS)
 k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
-             const int *__restrict__ tile_node, const int *__restrict__ tile_start, const TreeCtl *__restrict__ ctl,
-             const int *__restrict__ rec_idx, const unsigned char *__restrict__ binsT, size_t Npad,
-             unsigned *__restrict__ bits, int *__restrict__ tile_left) {
-    const int t = blockIdx.x;
-    if (t >= ctl->n_part_tiles) return;
+             const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
+             const unsigned char *__restrict__ binsT, size_t Npad, unsigned *__restrict__ bits, int *__restrict__ tile_left) {
     __shared__ int wsum[32];
-    const int n = tile_node[t];
-    const TreeNode nd = nodes[(1 << level) - 1 + n];
-    const bool splittable = nd.is_valid && !nd.is_leaf;
-    if (!splittable) { if (threadIdx.x == 0) tile_left[t] = 0; return; }
-    const int p = tile_start[t] + threadIdx.x;
-    const int end = seg_begin[n] + seg_cnt[n];
-    bool left = false;
-    if (p < end) {
-        const int r = rec_idx ? rec_idx[p] : p;
-        const unsigned char b = binsT[(size_t)nd.split_feature_id * Npad + r];
-        left = (b == MISSING_BIN) ? !nd.default_right : (b < nd.split_bid);
-    }
-    const unsigned m = __ballot_sync(0xffffffffu, left);
+    __shared__ int sh_n;
+    const int nt = ctl->n_part_tiles, nl = 1 << level;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (lane == 0) { bits[(size_t)t * 32 + warp] = m; wsum[warp] = __popc(m); }
-    __syncthreads();
-    if (warp == 0) {
-        int v = wsum[lane];
+    for (int t = blockIdx.x; t < nt; t += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x == 0) sh_n = tile_owner(node_tile0, nl, t);
+        __syncthreads();
+        const int n = sh_n;
+        const TreeNode nd = nodes[nl - 1 + n];
+        if (!(nd.is_valid && !nd.is_leaf)) { if (threadIdx.x == 0) tile_left[t] = 0; continue; }
+        const int p0 = seg_begin[n] + (t - node_tile0[n]) * PART_TILE, end = seg_begin[n] + seg_cnt[n];
+        const unsigned char *colp = binsT + (size_t)nd.split_feature_id * Npad;
+        int r[PART_RPT];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0) tile_left[t] = v;
+        for (int j = 0; j < PART_RPT; ++j) {
+            const int p = p0 + j * PART_THREADS + threadIdx.x;
+            r[j] = p < end ? (rec_idx ? rec_idx[p] : p) : -1;
+        }
+        unsigned char b[PART_RPT];
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) b[j] = r[j] >= 0 ? colp[r[j]] : 0;
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) {
+            const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (b[j] < nd.split_bid));
+            const unsigned m = __ballot_sync(0xffffffffu, left);
+            if (lane == 0) { bits[(size_t)t * (PART_TILE / 32) + j * 32 + warp] = m; cnt += __popc(m); }
+        }
+        if (lane == 0) wsum[warp] = cnt;
+        __syncthreads();
+        if (warp == 0) {
+            int v = wsum[lane];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) tile_left[t] = v;
+        }
     }
 }
 
 // Prefix of the left counts over the tiles of every node, child segment table of the next level,
 // done-list offsets of finished nodes.  One block of 1024 threads.
 static __global__ void __launch_bounds__(1024)
-k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
-            const int *__restrict__ seg_cnt, const int *__restrict__ node_tile0, int *__restrict__ tile_left,
-            int *__restrict__ next_begin, int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base,
-            TreeCtl *__restrict__ ctl) {
-    __shared__ int wsum[32];
-    __shared__ int carry;
+k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_cnt,
+            const int *__restrict__ node_tile0, int *__restrict__ tile_left, int *__restrict__ next_begin,
+            int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base, TreeCtl *__restrict__ ctl) {
+    __shared__ int scratch[33];
     const int nt = ctl->n_part_tiles, nl = 1 << level;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x == 0) carry = 0;
-    __syncthreads();
-    // inclusive scan of tile_left over all tiles (in place)
-    for (int base = 0; base < nt; base += 1024) {
-        const int i = base + threadIdx.x;
-        int v = i < nt ? tile_left[i] : 0;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
-        if (lane == 31) wsum[warp] = v;
-        __syncthreads();
-        if (warp == 0) {
-            int s = wsum[lane];
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, s, o); if (lane >= o) s += u; }
-            wsum[lane] = s;
-        }
-        __syncthreads();
-        v += (warp ? wsum[warp - 1] : 0) + carry;
-        if (i < nt) tile_left[i] = v;
-        __syncthreads();
-        if (threadIdx.x == 1023) carry = v;
-        __syncthreads();
-    }
-    // per node: children counts
     const bool last = level == depth - 1;
+    // tile_left becomes the inclusive prefix over all tiles
+    block_scan_excl(nt, [&](int i) { return tile_left[i]; }, [&](int i, int excl) { tile_left[i] += excl; }, scratch);
+    auto splittable = [&](int n) { const TreeNode &nd = nodes[nl - 1 + n]; return nd.is_valid && !nd.is_leaf; };
     for (int n = threadIdx.x; n < nl; n += 1024) {
-        const TreeNode nd = nodes[nl - 1 + n];
-        const bool splittable = nd.is_valid && !nd.is_leaf;
         int cl = 0, cr = 0;
-        if (splittable && seg_cnt[n] > 0) {
+        if (splittable(n) && seg_cnt[n] > 0) {
             const int t0 = node_tile0[n], t1 = node_tile0[n + 1];
             cl = tile_left[t1 - 1] - (t0 > 0 ? tile_left[t0 - 1] : 0);
             cr = seg_cnt[n] - cl;
@@ -673,107 +747,124 @@ k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int 
         gcnt[2 * n] = cl; gcnt[2 * n + 1] = cr;
     }
     __syncthreads();
+    const int alive = block_scan_excl(2 * nl, [&](int c) { return next_cnt[c]; }, [&](int c, int pos) { next_begin[c] = pos; }, scratch);
+    const int done0 = ctl->done_count;
+    const int fin = block_scan_excl(nl, [&](int n) { return (!splittable(n) || last) ? seg_cnt[n] : 0; },
+                                    [&](int n, int pos) { node_done_base[n] = done0 + pos; }, scratch);
     if (threadIdx.x == 0) {
-        // exclusive scans in node order (at most 2^depth entries)
-        int pos = 0, done = ctl->done_count;
-        for (int n = 0; n < nl; ++n) {
-            const TreeNode nd = nodes[nl - 1 + n];
-            const bool splittable = nd.is_valid && !nd.is_leaf;
-            next_begin[2 * n] = pos; pos += next_cnt[2 * n];
-            next_begin[2 * n + 1] = pos; pos += next_cnt[2 * n + 1];
-            node_done_base[n] = done;
-            if (!splittable || last) done += seg_cnt[n];
-        }
-        ctl->done_count = done;
-        ctl->n_records = last ? 0 : pos;
+        ctl->done_count = done0 + fin;
+        ctl->n_records = last ? 0 : alive;
     }
 }
 
 // Stable scatter of the records into the child segments (or, for nodes that stopped splitting and
 // at the last level, into the done list with the id of the node the row ended in).
-static __global__ void __launch_bounds__(PART_TILE)
+static __global__ void __launch_bounds__(PART_THREADS)
 k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
-               const int *__restrict__ seg_cnt, const int *__restrict__ tile_node, const int *__restrict__ tile_start,
-               const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
-               const int2 *__restrict__ rec_gh, const unsigned *__restrict__ bits, const int *__restrict__ tile_left,
-               const int *__restrict__ next_begin, const int *__restrict__ node_done_base, int *__restrict__ out_idx,
-               int2 *__restrict__ out_gh, int *__restrict__ done_idx, int *__restrict__ done_nid) {
-    const int t = blockIdx.x;
-    if (t >= ctl->n_part_tiles) return;
-    __shared__ int wpre[32];
-    const int n = tile_node[t];
-    const int nid = (1 << level) - 1 + n;
-    const TreeNode nd = nodes[nid];
-    const bool splittable = nd.is_valid && !nd.is_leaf;
+               const int *__restrict__ seg_cnt, const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl,
+               const int *__restrict__ rec_idx, const int2 *__restrict__ rec_gh, const unsigned *__restrict__ bits,
+               const int *__restrict__ tile_left, const int *__restrict__ next_begin, const int *__restrict__ node_done_base,
+               int *__restrict__ out_idx, int2 *__restrict__ out_gh, int *__restrict__ done_idx, int *__restrict__ done_nid) {
+    constexpr int WORDS = PART_TILE / 32;  // 128
+    __shared__ int wpre[WORDS];
+    __shared__ int wtot[4];
+    __shared__ int sh_n;
+    const int nt = ctl->n_part_tiles, nl = 1 << level;
     const bool last = level == depth - 1;
-    const int p0 = tile_start[t];
-    const int p = p0 + threadIdx.x;
-    const int b = seg_begin[n], end = b + seg_cnt[n];
-    const bool ok = p < end;
-    const int r = ok ? (rec_idx ? rec_idx[p] : p) : 0;
-    if (!splittable) {
-        if (ok) { const int d = node_done_base[n] + (p - b); done_idx[d] = r; done_nid[d] = nid; }
-        return;
-    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const unsigned m = bits[(size_t)t * 32 + warp];
-    if (lane == 0) wpre[warp] = __popc(m);
-    __syncthreads();
-    if (warp == 0) {
-        int v = wpre[lane];
+    for (int t = blockIdx.x; t < nt; t += gridDim.x) {
+        __syncthreads();
+        if (threadIdx.x == 0) sh_n = tile_owner(node_tile0, nl, t);
+        __syncthreads();
+        const int n = sh_n;
+        const int nid = nl - 1 + n;
+        const TreeNode nd = nodes[nid];
+        const int b = seg_begin[n], end = b + seg_cnt[n];
+        const int t0 = node_tile0[n];
+        const int p0 = b + (t - t0) * PART_TILE;
+        if (!(nd.is_valid && !nd.is_leaf)) {  // finished node: its rows go to the done list
+            const int base = node_done_base[n];
 #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
-        wpre[lane] = v - __popc(bits[(size_t)t * 32 + lane]);  // exclusive
-    }
-    __syncthreads();
-    if (!ok) return;
-    const bool left = (m >> lane) & 1u;
-    const int t0 = node_tile0[n];
-    const int lefts_before_tile = (t > 0 ? tile_left[t - 1] : 0) - (t0 > 0 ? tile_left[t0 - 1] : 0);
-    const int lefts_before = lefts_before_tile + wpre[warp] + __popc(m & ((1u << lane) - 1u));
-    const int t1 = node_tile0[n + 1];
-    const int n_left = tile_left[t1 - 1] - (t0 > 0 ? tile_left[t0 - 1] : 0);
-    const int rank = left ? lefts_before : (p - b) - lefts_before;
-    if (last) {
-        const int d = node_done_base[n] + (left ? rank : n_left + rank);
-        done_idx[d] = r;
-        done_nid[d] = left ? nd.lch_index : nd.rch_index;
-    } else {
-        const int d = (left ? next_begin[2 * n] : next_begin[2 * n + 1]) + rank;
-        out_idx[d] = r;
-        out_gh[d] = rec_gh[p];
+            for (int j = 0; j < PART_RPT; ++j) {
+                const int p = p0 + j * PART_THREADS + threadIdx.x;
+                if (p < end) { done_idx[base + (p - b)] = rec_idx ? rec_idx[p] : p; done_nid[base + (p - b)] = nid; }
+            }
+            continue;
+        }
+        // loads first, so that they overlap with the rank computation
+        int r[PART_RPT];
+        int2 g[PART_RPT];
+        unsigned m[PART_RPT];
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) {
+            const int p = p0 + j * PART_THREADS + threadIdx.x;
+            r[j] = p < end ? (rec_idx ? rec_idx[p] : p) : -1;
+            if (!last && p < end) g[j] = rec_gh[p];
+            m[j] = bits[(size_t)t * WORDS + j * 32 + warp];
+        }
+        // exclusive prefix of the left counts over the tile's 128 ballot words (record order = word order)
+        if (threadIdx.x < WORDS) {
+            const int c = __popc(bits[(size_t)t * WORDS + threadIdx.x]);
+            int v = c;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+            wpre[threadIdx.x] = v - c;
+            if (lane == 31) wtot[warp] = v;
+        }
+        __syncthreads();
+        const int t1 = node_tile0[n + 1];
+        const int node_l0 = t0 > 0 ? tile_left[t0 - 1] : 0;
+        const int lefts_before_tile = (t > 0 ? tile_left[t - 1] : 0) - node_l0;
+        const int n_left = tile_left[t1 - 1] - node_l0;
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) {
+            if (r[j] < 0) continue;
+            const int p = p0 + j * PART_THREADS + threadIdx.x;
+            const int w = j * 32 + warp;
+            int pre = wpre[w];
+            for (int q = 0; q < (w >> 5); ++q) pre += wtot[q];
+            const bool left = (m[j] >> lane) & 1u;
+            const int lefts_before = lefts_before_tile + pre + __popc(m[j] & ((1u << lane) - 1u));
+            const int rank = left ? lefts_before : (p - b) - lefts_before;
+            if (last) {
+                const int d = node_done_base[n] + (left ? rank : n_left + rank);
+                done_idx[d] = r[j];
+                done_nid[d] = left ? nd.lch_index : nd.rch_index;
+            } else {
+                const int d = (left ? next_begin[2 * n] : next_begin[2 * n + 1]) + rank;
+                out_idx[d] = r[j];
+                out_gh[d] = g[j];
+            }
+        }
     }
 }
 
 // ------------------------------------------------------------------ end of tree
-// Tree::prune_self / try_prune_leaf / reorder_nid (src/thundergbm/tree.cu:85-128); the node table is
-// staged in shared memory and walked by one thread in the reference's order.
-static __global__ void k_prune(TreeNode *__restrict__ nodes, int n_nodes, float gamma) {
+// Tree::prune_self / try_prune_leaf / reorder_nid (src/thundergbm/tree.cu:85-128).  The reference walks the
+// leaves in index order and climbs while a parent has two leaf children and gain < gamma; the fixed point of that
+// walk does not depend on the order, so the levels are processed bottom-up with one thread per node.  One block.
+static __global__ void __launch_bounds__(1024)
+k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma) {
     extern __shared__ __align__(16) unsigned char sm[];
+    __shared__ int scratch[33];
     TreeNode *sn = reinterpret_cast<TreeNode *>(sm);
-    int *cnt = reinterpret_cast<int *>(sm + sizeof(TreeNode) * (size_t)n_nodes);
-    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) { sn[i] = nodes[i]; cnt[i] = 0; }
+    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) sn[i] = nodes[i];
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < n_nodes; ++i) {
-            if (!(sn[i].is_leaf && sn[i].is_valid)) continue;
-            int n = i;
-            while (true) {
-                const int p = sn[n].parent_index;
-                if (p == -1) break;
-                cnt[p]++;
-                if (cnt[p] >= 2 && sn[p].gain < gamma) {
-                    sn[sn[p].lch_index].is_pruned = 1;
-                    sn[sn[p].rch_index].is_pruned = 1;
-                    sn[p].is_leaf = 1;
-                    n = p;
-                } else break;
+    for (int level = depth - 1; level >= 0; --level) {
+        const int nl = 1 << level, off = nl - 1;
+        for (int n = threadIdx.x; n < nl; n += blockDim.x) {
+            TreeNode &p = sn[off + n];
+            if (p.is_valid && !p.is_leaf) {
+                TreeNode &l = sn[p.lch_index], &r = sn[p.rch_index];
+                if (l.is_valid && l.is_leaf && r.is_valid && r.is_leaf && p.gain < gamma) {
+                    l.is_pruned = 1; r.is_pruned = 1; p.is_leaf = 1;
+                }
             }
         }
-        int id = 0;
-        for (int i = 0; i < n_nodes; ++i) if (sn[i].is_valid && !sn[i].is_pruned) sn[i].final_id = id++;
+        __syncthreads();
     }
-    __syncthreads();
+    block_scan_excl(n_nodes, [&](int i) { return (sn[i].is_valid && !sn[i].is_pruned) ? 1 : 0; },
+                    [&](int i, int id) { if (sn[i].is_valid && !sn[i].is_pruned) sn[i].final_id = id; }, scratch);
     for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) nodes[i] = sn[i];
 }
 
@@ -822,12 +913,13 @@ static __global__ void k_metric_partial(int objective, const float *__restrict__
         partial[blockIdx.x] = t;
     }
 }
+// one warp: lane l adds partial[l], partial[l+32], ... in that order, then a fixed shuffle tree
 static __global__ void k_metric_sum(const double *__restrict__ partial, int nb, double *__restrict__ out) {
-    if (threadIdx.x == 0 && blockIdx.x == 0) {
-        double t = 0;
-        for (int i = 0; i < nb; ++i) t += partial[i];
-        *out = t;
-    }
+    double t = 0;
+    for (int i = threadIdx.x; i < nb; i += 32) t += partial[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) *out = t;
 }
 static __global__ void k_metric_final(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
