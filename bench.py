@@ -42,8 +42,9 @@ PARAMS = dict(objective='binary:logistic', depth=8, max_num_bin=255, learning_ra
               min_child_weight=1.0, **{'lambda': 1.0})
 WORKLOAD = 'higgs-shape 10.5M x 28 f32, binary:logistic, depth 8, 255 bins, lr 0.1, lambda 1'
 SAMPLE_ROWS = 1_000_000
-# dram bytes per root-level histogram launch from the committed ncu capture (profiles/), or None
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per k_hist launch, mean of the three launches captured with ncu
+# (root 425.1 MB, level 1 333.0 MB, level 2 431.7 MB; profiles/k_hist_higgs_10p5M_x28.md)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 396.6e6
 
 
 def measured_peaks():

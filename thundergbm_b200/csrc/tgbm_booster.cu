@@ -366,9 +366,8 @@ void BoosterImpl::build_tree(int round, int k) {
         const int *idx_in = level == 0 ? nullptr : rec_idx[cur].p;
         const int2 *gh_in = level == 0 ? gq : rec_gh[cur].p;
         // -- histogram of the root / of the smaller child of every pair
-        if (level > 0 && comm && comm->active()) comm->allreduce(gcnt.p, nl, Comm::I32, Comm::SUM, stream);
-        k_hist_plan<<<1, 1024, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, gcnt.p, built_right.p, hist_work.p,
-                                          hist_tile_base.p, ctl.p);
+        k_hist_plan<<<1, 1024, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, gcnt.p, nodes.p, (comm && comm->active()) ? 1 : 0,
+                                            built_right.p, hist_work.p, hist_tile_base.p, ctl.p);
         long long *built = level == 0 ? hist_full.p : hist_built.p;
         TGBM_CUDA(cudaMemsetAsync(built, 0, sizeof(long long) * 2 * (size_t)B * pairs, stream));
         TimedEvent ev{};

@@ -280,8 +280,9 @@ __device__ inline int block_scan_excl(int n, In in, Out out, int *scratch) {
 // hist_tree_builder_single.cu:466) and the work list of the level.  One block of 1024 threads.
 static __global__ void __launch_bounds__(1024)
 k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
-            const int *__restrict__ gcnt, int *__restrict__ built_right, HistWork *__restrict__ work,
-            int *__restrict__ tile_base, TreeCtl *__restrict__ ctl) {
+            const int *__restrict__ gcnt, const TreeNode *__restrict__ nodes, int by_hessian,
+            int *__restrict__ built_right, HistWork *__restrict__ work, int *__restrict__ tile_base,
+            TreeCtl *__restrict__ ctl) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     if (level == 0) {
@@ -300,7 +301,17 @@ k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict_
     const int pairs = 1 << (level - 1);
     if (threadIdx.x == 0) rows = 0;
     __syncthreads();
-    auto right_of = [&](int j) {  // -1: nothing to do, else which child is built
+    // -1: nothing to do, else which child is built.  One rank: the child with fewer rows, like the reference.
+    // Several ranks: the row counts are rank-local, so every rank takes the child with the smaller hessian sum from
+    // the replicated node table -- the same choice everywhere without a collective.  All histogram sums are exact
+    // integers, so built and subtracted histograms are identical whichever sibling is built.
+    auto right_of = [&](int j) {
+        if (by_hessian) {
+            const int off = (1 << level) - 1;
+            const TreeNode &l = nodes[off + 2 * j], &r = nodes[off + 2 * j + 1];
+            if (!l.is_valid || !r.is_valid) return -1;
+            return l.sum_h > r.sum_h ? 1 : 0;
+        }
         const int gl = gcnt[2 * j], gr = gcnt[2 * j + 1];
         return max(gl, gr) == 0 ? -1 : (gl > gr ? 1 : 0);
     };
