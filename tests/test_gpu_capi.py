@@ -156,3 +156,28 @@ def test_cli_train_and_predict(gpu, tmp_path):
     assert out2.returncode == 0, out2.stderr
     rmse_pred = float(out2.stdout.split('RMSE = ')[1].split()[0])
     assert abs(rmse_pred - rmse_train) < 1e-4
+
+
+def test_metric_score_entry_point(gpu, orc, cases):
+    """tgbm_metric_score on the raw training scores reproduces the per-round metric of training."""
+    from thundergbm_b200 import _lib
+    from thundergbm_b200.booster import Booster
+    lib = _lib.lib()
+    for name in ('c1_dense_reg', 'fixture_bin', 'c3_covtype_small', 'c5_mslr_small'):
+        d, params = cases(name)
+        kw = {k: v for k, v in params.items() if k != 'tree_method'}
+        kw['n_trees'] = 2
+        b = Booster(d, **kw)
+        b.boost(2)
+        raw = np.ascontiguousarray(b.ypred())
+        o = orc.train(d, hist_mode=1, **kw)
+        y = np.ascontiguousarray(d.y, np.float32)
+        if o.labels.size:  # class index, as the library stores it
+            y = np.searchsorted(o.labels, y).astype(np.float32)
+        grp = np.ascontiguousarray(d.group, np.int32)
+        out = C.c_float(0)
+        rc = lib.tgbm_metric_score(params['objective'].encode(), d.n_rows, raw.shape[0], _vp(y), _vp(raw),
+                                   _vp(grp) if grp.size else None, int(grp.size), C.byref(out))
+        assert rc == 0, lib.tgbm_last_error()
+        assert out.value == b.metrics()[-1], name
+        b.close()

@@ -22,6 +22,7 @@ def lib():
 def declared_symbols():
     text = open(os.path.join(ROOT, 'include', 'thundergbm.h')).read()
     text = re.sub(r'/\*.*?\*/', '', text, flags=re.S)
+    text = '\n'.join(l for l in text.splitlines() if not l.lstrip().startswith('#'))
     return sorted(set(re.findall(r'\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{]*\)\s*;', text)))
 
 

@@ -6,7 +6,9 @@
 #include <cub/cub.cuh>
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "tgbm_kernels.cuh"
@@ -85,14 +87,24 @@ static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) 
 // the boosting loop.  With several ranks every rank contributes its distinct keys and all ranks
 // derive identical cut points from the union, so the bins equal the single-GPU ones.
 void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
-    const size_t nnz = (size_t)ds.row_ptr[N];
+    const bool timing = getenv("TGBM_TIMING") != nullptr;  // phase times of the set-up on stderr
+    auto t_prev = std::chrono::steady_clock::now();
+    auto lap = [&](const char *what) {
+        if (!timing) return;
+        cudaStreamSynchronize(stream);
+        const auto t = std::chrono::steady_clock::now();
+        fprintf(stderr, "[tgbm init] %-28s %8.1f ms\n", what, std::chrono::duration<double, std::milli>(t - t_prev).count());
+        t_prev = t;
+    };
+    const size_t nnz = (size_t)ds.rp[N];
     DevBuf<int> d_row_ptr, d_col;
     DevBuf<float> d_val;
     d_row_ptr.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1));
-    TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.row_ptr.data(), sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
-    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.col.data(), sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
-    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.val.data(), sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
 
+    lap("alloc + H2D of the CSR");
     long long nu = 0;
     DevBuf<unsigned long long> ukeys;
     {
@@ -151,6 +163,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         if (nu) TGBM_CUDA(cudaMemcpyAsync(ukeys.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
         TGBM_CUDA(cudaStreamSynchronize(stream));
     }
+    lap("sort + unique of the keys");
     // distinct values per feature -> stride and number of cut points per feature (host, F+1 numbers)
     DevBuf<long long> ustart;
     ustart.alloc(F + 1);
@@ -177,6 +190,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     h_cut_val.resize(B);
     TGBM_CUDA(cudaMemcpyAsync(h_cut_val.data(), cut_val.p, sizeof(float) * B, cudaMemcpyDeviceToHost, stream));
 
+    lap("cut point selection");
     // bin matrix in both layouts
     bins.alloc((size_t)N * Fpad);
     binsT.alloc((size_t)F * Npad);
@@ -185,6 +199,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     if (N) k_bin_dense<<<ceil_div(N, 128), 128, 0, stream>>>(d_row_ptr.p, d_col.p, d_val.p, N, cut_ptr.p, cut_val.p, Fpad, Npad, bins.p, binsT.p);
     TGBM_CUDA(cudaStreamSynchronize(stream));
     TGBM_CUDA(cudaGetLastError());
+    lap("binning");
 }
 
 // ------------------------------------------------------------------------------------------------

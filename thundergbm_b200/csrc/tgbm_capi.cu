@@ -375,6 +375,21 @@ void tgbm_booster_free(TgbmBooster *b) {
     delete b;
 }
 
+int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, const float *label, const float *raw,
+                      const int *group, int num_group, float *out) {
+    return guard([&] {
+        const int o = tgbm::objective_from_name(objective ? objective : "");
+        TGBM_CHECK(o != tgbm::OBJ_UNKNOWN, std::string("undefined objective ") + (objective ? objective : "(null)"));
+        TGBM_CHECK(n_rows > 0 && trees_per_round >= 1 && label && raw && out, "bad arguments");
+        tgbm::DataSet ds;
+        ds.n_rows = n_rows;
+        ds.y.assign(label, label + n_rows);
+        if (group) ds.group.assign(group, group + num_group);
+        std::vector<float> r(raw, raw + (size_t)n_rows * trees_per_round);
+        *out = tgbm::metric_score(o, ds, trees_per_round, r);
+    });
+}
+
 int tgbm_predict_raw(int n_rows, const float *val, const int *row_ptr, const int *col, const void *nodes, int n_rounds,
                      int trees_per_round, int n_nodes, float learning_rate, float base_score, float *out) {
     return guard([&] {

@@ -95,6 +95,10 @@ struct Error : std::runtime_error {
 struct DataSet {
     int n_rows = 0;
     int n_features = 0;
+    // CSR views: borrowed from the caller (load_from_sparse; valid for the duration of the call, like the
+    // reference's copies) or pointing into the owned vectors below (load_from_file)
+    const int *rp = nullptr, *ci = nullptr;
+    const float *vv = nullptr;
     std::vector<int> row_ptr, col;
     std::vector<float> val, y;
     std::vector<int> group;

@@ -9,6 +9,7 @@
 #include <fstream>
 #include <map>
 #include <sstream>
+#include <thread>
 
 namespace tgbm {
 
@@ -33,16 +34,27 @@ void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *
     const long long nnz = rp[n];
     TGBM_CHECK(nnz >= 0, "bad CSR row_ptr");
     n_rows = n;
-    row_ptr.assign(rp, rp + n + 1);
-    col.assign(ci, ci + nnz);
-    val.assign(v, v + nnz);
+    row_ptr.clear(); col.clear(); val.clear();
+    this->rp = rp; this->ci = ci; this->vv = v;  // borrowed: the 2.4 GB of a Higgs-sized CSR are not copied on the host
     y.assign(n, 0.f);
     if (yy) y.assign(yy, yy + n);
     label.clear();
     group.clear();
-    int mx = 0;
-    for (long long i = 0; i < nnz; ++i) mx = std::max(mx, ci[i]);
-    n_features = mx + 1;
+    // n_features = largest column index + 1 (dataset.cpp:54-57), scanned by a few threads
+    {
+        const int nt = (int)std::max<long long>(1, std::min<long long>(16, nnz / (1 << 22)));
+        std::vector<int> part(nt, 0);
+        std::vector<std::thread> th;
+        for (int t = 0; t < nt; ++t)
+            th.emplace_back([&, t] {
+                const long long a = nnz * t / nt, b = nnz * (t + 1) / nt;
+                int m = 0;
+                for (long long i = a; i < b; ++i) m = std::max(m, ci[i]);
+                part[t] = m;
+            });
+        for (auto &x : th) x.join();
+        n_features = *std::max_element(part.begin(), part.end()) + 1;
+    }
     const int o = objective_from_name(param.objective);
     if (yy && need_group_label(o)) {
         group_label();
@@ -125,6 +137,7 @@ void DataSet::load_from_file(const std::string &file, GBMParam &param) {
     }
     n_rows = (int)y.size();
     n_features = maxf;
+    rp = row_ptr.data(); ci = col.data(); vv = val.data();
     log_info("#instances = %d, #features = %d", n_rows, n_features);
     const int o = objective_from_name(param.objective);
     if (need_group_file(o)) load_group_file(file + ".group");

@@ -114,15 +114,15 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
         }
     cudaStream_t st;
     TGBM_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
-    const size_t nnz = (size_t)ds.row_ptr[N];
+    const size_t nnz = (size_t)ds.rp[N];
     DevBuf<int> d_rp, d_col;
     DevBuf<float> d_val, d_out;
     DevBuf<PNode> d_model;
     d_rp.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1)); d_out.alloc((size_t)N * K);
     d_model.alloc(flat.size());
-    TGBM_CUDA(cudaMemcpyAsync(d_rp.p, ds.row_ptr.data(), sizeof(int) * (N + 1), cudaMemcpyHostToDevice, st));
-    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.col.data(), sizeof(int) * nnz, cudaMemcpyHostToDevice, st));
-    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.val.data(), sizeof(float) * nnz, cudaMemcpyHostToDevice, st));
+    TGBM_CUDA(cudaMemcpyAsync(d_rp.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, st));
+    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, st));
+    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, st));
     TGBM_CUDA(cudaMemcpyAsync(d_model.p, flat.data(), sizeof(PNode) * flat.size(), cudaMemcpyHostToDevice, st));
     const int F = ds.n_features;
     const size_t smem = (size_t)F * PRED_ROWS * sizeof(float);
