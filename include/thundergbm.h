@@ -137,6 +137,21 @@ int tgbm_predict_raw(int n_rows, const float *val, const int *row_ptr, const int
 int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, const float *label, const float *raw,
                       const int *group, int num_group, float *out);
 
+/* The same metric for callers that must not allocate device memory: a host whose own pool already owns the whole
+ * GPU, or a hook inside another program's step loop that cannot afford the device-wide synchronisation of
+ * cudaMalloc / cudaFree.  No counterpart in the reference (every reference entry point allocates).
+ * d_label, d_raw (raw[t * n_rows + i]) and d_out (one float) are DEVICE pointers owned by the caller; the kernels
+ * are queued on `cuda_stream` (a cudaStream_t, NULL = default stream) and the call returns without waiting.
+ * The reduction scratch is a fixed 8.2 KB array inside the library image on every GPU that loads the library.
+ * n_rows <= TGBM_NOALLOC_MAX_ROWS, trees_per_round <= TGBM_NOALLOC_MAX_CLASSES, no ranking objectives; anything else
+ * returns 1 with the reason in tgbm_last_error().  The first call on each device resolves the scratch address and
+ * should be made outside stream capture.  All calls on a device share the scratch: calls whose kernels can overlap
+ * on the GPU (unordered streams) race; calls on one stream are safe. */
+#define TGBM_NOALLOC_MAX_ROWS (1 << 30)
+#define TGBM_NOALLOC_MAX_CLASSES 1024
+int tgbm_metric_score_noalloc(const char *objective, int n_rows, int trees_per_round, const float *d_label,
+                              const float *d_raw, float *d_out, void *cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

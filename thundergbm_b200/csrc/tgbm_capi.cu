@@ -110,6 +110,10 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
 }
 }  // namespace
 
+namespace tgbm {
+void set_last_error(const std::string &msg) { g_err = msg; }
+}  // namespace tgbm
+
 extern "C" {
 
 const char *tgbm_last_error(void) { return g_err.c_str(); }

@@ -115,6 +115,9 @@ void set_verbosity(int v);
 int verbosity();
 void log_info(const char *fmt, ...);
 
+// message returned by tgbm_last_error() on the calling thread
+void set_last_error(const std::string &msg);
+
 void parse_param(GBMParam &p, int argc, char **argv);
 void save_model(const std::string &path, const GBMParam &p, const std::vector<std::vector<Tree>> &model,
                 const std::vector<float> &label);
