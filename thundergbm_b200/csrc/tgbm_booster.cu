@@ -269,7 +269,17 @@ void Booster::init(const DataSet &ds) {
                "multi:softmax / multi:softprob need more than two classes; use binary:logistic for two");
     m.num_class = p.num_class;
 
+    const bool timing = getenv("TGBM_TIMING") != nullptr;
+    auto t_mark = std::chrono::steady_clock::now();
+    auto lap = [&](const char *what) {
+        if (!timing) return;
+        cudaStreamSynchronize(m.stream);
+        const auto t = std::chrono::steady_clock::now();
+        fprintf(stderr, "[tgbm init] %-28s %8.1f ms\n", what, std::chrono::duration<double, std::milli>(t - t_mark).count());
+        t_mark = t;
+    };
     m.find_cuts_and_bins(ds);
+    lap("= cuts and bins, with frees");
 
     const int N = m.N, K = m.K, depth = m.depth;
     const size_t n1 = std::max<size_t>(N, 1);
@@ -311,9 +321,11 @@ void Booster::init(const DataSet &ds) {
     if (sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
         TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(TreeNode) * (size_t)m.n_nodes)));
     if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream);
+    lap("training buffers");
     m.init_base_score();
     TGBM_CUDA(cudaStreamSynchronize(m.stream));
     TGBM_CUDA(cudaGetLastError());
+    lap("base score");
 }
 
 // ------------------------------------------------------------------------------------------------
