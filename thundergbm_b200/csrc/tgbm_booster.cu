@@ -53,7 +53,7 @@ struct BoosterImpl {
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     DevBuf<SplitRec> recs;
-    DevBuf<int> node_tile0, tile_left, node_done_base;
+    DevBuf<int> node_tile0[2], tile_left, node_done_base;
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
     DevBuf<double> metric_partial, metric_sum;
@@ -308,7 +308,8 @@ void Booster::init(const DataSet &ds) {
     m.recs.alloc(((size_t)1 << (depth - 1)) * m.F);
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
     m.tile_left.alloc(m.max_tiles);
-    m.node_tile0.alloc(((size_t)1 << depth) + 1); m.node_done_base.alloc((size_t)1 << depth);
+    m.node_tile0[0].alloc(((size_t)1 << depth) + 1); m.node_tile0[1].alloc(((size_t)1 << depth) + 1);
+    m.node_done_base.alloc((size_t)1 << depth);
     m.bits.alloc((size_t)m.max_tiles * (PART_TILE / 32));
     m.ctl.alloc(1);
     m.ctl.zero(m.stream);
@@ -384,7 +385,10 @@ void BoosterImpl::build_tree(int round, int k) {
     const int2 *gq = ghq.p + (size_t)k * N;
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
-    ++launches;
+    k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
+                                        node_tile0[0].p, ctl.p);
+    launches += 2;
+    const int by_hessian = (comm && comm->active()) ? 1 : 0;
     const int hist_ctas = num_sms;
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * 2));
     for (int level = 0; level < depth; ++level) {
@@ -393,8 +397,6 @@ void BoosterImpl::build_tree(int round, int k) {
         const int *idx_in = level == 0 ? nullptr : rec_idx[cur].p;
         const int2 *gh_in = level == 0 ? gq : rec_gh[cur].p;
         // -- histogram of the root / of the smaller child of every pair
-        k_hist_plan<<<1, 1024, 0, stream>>>(level, seg_begin[cur].p, seg_cnt[cur].p, gcnt.p, nodes.p, (comm && comm->active()) ? 1 : 0,
-                                            built_right.p, hist_work.p, hist_tile_base.p, ctl.p);
         long long *built = level == 0 ? hist_full.p : hist_built.p;
         TGBM_CUDA(cudaMemsetAsync(built, 0, sizeof(long long) * 2 * (size_t)B * pairs, stream));
         TimedEvent ev{};
@@ -419,16 +421,16 @@ void BoosterImpl::build_tree(int round, int k) {
         // -- move the rows
         TimedEvent pv{};
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
-        k_part_plan<<<1, 1024, 0, stream>>>(level, seg_cnt[cur].p, node_tile0.p, ctl.p);
-        k_part_count<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0.p, ctl.p,
+        k_part_count<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
                                                              idx_in, binsT.p, Npad, bits.p, tile_left.p);
-        k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_cnt[cur].p, node_tile0.p, tile_left.p,
-                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, node_done_base.p, ctl.p);
-        k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0.p, ctl.p,
+        k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
+                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, node_done_base.p, ctl.p,
+                                            by_hessian, built_right.p, hist_work.p, hist_tile_base.p, node_tile0[nxt].p);
+        k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
                                                                idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p, node_done_base.p,
                                                                rec_idx[nxt].p, rec_gh[nxt].p, done_idx.p, done_nid.p);
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
-        launches += 8;
+        launches += 6;
     }
     k_prune<<<1, 1024, sizeof(TreeNode) * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, depth, p.gamma);
     if (N) k_predict_update<<<ceil_div(N, 256), 256, 0, stream>>>(nodes.p, done_idx.p, done_nid.p, N, p.learning_rate, ypred.p + (size_t)k * N,
@@ -486,7 +488,7 @@ HistProfile Booster::profile() {
     for (auto &e : m.events) {
         float ms = 0;
         cudaEventElapsedTime(&ms, e.a, e.b);
-        if (e.kind == 2) { r.partition_ms += ms; r.partition_launches += 4; }
+        if (e.kind == 2) { r.partition_ms += ms; r.partition_launches += 3; }
         else {
             r.hist_ms += ms; r.hist_launches += 1;
             if (e.kind == 0) { r.hist_root_ms += ms; r.hist_root_launches += 1; }

@@ -32,9 +32,8 @@ struct TreeCtl {  // device-side scalars of the tree being built
     int done_count;
     int n_hist_tiles;
     int n_hist_work;
-    int n_part_tiles;
+    int n_part_tiles[2];  // by level parity: level l+1 is planned while level l is still being scattered
     int n_records;  // records alive at the current level
-    int pad_;
     unsigned long long stat_rows_root, stat_rows_gather, stat_hists, stat_part_rows;
 };
 
@@ -277,12 +276,11 @@ __device__ inline int block_scan_excl(int n, In in, Out out, int *scratch) {
 }
 
 // Which sibling to build (the one with fewer rows over all ranks, ties -> left:
-// hist_tree_builder_single.cu:466) and the work list of the level.  One block of 1024 threads.
-static __global__ void __launch_bounds__(1024)
-k_hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
-            const int *__restrict__ gcnt, const TreeNode *__restrict__ nodes, int by_hessian,
-            int *__restrict__ built_right, HistWork *__restrict__ work, int *__restrict__ tile_base,
-            TreeCtl *__restrict__ ctl) {
+// hist_tree_builder_single.cu:466) and the work list of the level.  Called by every thread of a 1024-thread block.
+__device__ inline void hist_plan(int level, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+                                 const int *__restrict__ gcnt, const TreeNode *__restrict__ nodes, int by_hessian,
+                                 int *__restrict__ built_right, HistWork *__restrict__ work, int *__restrict__ tile_base,
+                                 TreeCtl *__restrict__ ctl) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     if (level == 0) {
@@ -658,9 +656,9 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
 // ------------------------------------------------------------------ instance partition
 // (replaces update_ins2node_id + the per-level radix sort, hist_tree_builder_single.cu:908-1020, :397-415)
 // Every node of the level that holds records gets ceil(count / PART_TILE) tiles of 4096 records;
-// node_tile0[n] is the first tile of node n.  One block.
-static __global__ void __launch_bounds__(1024)
-k_part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl) {
+// node_tile0[n] is the first tile of node n.  Called by every thread of a 1024-thread block.
+__device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0,
+                                 TreeCtl *__restrict__ ctl) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     const int nl = 1 << level;
@@ -673,7 +671,7 @@ k_part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_t
                                       }, scratch);
     if (threadIdx.x == 0) {
         node_tile0[nl] = total;
-        ctl->n_part_tiles = total;
+        ctl->n_part_tiles[level & 1] = total;
         ctl->stat_part_rows += rows;
     }
 }
@@ -697,7 +695,7 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
              const unsigned char *__restrict__ binsT, size_t Npad, unsigned *__restrict__ bits, int *__restrict__ tile_left) {
     __shared__ int wsum[32];
     __shared__ int sh_n;
-    const int nt = ctl->n_part_tiles, nl = 1 << level;
+    const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = blockIdx.x; t < nt; t += gridDim.x) {
         __syncthreads();
@@ -740,9 +738,11 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
 static __global__ void __launch_bounds__(1024)
 k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_cnt,
             const int *__restrict__ node_tile0, int *__restrict__ tile_left, int *__restrict__ next_begin,
-            int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base, TreeCtl *__restrict__ ctl) {
+            int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base, TreeCtl *__restrict__ ctl,
+            int by_hessian, int *__restrict__ built_right, HistWork *__restrict__ work, int *__restrict__ hist_tile_base,
+            int *__restrict__ next_node_tile0) {
     __shared__ int scratch[33];
-    const int nt = ctl->n_part_tiles, nl = 1 << level;
+    const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const bool last = level == depth - 1;
     // tile_left becomes the inclusive prefix over all tiles
     block_scan_excl(nt, [&](int i) { return tile_left[i]; }, [&](int i, int excl) { tile_left[i] += excl; }, scratch);
@@ -766,6 +766,22 @@ k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int 
         ctl->done_count = done0 + fin;
         ctl->n_records = last ? 0 : alive;
     }
+    if (!last) {  // work lists of the next level, so that it needs no planning launches of its own
+        __syncthreads();
+        hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl);
+        __syncthreads();
+        part_plan(level + 1, next_cnt, next_node_tile0, ctl);
+    }
+}
+
+// work lists of level 0 (the whole data set in the root)
+static __global__ void __launch_bounds__(1024)
+k_plan_root(const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt, const int *__restrict__ gcnt,
+            const TreeNode *__restrict__ nodes, int *__restrict__ built_right, HistWork *__restrict__ work,
+            int *__restrict__ hist_tile_base, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl) {
+    hist_plan(0, seg_begin, seg_cnt, gcnt, nodes, 0, built_right, work, hist_tile_base, ctl);
+    __syncthreads();
+    part_plan(0, seg_cnt, node_tile0, ctl);
 }
 
 // Stable scatter of the records into the child segments (or, for nodes that stopped splitting and
@@ -780,7 +796,7 @@ k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const i
     __shared__ int wpre[WORDS];
     __shared__ int wtot[4];
     __shared__ int sh_n;
-    const int nt = ctl->n_part_tiles, nl = 1 << level;
+    const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const bool last = level == depth - 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = blockIdx.x; t < nt; t += gridDim.x) {
