@@ -83,6 +83,7 @@ typedef struct {
 typedef struct {
     int n_rows, n_features, fpad, n_bins, trees_per_round, n_nodes, num_class, rounds_done, n_labels;
     float base_score;
+    int csr_layout; /* 1: wide sparse data kept as CSR of global bin ids, 0: dense byte matrices */
 } TgbmInfo;
 
 typedef struct {
@@ -117,7 +118,8 @@ int tgbm_booster_get_trees(TgbmBooster *b, void *nodes_out);
 int tgbm_booster_get_metrics(TgbmBooster *b, float *out);            /* rounds_done */
 int tgbm_booster_get_ypred(TgbmBooster *b, float *out);              /* trees_per_round * n_rows */
 int tgbm_booster_get_cuts(TgbmBooster *b, float *cut_val, int *cut_ptr); /* n_bins, n_features+1 */
-int tgbm_booster_get_bins(TgbmBooster *b, unsigned char *out);       /* n_rows * fpad, 255 = missing */
+int tgbm_booster_get_bins(TgbmBooster *b, unsigned char *out);       /* dense layout: n_rows * fpad, 255 = missing */
+int tgbm_booster_get_bins_csr(TgbmBooster *b, int *out);             /* CSR layout: global bin id per stored value */
 int tgbm_booster_get_nid(TgbmBooster *b, int *out);                  /* rounds_done*trees_per_round*n_rows (keep_nid) */
 int tgbm_booster_get_root_hist(TgbmBooster *b, long long *out);      /* n_bins*2 of the last tree */
 int tgbm_booster_get_quant_scale(TgbmBooster *b, double *out);       /* rounds_done*2 */

@@ -29,7 +29,11 @@ def test_cuts_and_bins_bit_exact(gpu, orc, cases, name):
     cv, cp = b.cuts()
     assert np.array_equal(cp, cut_ptr)
     assert cv.tobytes() == cut_val.tobytes()
-    assert np.array_equal(b.bins(), orc.bins_to_dense(d, bins, cut_ptr, b.info.fpad))
+    if b.info.csr_layout:
+        assert name == 'c4_sparse_small'
+        assert np.array_equal(b.bins_csr(d.nnz), bins)
+    else:
+        assert np.array_equal(b.bins(), orc.bins_to_dense(d, bins, cut_ptr, b.info.fpad))
     # and against what the reference itself produced
     g = load_golden(name)
     assert cv.tobytes() == g['cut_val'].tobytes() and np.array_equal(cp, g['cut_ptr'])
@@ -54,6 +58,40 @@ def test_training_bit_exact_with_oracle(gpu, orc, cases, name):
     assert np.array_equal(b.ypred(), o.ypred)        # raw training scores
     assert np.array_equal(b.metrics(), o.metric)
     b.close()
+
+
+@pytest.mark.parametrize('name', ['fixture_reg', 'fixture_rank', 'c2_higgs_small', 'c3_covtype_small', 'c5_mslr_small'])
+def test_csr_layout_forced_on_dense_data(gpu, orc, cases, name, monkeypatch):
+    """The CSR-of-bin-ids layout (chosen by itself only for wide sparse data) gives the same bits as the dense one."""
+    monkeypatch.setenv('TGBM_LAYOUT', 'sparse')
+    d, params = cases(name)
+    p = {**params, 'n_trees': min(params['n_trees'], 8)}
+    o = orc.train(d, hist_mode=1, keep_nid=1, **p)
+    b = _booster(d, p, keep_nid=1)
+    assert b.info.csr_layout == 1
+    b.boost(p['n_trees'])
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid)
+    assert np.array_equal(b.metrics(), o.metric)
+    assert np.array_equal(b.bins_csr(d.nnz), orc.bin_only(d, p['max_num_bin'])[2])
+    b.close()
+
+
+def test_csr_layout_unordered_columns(gpu, orc, cases):
+    """Rows whose columns arrive in arbitrary order train to the same trees (the bin ids are sorted per row at set-up)."""
+    from thundergbm_b200.synth import CsrData
+    d, params = cases('c4_sparse_small')
+    p = {**params, 'n_trees': 4}
+    rng = np.random.default_rng(5)
+    rows = np.repeat(np.arange(d.n_rows), np.diff(d.row_ptr))
+    order = np.lexsort((rng.random(d.nnz), rows))              # shuffle inside every row
+    ds = CsrData(d.n_rows, d.n_cols, d.row_ptr.copy(), d.col[order].copy(), d.val[order].copy(), d.y)
+    a = _booster(d, p); a.boost(4)
+    b = _booster(ds, p); b.boost(4)
+    assert b.info.csr_layout == 1
+    assert a.trees().tobytes() == b.trees().tobytes()
+    assert np.array_equal(a.bins_csr(d.nnz), b.bins_csr(d.nnz))
+    a.close(); b.close()
 
 
 @pytest.mark.parametrize('name', ['fixture_bin', 'c1_dense_reg', 'c2_higgs_small', 'c3_covtype_small', 'c4_sparse_small'])

@@ -20,7 +20,7 @@ class TgbmParam(C.Structure):
 
 class TgbmInfo(C.Structure):
     _fields_ = [(n, C.c_int) for n in ('n_rows', 'n_features', 'fpad', 'n_bins', 'trees_per_round', 'n_nodes',
-                                       'num_class', 'rounds_done', 'n_labels')] + [('base_score', C.c_float)]
+                                       'num_class', 'rounds_done', 'n_labels')] + [('base_score', C.c_float), ('csr_layout', C.c_int)]
 
 
 class TgbmProfile(C.Structure):
@@ -50,7 +50,7 @@ def load() -> C.CDLL:
     lib.tgbm_booster_boost_timed.argtypes = [vp, C.c_int, fp]
     lib.tgbm_booster_info.argtypes = [vp, P(TgbmInfo)]
     lib.tgbm_booster_profile.argtypes = [vp, P(TgbmProfile)]
-    for name in ('get_trees', 'get_metrics', 'get_ypred', 'get_bins', 'get_nid', 'get_root_hist', 'get_quant_scale',
+    for name in ('get_trees', 'get_metrics', 'get_ypred', 'get_bins', 'get_bins_csr', 'get_nid', 'get_root_hist', 'get_quant_scale',
                  'get_labels', 'to_model'):
         getattr(lib, 'tgbm_booster_' + name).argtypes = [vp, vp]
     lib.tgbm_booster_get_cuts.argtypes = [vp, vp, vp]

@@ -127,6 +127,10 @@ class Booster:
         i = self.info
         return self._get('get_bins', (i.n_rows, i.fpad), np.uint8)
 
+    def bins_csr(self, nnz: int) -> np.ndarray:
+        """CSR layout (info.csr_layout == 1): global bin id of every stored value, in input order."""
+        return self._get('get_bins_csr', (nnz,), np.int32)
+
     def nid(self) -> np.ndarray:
         i = self.info
         return self._get('get_nid', (i.rounds_done * i.trees_per_round, i.n_rows), np.int32)

@@ -37,6 +37,11 @@ struct BoosterImpl {
     std::vector<float> label;
 
     DevBuf<unsigned char> bins, binsT;
+    // wide sparse data: CSR of global bin ids instead of the two dense matrices
+    bool sparse = false;
+    long long nnz_local = 0;
+    DevBuf<int> sp_row_ptr, sp_bin, chunk_bin0;
+    int n_chunks = 0;
     DevBuf<float> cut_val, y, ypred, metric;
     DevBuf<int> cut_ptr, cut_fid;
     DevBuf<float2> gh;
@@ -191,12 +196,66 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     TGBM_CUDA(cudaMemcpyAsync(h_cut_val.data(), cut_val.p, sizeof(float) * B, cudaMemcpyDeviceToHost, stream));
 
     lap("cut point selection");
-    // bin matrix in both layouts
-    bins.alloc((size_t)N * Fpad);
-    binsT.alloc((size_t)F * Npad);
-    TGBM_CUDA(cudaMemsetAsync(bins.p, MISSING_BIN, bins.bytes(), stream));
-    TGBM_CUDA(cudaMemsetAsync(binsT.p, MISSING_BIN, binsT.bytes(), stream));
-    if (N) k_bin_dense<<<ceil_div(N, 128), 128, 0, stream>>>(d_row_ptr.p, d_col.p, d_val.p, N, cut_ptr.p, cut_val.p, Fpad, Npad, bins.p, binsT.p);
+    // Layout: dense byte matrices (row-major + column-major) unless they would dwarf the data itself -- then the
+    // reference's CSR of global bin ids.  TGBM_LAYOUT=dense|sparse overrides the choice (tests).
+    {
+        const double dense_bytes = 2.0 * (double)N * Fpad, csr_bytes = 4.0 * (double)nnz;
+        sparse = F > 256 && dense_bytes > 4.0 * csr_bytes;
+        if (const char *e = getenv("TGBM_LAYOUT")) {
+            if (!strcmp(e, "sparse")) sparse = true;
+            if (!strcmp(e, "dense")) sparse = false;
+        }
+        TGBM_CHECK(sparse || (long long)F * 32 <= (1 << 21), "the dense bin matrix supports at most 65536 features");
+    }
+    nnz_local = (long long)nnz;
+    if (sparse) {
+        sp_row_ptr.alloc(N + 1);
+        sp_bin.alloc(std::max<size_t>(nnz, 1));
+        TGBM_CUDA(cudaMemcpyAsync(sp_row_ptr.p, d_row_ptr.p, sizeof(int) * (N + 1), cudaMemcpyDeviceToDevice, stream));
+        if (nnz) k_bin_csr<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_col.p, d_val.p, nnz, cut_ptr.p, cut_val.p, sp_bin.p);
+        // rows whose columns arrive unordered are put in ascending bin order (= ascending column order)
+        if (nnz) {
+            DevBuf<int> unsorted;
+            unsorted.alloc(1);
+            TGBM_CUDA(cudaMemsetAsync(unsorted.p, 0, sizeof(int), stream));
+            k_rows_unsorted<<<std::min(ceil_div(N, 256), num_sms * 16), 256, 0, stream>>>(sp_row_ptr.p, sp_bin.p, N, unsorted.p);
+            int h_unsorted = 0;
+            TGBM_CUDA(cudaMemcpyAsync(&h_unsorted, unsorted.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
+            TGBM_CUDA(cudaStreamSynchronize(stream));
+            if (h_unsorted) {
+                DevBuf<int> sorted_bin;
+                sorted_bin.alloc(nnz);
+                size_t tmp_bytes = 0;
+                TGBM_CUDA(cub::DeviceSegmentedSort::SortKeys(nullptr, tmp_bytes, sp_bin.p, sorted_bin.p, (long long)nnz, (long long)N, sp_row_ptr.p,
+                                                             sp_row_ptr.p + 1, stream));
+                DevBuf<unsigned char> tmp;
+                tmp.alloc(std::max<size_t>(tmp_bytes, 1));
+                TGBM_CUDA(cub::DeviceSegmentedSort::SortKeys(tmp.p, tmp_bytes, sp_bin.p, sorted_bin.p, (long long)nnz, (long long)N, sp_row_ptr.p,
+                                                             sp_row_ptr.p + 1, stream));
+                TGBM_CUDA(cudaMemcpyAsync(sp_bin.p, sorted_bin.p, sizeof(int) * nnz, cudaMemcpyDeviceToDevice, stream));
+                TGBM_CUDA(cudaStreamSynchronize(stream));
+            }
+        }
+        // chunks of whole features with at most 256 bins for the split evaluation
+        std::vector<int> cb(1, 0);
+        int cur = 0;
+        for (int f = 0; f < F; ++f) {
+            const int nbf = h_cut_ptr[f + 1] - h_cut_ptr[f];
+            if (cur + nbf > 256 && cur > 0) { cb.push_back(h_cut_ptr[f]); cur = 0; }
+            cur += nbf;
+        }
+        if (cb.back() != B) cb.push_back(B);
+        n_chunks = (int)cb.size() - 1;
+        chunk_bin0.alloc(cb.size());
+        TGBM_CUDA(cudaMemcpyAsync(chunk_bin0.p, cb.data(), sizeof(int) * cb.size(), cudaMemcpyHostToDevice, stream));
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+    } else {
+        bins.alloc((size_t)N * Fpad);
+        binsT.alloc((size_t)F * Npad);
+        TGBM_CUDA(cudaMemsetAsync(bins.p, MISSING_BIN, bins.bytes(), stream));
+        TGBM_CUDA(cudaMemsetAsync(binsT.p, MISSING_BIN, binsT.bytes(), stream));
+        if (N) k_bin_dense<<<ceil_div(N, 128), 128, 0, stream>>>(d_row_ptr.p, d_col.p, d_val.p, N, cut_ptr.p, cut_val.p, Fpad, Npad, bins.p, binsT.p);
+    }
     TGBM_CUDA(cudaStreamSynchronize(stream));
     TGBM_CUDA(cudaGetLastError());
     lap("binning");
@@ -250,7 +309,6 @@ void Booster::init(const DataSet &ds) {
     }
     TGBM_CHECK(m.N_global < (1ll << 31), "row count must fit 32 bits");
     TGBM_CHECK(m.F >= 1, "data set has no features");
-    TGBM_CHECK((long long)m.F * 32 <= (1 << 21), "dense bin matrix supports at most 65536 features; wider data needs the sparse layout");
     m.Fpad = (m.F + 31) / 32 * 32;
     m.G = m.Fpad / 32;
     m.Npad = ((size_t)m.N + 127) / 128 * 128;
@@ -305,7 +363,7 @@ void Booster::init(const DataSet &ds) {
     m.hist_built.alloc(std::max<size_t>(1, (size_t)1 << std::max(0, depth - 2)) * B1 * 2);
     const int max_pairs = std::max(1, 1 << std::max(0, depth - 2));
     m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
-    m.recs.alloc(((size_t)1 << (depth - 1)) * m.F);
+    m.recs.alloc(((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
     m.tile_left.alloc(m.max_tiles);
     m.node_tile0[0].alloc(((size_t)1 << depth) + 1); m.node_tile0[1].alloc(((size_t)1 << depth) + 1);
@@ -319,6 +377,8 @@ void Booster::init(const DataSet &ds) {
     m.hist_smem = 2 * 256 * 32 * 4 + 2 * 256 * 32 * 8;  // int32 accumulators + int64 totals, both [2][256 bins][32 features]
     TGBM_CUDA(cudaFuncSetAttribute(k_hist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
+    TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
+    TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
     if (sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
         TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(TreeNode) * (size_t)m.n_nodes)));
     if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream);
@@ -405,7 +465,16 @@ void BoosterImpl::build_tree(int round, int k) {
             ev.kind = level == 0 ? 0 : 1;
             cudaEventRecord(ev.a, stream);
         }
-        if (level == 0)
+        if (sparse) {
+            const int sp_ctas = num_sms * 2;
+            const size_t sp_smem = (size_t)std::min(B, SPARSE_SMEM_BINS) * 16;
+            if (level == 0)
+                k_hist_sparse<false><<<sp_ctas, SPARSE_THREADS, sp_smem, stream>>>(sp_row_ptr.p, sp_bin.p, nullptr, gh_in, hist_work.p,
+                                                                                   hist_tile_base.p, ctl.p, built, B);
+            else
+                k_hist_sparse<true><<<sp_ctas, SPARSE_THREADS, sp_smem, stream>>>(sp_row_ptr.p, sp_bin.p, idx_in, gh_in, hist_work.p,
+                                                                                  hist_tile_base.p, ctl.p, built, B);
+        } else if (level == 0)
             k_hist<false><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, nullptr, gh_in, hist_work.p, hist_tile_base.p,
                                                                                    ctl.p, cut_ptr.p, cut_fid.p, built, B, window_rows);
         else
@@ -414,15 +483,26 @@ void BoosterImpl::build_tree(int round, int k) {
         if (profile_on) { cudaEventRecord(ev.b, stream); events.push_back(ev); }
         if (comm && comm->active()) comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
         // -- split selection and tree update
-        k_eval<<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built,
-                                                  level == 0 ? nullptr : hist_full.p + full_offset(level - 1),
-                                                  hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p);
-        k_best_apply<<<nl, 32, 0, stream>>>(level, F, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda);
+        const long long *parent_hist = level == 0 ? nullptr : hist_full.p + full_offset(level - 1);
+        if (sparse) {
+            k_eval_chunk<<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
+                                                                   built, parent_hist, hist_full.p + full_offset(level), qinfo.p,
+                                                                   p.min_child_weight, p.lambda, recs.p);
+            k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
+        } else {
+            k_eval<<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built, parent_hist,
+                                                      hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p);
+            k_best_apply<<<nl, 32, 0, stream>>>(level, F, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 0);
+        }
         // -- move the rows
         TimedEvent pv{};
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
-        k_part_count<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                             idx_in, binsT.p, Npad, bits.p, tile_left.p);
+        if (sparse)
+            k_part_count<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
+                                                                       idx_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, bits.p, tile_left.p);
+        else
+            k_part_count<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
+                                                                        idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p);
         k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
                                             seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, node_done_base.p, ctl.p,
                                             by_hessian, built_right.p, hist_work.p, hist_tile_base.p, node_tile0[nxt].p);
@@ -497,8 +577,10 @@ HistProfile Booster::profile() {
     TreeCtl c;
     TGBM_CUDA(cudaMemcpy(&c, m.ctl.p, sizeof(c), cudaMemcpyDeviceToHost));
     // algorithmic bytes: rows * (F bin bytes + 8 gradient bytes [+ 4 row index]) + histograms * B * 16 written
-    r.hist_root_bytes = (double)c.stat_rows_root * (m.F + 8);
-    r.hist_bytes = r.hist_root_bytes + (double)c.stat_rows_gather * (m.F + 8 + 4) + (double)c.stat_hists * m.B * 16.0;
+    // per row: its bin ids (F bytes dense; 4 bytes per stored value + a row pointer in the CSR layout), 8 gradient bytes
+    const double row_bytes = m.sparse ? 4.0 * (double)m.nnz_local / std::max(1, m.N) + 4.0 : (double)m.F;
+    r.hist_root_bytes = (double)c.stat_rows_root * (row_bytes + 8);
+    r.hist_bytes = r.hist_root_bytes + (double)c.stat_rows_gather * (row_bytes + 8 + 4) + (double)c.stat_hists * m.B * 16.0;
     r.partition_bytes = (double)c.stat_part_rows * (4 + 1 + 4);
     r.kernel_launches = m.launches;
     return r;
@@ -531,7 +613,17 @@ std::vector<float> Booster::get_metrics() { sync(); return to_host(impl_->metric
 std::vector<float> Booster::get_ypred() { sync(); return to_host(impl_->ypred.p, (size_t)impl_->N * impl_->K); }
 std::vector<float> Booster::get_cut_val() const { return impl_->h_cut_val; }
 std::vector<int> Booster::get_cut_ptr() const { return impl_->h_cut_ptr; }
-std::vector<unsigned char> Booster::get_bins() { sync(); return to_host(impl_->bins.p, (size_t)impl_->N * impl_->Fpad); }
+std::vector<unsigned char> Booster::get_bins() {
+    sync();
+    TGBM_CHECK(!impl_->sparse, "the booster holds the CSR layout: use get_bins_csr");
+    return to_host(impl_->bins.p, (size_t)impl_->N * impl_->Fpad);
+}
+std::vector<int> Booster::get_bins_csr() {
+    sync();
+    TGBM_CHECK(impl_->sparse, "the booster holds the dense layout: use get_bins");
+    return to_host(impl_->sp_bin.p, (size_t)impl_->nnz_local);
+}
+bool Booster::is_sparse() const { return impl_->sparse; }
 std::vector<int> Booster::get_nid() {
     sync();
     if (!impl_->p.keep_nid) return {};

@@ -58,7 +58,9 @@ public:
     std::vector<float> get_ypred();                       // [K][N] raw scores of the training rows
     std::vector<float> get_cut_val() const;
     std::vector<int> get_cut_ptr() const;
-    std::vector<unsigned char> get_bins();                // [N][Fpad] local bin ids, 255 = missing
+    std::vector<unsigned char> get_bins();                // dense layout: [N][Fpad] local bin ids, 255 = missing
+    std::vector<int> get_bins_csr();                      // CSR layout: global bin id per stored value
+    bool is_sparse() const;
     std::vector<int> get_nid();                           // [tree][N] when param.keep_nid
     std::vector<long long> get_root_hist();               // [B][2] level-0 histogram of the last tree built
     std::vector<double> get_quant_scale();                // per round: scale_g, scale_h

@@ -342,6 +342,7 @@ int tgbm_booster_info(TgbmBooster *b, TgbmInfo *o) {
         o->n_rows = b->n_rows; o->n_features = b->b->n_features(); o->fpad = b->b->fpad(); o->n_bins = b->b->n_bins();
         o->trees_per_round = b->b->trees_per_round(); o->n_nodes = b->b->n_nodes(); o->num_class = b->b->num_class();
         o->rounds_done = b->b->rounds_done(); o->n_labels = (int)b->label.size(); o->base_score = b->b->base_score();
+        o->csr_layout = b->b->is_sparse() ? 1 : 0;
     });
 }
 int tgbm_booster_profile(TgbmBooster *b, TgbmProfile *o) {
@@ -368,6 +369,7 @@ int tgbm_booster_get_cuts(TgbmBooster *b, float *cut_val, int *cut_ptr) {
     });
 }
 int tgbm_booster_get_bins(TgbmBooster *b, unsigned char *out) { return guard([&] { auto v = b->b->get_bins(); std::copy(v.begin(), v.end(), out); }); }
+int tgbm_booster_get_bins_csr(TgbmBooster *b, int *out) { return guard([&] { auto v = b->b->get_bins_csr(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_nid(TgbmBooster *b, int *out) { return guard([&] { auto v = b->b->get_nid(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_root_hist(TgbmBooster *b, long long *out) { return guard([&] { auto v = b->b->get_root_hist(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_quant_scale(TgbmBooster *b, double *out) { return guard([&] { auto v = b->b->get_quant_scale(); std::copy(v.begin(), v.end(), out); }); }

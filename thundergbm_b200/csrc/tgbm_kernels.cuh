@@ -117,6 +117,31 @@ static __global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *_
     }
 }
 
+// Wide sparse data: the reference's own layout, one global bin id per stored value
+// (hist_tree_builder_single.cu:113-119), sharing the CSR row pointers.
+static __global__ void k_bin_csr(const int *__restrict__ col, const float *__restrict__ val, size_t nnz,
+                                 const int *__restrict__ cut_ptr, const float *__restrict__ cut_val, int *__restrict__ out) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nnz; i += (size_t)gridDim.x * blockDim.x) {
+        const int f = col[i];
+        const float v = val[i];
+        int lo = cut_ptr[f], hi = cut_ptr[f + 1] - 1;
+        while (lo < hi) {
+            const int mid = lo + (hi - lo) / 2;
+            if (cut_val[mid] <= v) lo = mid + 1; else hi = mid;
+        }
+        out[i] = lo;
+    }
+}
+
+// flag = 1 when some row's bin ids do not ascend (the partition looks a feature up by binary search inside the row)
+static __global__ void k_rows_unsorted(const int *__restrict__ row_ptr, const int *__restrict__ bin, int n_rows, int *__restrict__ flag) {
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n_rows; r += gridDim.x * blockDim.x) {
+        bool bad = false;
+        for (int i = row_ptr[r] + 1; i < row_ptr[r + 1]; ++i) bad |= bin[i - 1] > bin[i];
+        if (bad) *flag = 1;
+    }
+}
+
 // ------------------------------------------------------------------ objectives
 // block-wide maximum of |g| and h, then one atomic pair per block (every thread of the block must call it)
 __device__ inline void track_max(float ag, float h, unsigned *maxbits) {
@@ -491,6 +516,72 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
     flush(slab_cur);
 }
 
+// Histogram build for the wide sparse layout (CSR of global bin ids).  A histogram of ~100k bins does not fit in
+// shared memory; with Zipf-like column frequencies most updates hit the lowest column ids, so the first
+// SPARSE_SMEM_BINS bins are accumulated per CTA in shared memory (int64 atomics) and the long tail goes straight to
+// the node's histogram with global int64 atomics (L2-resident: 16 B per bin).  One warp per row, lanes over its values.
+constexpr int SPARSE_SMEM_BINS = 6144;
+constexpr int SPARSE_THREADS = 256;
+
+template <bool GATHER>
+static __global__ void __launch_bounds__(SPARSE_THREADS)
+k_hist_sparse(const int *__restrict__ row_ptr, const int *__restrict__ bin, const int *__restrict__ rec_idx,
+              const int2 *__restrict__ rec_gh, const HistWork *__restrict__ work, const int *__restrict__ tile_base,
+              const TreeCtl *__restrict__ ctl, long long *__restrict__ slab, int B) {
+    extern __shared__ __align__(16) long long sh_sparse[];  // [SPARSE_SMEM_BINS][2]
+    const int nsm = min(B, SPARSE_SMEM_BINS);
+    const int total = ctl->n_hist_tiles, nwork = ctl->n_hist_work;
+    const int per = (total + gridDim.x - 1) / gridDim.x;
+    const int t_begin = min(total, (int)blockIdx.x * per), t_end = min(total, t_begin + per);
+    if (t_begin >= t_end) return;
+    for (int i = threadIdx.x; i < 2 * nsm; i += SPARSE_THREADS) sh_sparse[i] = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    auto flush = [&](int slab_idx) {
+        __syncthreads();
+        long long *dst = slab + (size_t)slab_idx * B * 2;
+        for (int i = threadIdx.x; i < 2 * nsm; i += SPARSE_THREADS) {
+            const long long v = sh_sparse[i];
+            if (v) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + i), (unsigned long long)v); sh_sparse[i] = 0; }
+        }
+        __syncthreads();
+    };
+    int w = 0;
+    {
+        int lo = 0, hi = nwork - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) / 2;
+            if (tile_base[mid] <= t_begin) lo = mid; else hi = mid - 1;
+        }
+        w = lo;
+    }
+    int w_cur = w;
+    for (int t = t_begin; t < t_end; ++t) {
+        while (w + 1 < nwork && t >= tile_base[w + 1]) ++w;
+        if (w != w_cur) { flush(work[w_cur].slab); w_cur = w; }
+        const HistWork it = work[w];
+        long long *dst = slab + (size_t)it.slab * B * 2;
+        const int first = (t - tile_base[w]) * HIST_THREADS;
+        const int last = min(it.count, first + HIST_THREADS);
+        for (int q = first + warp; q < last; q += SPARSE_THREADS / 32) {
+            const int p = it.begin + q;
+            const int r = GATHER ? rec_idx[p] : p;
+            const int2 v = rec_gh[p];
+            for (int j = row_ptr[r] + lane; j < row_ptr[r + 1]; j += 32) {
+                const int b = bin[j];
+                if (b < nsm) {
+                    atomicAdd(reinterpret_cast<unsigned long long *>(sh_sparse + 2 * b), (unsigned long long)(long long)v.x);
+                    atomicAdd(reinterpret_cast<unsigned long long *>(sh_sparse + 2 * b + 1), (unsigned long long)(long long)v.y);
+                } else {
+                    atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b), (unsigned long long)(long long)v.x);
+                    atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b + 1), (unsigned long long)(long long)v.y);
+                }
+            }
+        }
+    }
+    flush(work[w_cur].slab);
+}
+
 // ------------------------------------------------------------------ split evaluation
 __device__ __forceinline__ float split_gain(float pg, float ph, float lg, float lh, float rg, float rh, float mcw, float lam) {
     // compute_gain, hist_tree_builder_single.cu:279-286 (no fused multiply-add: products feed divisions)
@@ -592,28 +683,156 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode 
     if (lane == 0) recs[(size_t)node_local * F + f] = SplitRec{best, best_bin, best_lg, best_lh, mg, mh};
 }
 
-// Per-node argmax over the features, SplitPoint decode and update_tree
-// (hist_tree_builder_single.cu:365-389 and :847-902).  One warp per node of the level.
-static __global__ void __launch_bounds__(32)
-k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
-             const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam) {
-    const int n = blockIdx.x, lane = threadIdx.x;
-    const int nid = (1 << level) - 1 + n;
-    if (!nodes[nid].is_valid) return;
-    unsigned long long key = 0;
-    for (int f = lane; f < F; f += 32) {
-        const SplitRec r = recs[(size_t)n * F + f];
-        if (r.bin < 0) continue;
-        const unsigned long long k = ((unsigned long long)__float_as_uint(fabsf(r.gain)) << 32) | (unsigned)(0x7fffffff - f);
-        if (k > key) key = k;
+// The same evaluation for data with many narrow features: one block handles a chunk of whole features whose bins
+// add up to at most 256 (a 100k-column one-hot-like data set has one or two bins per feature; a block per feature
+// would launch millions of near-empty blocks).  The scan is segmented by feature; the record of a (node, chunk) keeps
+// the GLOBAL bin index of its best candidate.  grid = (chunks, pairs); block = 64.
+static __global__ void __launch_bounds__(64)
+k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0, const int *__restrict__ cut_ptr,
+             const int *__restrict__ cut_fid, const TreeNode *__restrict__ nodes, const int *__restrict__ built_right,
+             const long long *__restrict__ built, const long long *__restrict__ parent, long long *__restrict__ full,
+             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs) {
+    __shared__ long long sg[2][256], sh[2][256];
+    const int c = blockIdx.x, j = blockIdx.y;
+    const int b0 = chunk_bin0[c], nb = chunk_bin0[c + 1] - b0;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_children = level == 0 ? 1 : 2;
+    const int node_local = level == 0 ? 0 : 2 * j + warp;
+    const int off = (1 << level) - 1;
+    const SplitRec none = {0.f, -1, 0.f, 0.f, 0.f, 0.f};
+    const int br = built_right[j];
+    if (nb == 0 || br < 0) {
+        if (lane == 0 && warp < n_children) recs[(size_t)node_local * n_chunks + c] = none;
+        return;
     }
-    // a record with gain 0 still has key == 0x7fffffff - f > 0, so 0 means "no record"
+    if (level == 0) {
+        for (int i = threadIdx.x; i < nb; i += 64) { sg[0][i] = built[2 * (b0 + i)]; sh[0][i] = built[2 * (b0 + i) + 1]; }
+    } else {
+        const long long *bp = built + (size_t)j * B * 2, *pp = parent + (size_t)j * B * 2;
+        long long *fb = full + (size_t)(2 * j + br) * B * 2, *fo = full + (size_t)(2 * j + 1 - br) * B * 2;
+        for (int i = threadIdx.x; i < nb; i += 64) {
+            const long long cg = bp[2 * (b0 + i)], ch = bp[2 * (b0 + i) + 1];
+            const long long og = pp[2 * (b0 + i)] - cg, oh = pp[2 * (b0 + i) + 1] - ch;
+            sg[br][i] = cg; sh[br][i] = ch;
+            sg[1 - br][i] = og; sh[1 - br][i] = oh;
+            fb[2 * (b0 + i)] = cg; fb[2 * (b0 + i) + 1] = ch;
+            fo[2 * (b0 + i)] = og; fo[2 * (b0 + i) + 1] = oh;
+        }
+    }
+    __syncthreads();
+    if (warp >= n_children) return;
+    const TreeNode nd = nodes[off + node_local];
+    if (!nd.is_valid) {
+        if (lane == 0) recs[(size_t)node_local * n_chunks + c] = none;
+        return;
+    }
+    // lane-local pass over 8 consecutive bins; sums restart where a feature starts
+    long long eg[8], eh[8];       // exclusive prefix inside the feature, as far as the lane can see
+    bool before_start[8];         // no feature start in this lane up to and including this bin -> add the carry
+    long long rg = 0, rh = 0;
+    bool seen = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int b = lane * 8 + i;
+        if (b < nb) {
+            const int f = cut_fid[b0 + b];
+            if (cut_ptr[f] == b0 + b) { rg = 0; rh = 0; seen = true; }
+            eg[i] = rg; eh[i] = rh; before_start[i] = !seen;
+            rg += sg[warp][b]; rh += sh[warp][b];
+        } else { eg[i] = 0; eh[i] = 0; before_start[i] = false; }
+    }
+    // segmented inclusive scan of the lanes' open tails (rg, rh); flag = the lane contains a feature start
+    long long vg = rg, vh = rh;
+    bool fl = seen;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const long long ug = shfl_up_ll(vg, o), uh = shfl_up_ll(vh, o);
+        const int uf = __shfl_up_sync(0xffffffffu, (int)fl, o);
+        if (lane >= o) {
+            if (!fl) { vg += ug; vh += uh; }
+            fl = fl || uf;
+        }
+    }
+    long long cg = shfl_up_ll(vg, 1), ch = shfl_up_ll(vh, 1);  // carry into this lane = inclusive value of lane-1
+    if (lane == 0) { cg = 0; ch = 0; }
+    // inclusive prefix per bin back into shared memory: the last bin of a feature then holds the feature total
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int b = lane * 8 + i;
+        if (b < nb) {
+            if (before_start[i]) { eg[i] += cg; eh[i] += ch; }
+            const long long ig = eg[i] + sg[warp][b], ih = eh[i] + sh[warp][b];
+            sg[warp][b] = ig; sh[warp][b] = ih;
+        }
+    }
+    __syncwarp();
+    const float pg = nd.sum_g, ph = nd.sum_h;
+    float best = 0.f, best_lg = 0.f, best_lh = 0.f, best_mg = 0.f, best_mh = 0.f;
+    int best_bin = -1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int b = lane * 8 + i;
+        if (b < nb) {
+            const int f = cut_fid[b0 + b];
+            const int lastb = cut_ptr[f + 1] - 1 - b0;
+            const float mg = __fsub_rn(pg, q2f(sg[warp][lastb], q->inv_sg)), mh = __fsub_rn(ph, q2f(sh[warp][lastb], q->inv_sh));
+            const float lg = q2f(eg[i], q->inv_sg), lh = q2f(eh[i], q->inv_sh);
+            const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
+            const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
+            const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
+            const float gn = gl > gr ? gl : -gr;
+            if (best_bin < 0 || fabsf(gn) > fabsf(best)) { best = gn; best_bin = b0 + b; best_lg = lg; best_lh = lh; best_mg = mg; best_mh = mh; }
+        }
+    }
+    unsigned long long key = best_bin < 0 ? 0ull
+                                          : (((unsigned long long)__float_as_uint(fabsf(best)) << 32) | (unsigned)(0x7fffffff - best_bin));
     unsigned long long mk = key;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const unsigned long long other = (unsigned long long)shfl_xor_ll((long long)mk, o);
         mk = other > mk ? other : mk;
     }
+    const unsigned win = __ballot_sync(0xffffffffu, key == mk && best_bin >= 0);
+    const int src = __ffs(win) - 1;
+    best = __shfl_sync(0xffffffffu, best, src);
+    best_bin = __shfl_sync(0xffffffffu, best_bin, src);
+    best_lg = __shfl_sync(0xffffffffu, best_lg, src);
+    best_lh = __shfl_sync(0xffffffffu, best_lh, src);
+    best_mg = __shfl_sync(0xffffffffu, best_mg, src);
+    best_mh = __shfl_sync(0xffffffffu, best_mh, src);
+    if (lane == 0) recs[(size_t)node_local * n_chunks + c] = SplitRec{best, best_bin, best_lg, best_lh, best_mg, best_mh};
+}
+
+// Per-node argmax over the features, SplitPoint decode and update_tree
+// (hist_tree_builder_single.cu:365-389 and :847-902).  One warp per node of the level.
+static __global__ void __launch_bounds__(32)
+k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
+             const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam,
+             const int *__restrict__ cut_fid, int chunked) {
+    // chunked: F is the number of chunks and a record's bin is a global bin index (k_eval_chunk);
+    // otherwise one record per feature with a feature-local bin (k_eval).  Ties go to the smaller global bin either way.
+    const int n = blockIdx.x, lane = threadIdx.x;
+    const int nid = (1 << level) - 1 + n;
+    if (!nodes[nid].is_valid) return;
+    unsigned long long key = 0;
+    int key_col = 0;  // record column (feature or chunk) of this lane's best key
+    for (int f = lane; f < F; f += 32) {
+        const SplitRec r = recs[(size_t)n * F + f];
+        if (r.bin < 0) continue;
+        const unsigned long long k = ((unsigned long long)__float_as_uint(fabsf(r.gain)) << 32) |
+                                     (unsigned)(0x7fffffff - (chunked ? r.bin : f));
+        if (k > key) { key = k; key_col = f; }
+    }
+    // a record with gain 0 still has a key > 0, so 0 means "no record"
+    unsigned long long mk = key;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = (unsigned long long)shfl_xor_ll((long long)mk, o);
+        mk = other > mk ? other : mk;
+    }
+    const unsigned winners = __ballot_sync(0xffffffffu, key == mk);
+    const int win_col = __shfl_sync(0xffffffffu, key_col, __ffs(winners) - 1);
     if (lane != 0) return;
     TreeNode &nd = nodes[nid];
     if (mk == 0) {  // no feature has a cut point: nothing to split on
@@ -622,8 +841,16 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
         nodes[nd.rch_index].is_valid = 0;
         return;
     }
-    const int f = 0x7fffffff - (int)(mk & 0xffffffffull);
-    const SplitRec r = recs[(size_t)n * F + f];
+    int f = 0x7fffffff - (int)(mk & 0xffffffffull);
+    SplitRec r;
+    if (chunked) {
+        const int gbin = f;
+        f = cut_fid[gbin];
+        r = recs[(size_t)n * F + win_col];
+        r.bin = gbin - cut_ptr[f];
+    } else {
+        r = recs[(size_t)n * F + f];
+    }
     const float gain = fabsf(r.gain);
     if (gain > rt_eps) {
         const bool default_right = r.gain < 0.f;
@@ -689,10 +916,15 @@ __device__ inline int tile_owner(const int *__restrict__ node_tile0, int nl, int
 // Direction of every record of a splittable node: left unless (missing and default right) or
 // bin >= split_bid (hist_tree_builder_single.cu:1003-1012).  One bit per record, one count per tile.
 // Persistent blocks; a thread handles PART_RPT records of a tile so that their loads overlap.
+// SPARSE: the row's bin of the split feature is searched in its CSR bin ids (hist_tree_builder_single.cu:941-966)
+// instead of being read from the column-major matrix.
+template <bool SPARSE>
 static __global__ void __launch_bounds__(PART_THREADS)
 k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
              const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
-             const unsigned char *__restrict__ binsT, size_t Npad, unsigned *__restrict__ bits, int *__restrict__ tile_left) {
+             const unsigned char *__restrict__ binsT, size_t Npad, const int *__restrict__ sp_row_ptr,
+             const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr, unsigned *__restrict__ bits,
+             int *__restrict__ tile_left) {
     __shared__ int wsum[32];
     __shared__ int sh_n;
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
@@ -705,7 +937,7 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
         const TreeNode nd = nodes[nl - 1 + n];
         if (!(nd.is_valid && !nd.is_leaf)) { if (threadIdx.x == 0) tile_left[t] = 0; continue; }
         const int p0 = seg_begin[n] + (t - node_tile0[n]) * PART_TILE, end = seg_begin[n] + seg_cnt[n];
-        const unsigned char *colp = binsT + (size_t)nd.split_feature_id * Npad;
+        const unsigned char *colp = SPARSE ? nullptr : binsT + (size_t)nd.split_feature_id * Npad;
         int r[PART_RPT];
 #pragma unroll
         for (int j = 0; j < PART_RPT; ++j) {
@@ -713,8 +945,24 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
             r[j] = p < end ? (rec_idx ? rec_idx[p] : p) : -1;
         }
         unsigned char b[PART_RPT];
+        if (SPARSE) {
+            const int c0 = cut_ptr[nd.split_feature_id], c1 = cut_ptr[nd.split_feature_id + 1];
 #pragma unroll
-        for (int j = 0; j < PART_RPT; ++j) b[j] = r[j] >= 0 ? colp[r[j]] : 0;
+            for (int j = 0; j < PART_RPT; ++j) {
+                b[j] = MISSING_BIN;
+                if (r[j] >= 0) {
+                    int lo = sp_row_ptr[r[j]], hi = sp_row_ptr[r[j] + 1];  // bin ids ascend inside a row
+                    while (lo < hi) {
+                        const int mid = lo + (hi - lo) / 2, v = sp_bin[mid];
+                        if (v >= c0 && v < c1) { b[j] = (unsigned char)(v - c0); break; }
+                        if (v < c0) lo = mid + 1; else hi = mid;
+                    }
+                }
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < PART_RPT; ++j) b[j] = r[j] >= 0 ? colp[r[j]] : 0;
+        }
         int cnt = 0;
 #pragma unroll
         for (int j = 0; j < PART_RPT; ++j) {
