@@ -296,6 +296,14 @@ TgbmBooster *tgbm_booster_create(int n_rows, const float *val, const int *row_pt
                                  const int *group, int num_group, const TgbmParam *param, TgbmComm *comm) {
     TgbmBooster *h = nullptr;
     guard([&] {
+        const bool timing = getenv("TGBM_TIMING") != nullptr;  // phase times of the set-up on stderr
+        auto t_mark = std::chrono::steady_clock::now();
+        auto lap = [&](const char *what) {
+            if (!timing) return;
+            const auto t = std::chrono::steady_clock::now();
+            fprintf(stderr, "[tgbm create] %-26s %8.1f ms\n", what, std::chrono::duration<double, std::milli>(t - t_mark).count());
+            t_mark = t;
+        };
         std::unique_ptr<TgbmBooster> b(new TgbmBooster);
         b->param = param_from_c(param);
         tgbm::set_verbosity(param->verbose);
@@ -309,11 +317,14 @@ TgbmBooster *tgbm_booster_create(int n_rows, const float *val, const int *row_pt
         } else {
             ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, b->param);
         }
+        lap("host view of the data");
         b->label = ds.label;
         b->n_rows = n_rows;
         b->b = new tgbm::Booster(b->param, c);
         b->b->set_profile(param->profile != 0);
+        lap("booster object");
         b->b->init(ds);
+        lap("init");
         h = b.release();
     });
     return h;

@@ -66,19 +66,44 @@ void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *
 
 // src/thundergbm/dataset.cpp:83-101: labels cast to int, sorted, uniqued; y -> index of its value
 void DataSet::group_label() {
-    std::vector<int> t(y.begin(), y.end());
+    // distinct int(label) values, found by a few threads (each keeps a small sorted set and a last-value cache)
+    const size_t n = y.size();
+    const int nt = (int)std::max<size_t>(1, std::min<size_t>(16, n / (1 << 20)));
+    std::vector<std::vector<int>> found(nt);
+    {
+        std::vector<std::thread> th;
+        for (int t = 0; t < nt; ++t)
+            th.emplace_back([&, t] {
+                std::vector<int> &set = found[t];
+                bool have = false;
+                int last = 0;
+                for (size_t i = n * t / nt; i < n * (t + 1) / nt; ++i) {
+                    const int v = (int)y[i];
+                    if (have && v == last) continue;
+                    have = true; last = v;
+                    auto it = std::lower_bound(set.begin(), set.end(), v);
+                    if (it == set.end() || *it != v) set.insert(it, v);
+                }
+            });
+        for (auto &x : th) x.join();
+    }
+    std::vector<int> t;
+    for (auto &f : found) t.insert(t.end(), f.begin(), f.end());
     std::sort(t.begin(), t.end());
     t.erase(std::unique(t.begin(), t.end()), t.end());
-    std::map<float, int> m;
     label.clear();
-    for (int v : t) {
-        m[(float)v] = (int)label.size();
-        label.push_back((float)v);
-    }
-    for (auto &v : y) {
-        auto it = m.find(v);
-        v = it == m.end() ? 0.f : (float)it->second;
-    }
+    for (int v : t) label.push_back((float)v);
+    // y -> index of its value among the labels; a label that is not an integer maps to 0
+    std::vector<std::thread> th;
+    for (int k = 0; k < nt; ++k)
+        th.emplace_back([&, k] {
+            for (size_t i = n * k / nt; i < n * (k + 1) / nt; ++i) {
+                const float v = y[i];
+                auto it = std::lower_bound(label.begin(), label.end(), v);
+                y[i] = (it != label.end() && *it == v) ? (float)(it - label.begin()) : 0.f;
+            }
+        });
+    for (auto &x : th) x.join();
 }
 
 // src/thundergbm/dataset.cpp:71-81
