@@ -194,6 +194,9 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()      # started before the warm-up so that the tool is already printing when timing starts
+        t_wait = time.time()
+        while not sampler.rows and time.time() - t_wait < 3.0:
+            time.sleep(0.01)
     b.boost(w)
     b.sync()
     b.set_profile(True)  # per-kernel CUDA events from here on: warm-up launches stay out of the profile

@@ -377,6 +377,8 @@ void Booster::init(const DataSet &ds) {
     m.hist_smem = 2 * 256 * 32 * 4 + 2 * 256 * 32 * 8;  // int32 accumulators + int64 totals, both [2][256 bins][32 features]
     TGBM_CUDA(cudaFuncSetAttribute(k_hist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
+    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
     if (sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
@@ -494,7 +496,9 @@ void BoosterImpl::build_tree(int round, int k) {
                                                       hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p);
             k_best_apply<<<nl, 32, 0, stream>>>(level, F, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 0);
         }
-        // -- move the rows
+        // -- move the rows (not after the last level: the finished tree is applied by walking it, see k_predict_walk)
+        launches += 3;
+        if (level == depth - 1) break;
         TimedEvent pv{};
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
         if (sparse)
@@ -510,11 +514,22 @@ void BoosterImpl::build_tree(int round, int k) {
                                                                idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p, node_done_base.p,
                                                                rec_idx[nxt].p, rec_gh[nxt].p, done_idx.p, done_nid.p);
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
-        launches += 6;
+        launches += 3;
     }
     k_prune<<<1, 1024, sizeof(TreeNode) * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, depth, p.gamma);
-    if (N) k_predict_update<<<ceil_div(N, 256), 256, 0, stream>>>(nodes.p, done_idx.p, done_nid.p, N, p.learning_rate, ypred.p + (size_t)k * N,
-                                                                  p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr);
+    if (N) {
+        const int in_smem = sizeof(WalkNode) * (size_t)n_nodes <= 160 * 1024;
+        const size_t walk_smem = in_smem ? sizeof(WalkNode) * (size_t)n_nodes : 0;
+        float *yp = ypred.p + (size_t)k * N;
+        int *nid_out = p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr;
+        const int walk_ctas = std::min(ceil_div(N, 256), num_sms * 8);
+        if (sparse)
+            k_predict_walk<true><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, nullptr, Fpad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, N,
+                                                                        p.learning_rate, yp, nid_out);
+        else
+            k_predict_walk<false><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
+                                                                         p.learning_rate, yp, nid_out);
+    }
     launches += 2;
     TGBM_CUDA(cudaMemcpyAsync(model.p + (size_t)tree_index * n_nodes, nodes.p, sizeof(TreeNode) * n_nodes, cudaMemcpyDeviceToDevice, stream));
 }

@@ -360,29 +360,29 @@ __device__ inline void hist_plan(int level, const int *__restrict__ seg_begin, c
     }
 }
 
-// Permute the 32 bin bytes of a row so that byte j of the register array is the bin of feature (j XOR lane):
-// at step j the 32 lanes of a warp then address 32 different features.  Lane bits 0-1 permute the bytes inside
-// every word (one PRMT each), bits 2-4 exchange whole words.
-__device__ __forceinline__ void xor_permute_row(uint32_t (&w)[8], int lane) {
-    const uint32_t sel = (lane & 2) ? ((lane & 1) ? 0x0123u : 0x1032u) : ((lane & 1) ? 0x2301u : 0x3210u);
+// Permute the 16 bin bytes of a half row so that byte j of the register array is the bin of slot (j XOR key),
+// key = 0..15: at step j the 16 lane pairs of a warp then address 16 different slots of either half.  Key bits 0-1
+// permute the bytes inside every word (one PRMT each), bits 2-3 exchange whole words.
+__device__ __forceinline__ void xor_permute_half(uint32_t (&w)[4], int key) {
+    const uint32_t sel = (key & 2) ? ((key & 1) ? 0x0123u : 0x1032u) : ((key & 1) ? 0x2301u : 0x3210u);
 #pragma unroll
-    for (int i = 0; i < 8; ++i) w[i] = __byte_perm(w[i], 0u, sel);
-    const int hi = lane >> 2;
+    for (int i = 0; i < 4; ++i) w[i] = __byte_perm(w[i], 0u, sel);
+    const int hi = key >> 2;
 #pragma unroll
-    for (int s = 1; s <= 4; s <<= 1) {
-        uint32_t t[8];
+    for (int s = 1; s <= 2; s <<= 1) {
+        uint32_t t[4];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t[i] = (hi & s) ? w[i ^ s] : w[i];
+        for (int i = 0; i < 4; ++i) t[i] = (hi & s) ? w[i ^ s] : w[i];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w[i] = t[i];
+        for (int i = 0; i < 4; ++i) w[i] = t[i];
     }
 }
 
 // Histogram build of one level (root: hist_tree_builder_single.cu:203-216, deeper levels: :485-505).
 // Persistent CTAs, one per SM; grid = (ctas, feature groups of 32).  Each CTA owns a contiguous range of
-// 1024-row tiles of the level's work list.  One lane = one row; the shared-memory accumulators are laid out
-// [bin][32 features] so that the bank is the feature index: lane l handles feature j^l at step j, so every
-// shared atomic of a warp hits 32 different banks.  Accumulators are int32.  Before they could overflow
+// 1024-row tiles of the level's work list.  A lane holds one 16-feature half of two rows; the shared-memory
+// accumulators are laid out [bin][32 features] so that the bank is the feature index, and at step j the 32 lanes
+// of a warp handle 32 different features, so every shared atomic of a warp hits 32 different banks.  Accumulators are int32.  Before they could overflow
 // (`window_rows` rows of at most 2^quant_bits each) they are drained into int64 totals, also in shared
 // memory; the totals go to the node's int64 histogram in global memory when the CTA moves on to another
 // node and at the end.
@@ -402,7 +402,6 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
     const int nf = min(32, F - f0);
     const int bin_lo = cut_ptr[f0], bin_hi = cut_ptr[f0 + nf];
     const int lane = threadIdx.x & 31;
-    const uint32_t lane4 = 4u * lane;
     const int total = ctl->n_hist_tiles, nwork = ctl->n_hist_work;
     const int per = (total + gridDim.x - 1) / gridDim.x;
     const int t_begin = min(total, (int)blockIdx.x * per), t_end = min(total, t_begin + per);
@@ -432,14 +431,21 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
         __syncthreads();
     };
 
+    // Two lanes share a row: lane l loads the 16-byte half (l & 1) of the rows at tile positions
+    // warp*32 + (l >> 1) ("A") and 16 further on ("B").  One load instruction of a warp therefore touches 16 rows
+    // (16 sectors) instead of 32 half-used ones, which halves the L1 wavefronts the gathered rows cost.
+    const int qa = (threadIdx.x & ~31) | (lane >> 1), qb = qa + 16;
+    const uint32_t laneoff = ((uint32_t)(lane & 1) << 6) | ((uint32_t)(lane >> 1) << 2);  // 4 * (16*half + key)
     // Software pipeline over tiles: while tile t is accumulated, the bin rows of tile t+1 are in flight and the
     // row index of tile t+2 is being fetched, so that no load waits for another inside an iteration.
-    // locate(): record position of this thread in tile t; w is a cursor over the work list that only moves forward
-    auto locate = [&](int t, int &w) -> long long {
-        if (t >= t_end) return -1;
+    // locate(): record position of tile slot q in tile t; w is a cursor over the work list that only moves forward
+    auto advance = [&](int t, int &w) {
         while (w + 1 < nwork && t >= tile_base[w + 1]) ++w;
+    };
+    auto locate = [&](int t, int w, int q) -> long long {
+        if (t >= t_end) return -1;
         const HistWork it = work[w];
-        const long long p = (long long)(t - tile_base[w]) * HIST_THREADS + threadIdx.x;
+        const long long p = (long long)(t - tile_base[w]) * HIST_THREADS + q;
         return p < it.count ? it.begin + p : -1;
     };
     int w0 = 0;
@@ -451,40 +457,41 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
         }
         w0 = lo;
     }
-    // stage 2 (tile t+2): position + row id; stage 1 (tile t+1): bin row + gradients; stage 0: being accumulated
+    // stage 2 (tile t+2): positions + row ids; stage 1 (tile t+1): bin half-rows + gradients; stage 0: being accumulated
     int w_cur = w0, w1 = w0, w2 = w0;
-    long long p1 = locate(t_begin, w1);
-    int r1 = p1 >= 0 ? (GATHER ? rec_idx[p1] : (int)p1) : 0;
+    advance(t_begin, w1);
+    long long p1a = locate(t_begin, w1, qa), p1b = locate(t_begin, w1, qb);
+    int r1a = p1a >= 0 ? (GATHER ? rec_idx[p1a] : (int)p1a) : 0;
+    int r1b = p1b >= 0 ? (GATHER ? rec_idx[p1b] : (int)p1b) : 0;
     w2 = w1;
-    long long p2 = locate(t_begin + 1, w2);
-    int r2 = p2 >= 0 ? (GATHER ? rec_idx[p2] : (int)p2) : 0;
+    if (t_begin + 1 < t_end) advance(t_begin + 1, w2);
+    long long p2a = locate(t_begin + 1, w2, qa), p2b = locate(t_begin + 1, w2, qb);
+    int r2a = p2a >= 0 ? (GATHER ? rec_idx[p2a] : (int)p2a) : 0;
+    int r2b = p2b >= 0 ? (GATHER ? rec_idx[p2b] : (int)p2b) : 0;
+    const size_t half_off = (size_t)f0 + 16u * (lane & 1);
     uint4 na = make_uint4(0, 0, 0, 0), nb = na;
-    int2 nv = make_int2(0, 0);
-    if (p1 >= 0) {
-        const uint4 *src = reinterpret_cast<const uint4 *>(bins + (size_t)r1 * Fpad + f0);
-        na = src[0]; nb = src[1];
-        nv = rec_gh[p1];
-    }
-    bool nok = p1 >= 0;
+    int2 nva = make_int2(0, 0), nvb = nva;
+    if (p1a >= 0) { na = *reinterpret_cast<const uint4 *>(bins + (size_t)r1a * Fpad + half_off); nva = rec_gh[p1a]; }
+    if (p1b >= 0) { nb = *reinterpret_cast<const uint4 *>(bins + (size_t)r1b * Fpad + half_off); nvb = rec_gh[p1b]; }
+    bool noka = p1a >= 0, nokb = p1b >= 0;
     int w_of_next = w1;
     int slab_cur = work[w_cur].slab;
     int since = 0;
     for (int t = t_begin; t < t_end; ++t) {
         const uint4 a = na, b = nb;
-        const int2 v = nv;
-        const bool ok = nok;
+        const int2 va = nva, vb = nvb;
+        const bool oka = noka, okb = nokb;
         const int w_this = w_of_next;
-        // tile t+1: its row id arrived during the previous iteration
-        nok = p2 >= 0;
+        // tile t+1: its row ids arrived during the previous iteration
+        noka = p2a >= 0; nokb = p2b >= 0;
         w_of_next = w2;
-        if (nok) {
-            const uint4 *src = reinterpret_cast<const uint4 *>(bins + (size_t)r2 * Fpad + f0);
-            na = src[0]; nb = src[1];
-            nv = rec_gh[p2];
-        }
-        // tile t+2: position and row id
-        p2 = locate(t + 2, w2);
-        r2 = p2 >= 0 ? (GATHER ? rec_idx[p2] : (int)p2) : 0;
+        if (noka) { na = *reinterpret_cast<const uint4 *>(bins + (size_t)r2a * Fpad + half_off); nva = rec_gh[p2a]; }
+        if (nokb) { nb = *reinterpret_cast<const uint4 *>(bins + (size_t)r2b * Fpad + half_off); nvb = rec_gh[p2b]; }
+        // tile t+2: positions and row ids
+        if (t + 2 < t_end) advance(t + 2, w2);
+        p2a = locate(t + 2, w2, qa); p2b = locate(t + 2, w2, qb);
+        r2a = p2a >= 0 ? (GATHER ? rec_idx[p2a] : (int)p2a) : 0;
+        r2b = p2b >= 0 ? (GATHER ? rec_idx[p2b] : (int)p2b) : 0;
         if (w_this != w_cur) {  // the tile belongs to the next node: hand the finished one over
             flush(slab_cur);
             w_cur = w_this;
@@ -495,21 +502,34 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
             since = 0;
         }
         since += HIST_THREADS;
-        if (ok) {
-            uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            xor_permute_row(w, lane);
-            // Step j adds the row to (bin of feature j^lane, feature j^lane).  Byte offset of the accumulator:
-            // bin * 128 | feature * 4 -- the bin field comes straight out of the packed word with one shift and
-            // one mask.  No test for missing values: bin 255 (missing, and the padding columns beyond F) lands in
-            // row 255 of the table, which no feature ever reads back.
-            char *const gbase = reinterpret_cast<char *>(hg);
+        // Step j adds a row to (bin of feature 16*half + (j ^ key), that feature), key = lane >> 1: the 32 lanes of a
+        // warp address 32 different features = 32 different banks.  Byte offset of the accumulator:
+        // bin * 128 | feature * 4 -- the bin field comes straight out of the packed word with one shift and one
+        // mask.  No test for missing values: bin 255 (missing, and the padding columns beyond F) lands in row 255
+        // of the table, which no feature ever reads back.
+        char *const gbase = reinterpret_cast<char *>(hg);
+        if (oka) {
+            uint32_t w[4] = {a.x, a.y, a.z, a.w};
+            xor_permute_half(w, lane >> 1);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
+            for (int j = 0; j < 16; ++j) {
                 const uint32_t word = w[j >> 2];
                 const uint32_t binoff = ((j & 3) == 0 ? (word << 7) : (word >> (8 * (j & 3) - 7))) & 0x7f80u;
-                const uint32_t off = binoff | (lane4 ^ (4u * j));
-                atomicAdd(reinterpret_cast<int *>(gbase + off), v.x);
-                atomicAdd(reinterpret_cast<int *>(gbase + off + 256 * 32 * 4), v.y);
+                const uint32_t off = binoff | (laneoff ^ (4u * j));
+                atomicAdd(reinterpret_cast<int *>(gbase + off), va.x);
+                atomicAdd(reinterpret_cast<int *>(gbase + off + 256 * 32 * 4), va.y);
+            }
+        }
+        if (okb) {
+            uint32_t w[4] = {b.x, b.y, b.z, b.w};
+            xor_permute_half(w, lane >> 1);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t word = w[j >> 2];
+                const uint32_t binoff = ((j & 3) == 0 ? (word << 7) : (word >> (8 * (j & 3) - 7))) & 0x7f80u;
+                const uint32_t off = binoff | (laneoff ^ (4u * j));
+                atomicAdd(reinterpret_cast<int *>(gbase + off), vb.x);
+                atomicAdd(reinterpret_cast<int *>(gbase + off + 256 * 32 * 4), vb.y);
             }
         }
     }
@@ -1144,17 +1164,68 @@ k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma) {
 }
 
 // TreeBuilder::predict_in_training (src/thundergbm/builder/tree_builder.cu:62-74); nvcc contracts the
-// reference's `y += lr * w` into one fused multiply-add, written out here
-static __global__ void k_predict_update(const TreeNode *__restrict__ nodes, const int *__restrict__ done_idx,
-                                 const int *__restrict__ done_nid, int n, float lr, float *__restrict__ yp,
-                                 int *__restrict__ nid_out) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n) return;
-    const int r = done_idx[i];
-    int nid = done_nid[i];
-    if (nid_out) nid_out[r] = nid;
-    while (nid != -1 && nodes[nid].is_pruned) nid = nodes[nid].parent_index;
-    yp[r] = __fmaf_rn(lr, nodes[nid].base_weight, yp[r]);
+// reference's `y += lr * w` into one fused multiply-add, written out here.
+// The reference looks the row's node up in ins2node_id; here every row walks the finished tree on its own bin
+// ids instead (the same comparisons the partition made, so the same node), in row order: the bin rows and the
+// scores are streamed once, nothing is scattered, and the last level needs no partition at all.
+// A node was split iff its children are valid; pruning only marks nodes, so the walk goes on below a pruned
+// parent to find the node the reference's table would hold (`nid_out`) while the score takes the weight of the
+// deepest node on the path that survived pruning.
+struct WalkNode { int x, flags, end; float weight; };  // x: split feature (CSR layout: first global bin of it, `end` one past its last)
+
+template <bool SPARSE>
+__device__ __forceinline__ WalkNode walk_node(const TreeNode *__restrict__ nodes, const int *__restrict__ cut_ptr, int i) {
+    const TreeNode nd = nodes[i];
+    const bool split = nd.is_valid && nd.lch_index >= 0 && nodes[nd.lch_index].is_valid;
+    const int f = split ? nd.split_feature_id : 0;
+    WalkNode w;
+    w.x = SPARSE ? cut_ptr[f] : f;
+    w.end = SPARSE ? cut_ptr[f + 1] : 0;
+    w.flags = (int)nd.split_bid | (nd.default_right ? 0x100 : 0) | (split ? 0x200 : 0) | (nd.is_pruned ? 0x400 : 0);
+    w.weight = nd.base_weight;
+    return w;
+}
+
+// `table_in_smem` = 0 for trees too large for shared memory (depth 13 and 14): the nodes are then decoded from global
+// memory at every step.
+template <bool SPARSE>
+static __global__ void __launch_bounds__(256)
+k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_smem, const unsigned char *__restrict__ bins, int Fpad,
+               const int *__restrict__ sp_row_ptr, const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr,
+               int n, float lr, float *__restrict__ yp, int *__restrict__ nid_out) {
+    extern __shared__ __align__(16) unsigned char walk_sm[];
+    WalkNode *wn = reinterpret_cast<WalkNode *>(walk_sm);
+    if (table_in_smem) {
+        for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) wn[i] = walk_node<SPARSE>(nodes, cut_ptr, i);
+        __syncthreads();
+    }
+    for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
+        int lo0 = 0, hi0 = 0;
+        if (SPARSE) { lo0 = sp_row_ptr[r]; hi0 = sp_row_ptr[r + 1]; }
+        const unsigned char *row = SPARSE ? nullptr : bins + (size_t)r * Fpad;
+        int nid = 0;
+        float weight = 0.f;
+        for (;;) {
+            const WalkNode w = table_in_smem ? wn[nid] : walk_node<SPARSE>(nodes, cut_ptr, nid);
+            if (!(w.flags & 0x400)) weight = w.weight;
+            if (!(w.flags & 0x200)) break;
+            int b = MISSING_BIN;
+            if (SPARSE) {
+                int lo = lo0, hi = hi0;
+                while (lo < hi) {  // bin ids ascend inside a row
+                    const int mid = lo + (hi - lo) / 2, v = sp_bin[mid];
+                    if (v >= w.x && v < w.end) { b = v - w.x; break; }
+                    if (v < w.x) lo = mid + 1; else hi = mid;
+                }
+            } else {
+                b = row[w.x];
+            }
+            const bool left = (b == MISSING_BIN) ? !(w.flags & 0x100) : (b < (w.flags & 0xff));
+            nid = 2 * nid + (left ? 1 : 2);
+        }
+        if (nid_out) nid_out[r] = nid;
+        yp[r] = __fmaf_rn(lr, weight, yp[r]);
+    }
 }
 
 // ------------------------------------------------------------------ metrics
