@@ -53,12 +53,12 @@ struct BoosterImpl {
     DevBuf<int> rec_idx[2];
     DevBuf<int2> rec_gh[2];
     DevBuf<int> seg_begin[2], seg_cnt[2], gcnt;
-    DevBuf<int> done_idx, done_nid, nid_keep;
+    DevBuf<int> nid_keep;
     DevBuf<long long> hist_full, hist_built;
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     DevBuf<SplitRec> recs;
-    DevBuf<int> node_tile0[2], tile_left, node_done_base;
+    DevBuf<int> node_tile0[2], tile_left;
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
     DevBuf<double> metric_partial, metric_sum;
@@ -356,7 +356,6 @@ void Booster::init(const DataSet &ds) {
     }
     m.gcnt.alloc((size_t)1 << depth);
     m.gcnt.zero(m.stream);
-    m.done_idx.alloc(n1); m.done_nid.alloc(n1);
     if (p.keep_nid) m.nid_keep.alloc(n1 * K * std::max(p.n_trees, 1));
     const size_t B1 = std::max(m.B, 1);
     m.hist_full.alloc((((size_t)1 << depth) - 1) * B1 * 2);
@@ -367,7 +366,6 @@ void Booster::init(const DataSet &ds) {
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
     m.tile_left.alloc(m.max_tiles);
     m.node_tile0[0].alloc(((size_t)1 << depth) + 1); m.node_tile0[1].alloc(((size_t)1 << depth) + 1);
-    m.node_done_base.alloc((size_t)1 << depth);
     m.bits.alloc((size_t)m.max_tiles * (PART_TILE / 32));
     m.ctl.alloc(1);
     m.ctl.zero(m.stream);
@@ -507,12 +505,12 @@ void BoosterImpl::build_tree(int round, int k) {
         else
             k_part_count<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
                                                                         idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p);
-        k_part_scan<<<1, 1024, 0, stream>>>(level, depth, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
-                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, node_done_base.p, ctl.p,
+        k_part_scan<<<1, 1024, 0, stream>>>(level, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
+                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p,
                                             by_hessian, built_right.p, hist_work.p, hist_tile_base.p, node_tile0[nxt].p);
-        k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, depth, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                               idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p, node_done_base.p,
-                                                               rec_idx[nxt].p, rec_gh[nxt].p, done_idx.p, done_nid.p);
+        k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
+                                                               idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p,
+                                                               rec_idx[nxt].p, rec_gh[nxt].p);
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
         launches += 3;
     }

@@ -29,7 +29,6 @@ struct HistWork {  // one histogram to build at a level
 };
 
 struct TreeCtl {  // device-side scalars of the tree being built
-    int done_count;
     int n_hist_tiles;
     int n_hist_work;
     int n_part_tiles[2];  // by level parity: level l+1 is planned while level l is still being scattered
@@ -264,7 +263,7 @@ static __global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, co
         t.is_valid = 1;
         t.base_weight = __fdiv_rn(-t.sum_g, __fadd_rn(t.sum_h, lambda));
         seg_begin[0] = 0; seg_cnt[0] = n_rows; gcnt[0] = n_rows;
-        ctl->done_count = 0; ctl->n_records = n_rows;
+        ctl->n_records = n_rows;
     }
     nodes[i] = t;
 }
@@ -1001,17 +1000,16 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
     }
 }
 
-// Prefix of the left counts over the tiles of every node, child segment table of the next level,
-// done-list offsets of finished nodes.  One block of 1024 threads.
+// Prefix of the left counts over the tiles of every node, child segment table and work lists of the next level.
+// Rows of nodes that stopped splitting simply drop out of the record lists.  One block of 1024 threads.
 static __global__ void __launch_bounds__(1024)
-k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_cnt,
+k_part_scan(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_cnt,
             const int *__restrict__ node_tile0, int *__restrict__ tile_left, int *__restrict__ next_begin,
-            int *__restrict__ next_cnt, int *__restrict__ gcnt, int *__restrict__ node_done_base, TreeCtl *__restrict__ ctl,
+            int *__restrict__ next_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl,
             int by_hessian, int *__restrict__ built_right, HistWork *__restrict__ work, int *__restrict__ hist_tile_base,
             int *__restrict__ next_node_tile0) {
     __shared__ int scratch[33];
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
-    const bool last = level == depth - 1;
     // tile_left becomes the inclusive prefix over all tiles
     block_scan_excl(nt, [&](int i) { return tile_left[i]; }, [&](int i, int excl) { tile_left[i] += excl; }, scratch);
     auto splittable = [&](int n) { const TreeNode &nd = nodes[nl - 1 + n]; return nd.is_valid && !nd.is_leaf; };
@@ -1027,19 +1025,12 @@ k_part_scan(int level, int depth, const TreeNode *__restrict__ nodes, const int 
     }
     __syncthreads();
     const int alive = block_scan_excl(2 * nl, [&](int c) { return next_cnt[c]; }, [&](int c, int pos) { next_begin[c] = pos; }, scratch);
-    const int done0 = ctl->done_count;
-    const int fin = block_scan_excl(nl, [&](int n) { return (!splittable(n) || last) ? seg_cnt[n] : 0; },
-                                    [&](int n, int pos) { node_done_base[n] = done0 + pos; }, scratch);
-    if (threadIdx.x == 0) {
-        ctl->done_count = done0 + fin;
-        ctl->n_records = last ? 0 : alive;
-    }
-    if (!last) {  // work lists of the next level, so that it needs no planning launches of its own
-        __syncthreads();
-        hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl);
-        __syncthreads();
-        part_plan(level + 1, next_cnt, next_node_tile0, ctl);
-    }
+    if (threadIdx.x == 0) ctl->n_records = alive;
+    // work lists of the next level, so that it needs no planning launches of its own
+    __syncthreads();
+    hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl);
+    __syncthreads();
+    part_plan(level + 1, next_cnt, next_node_tile0, ctl);
 }
 
 // work lists of level 0 (the whole data set in the root)
@@ -1052,40 +1043,29 @@ k_plan_root(const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt, 
     part_plan(0, seg_cnt, node_tile0, ctl);
 }
 
-// Stable scatter of the records into the child segments (or, for nodes that stopped splitting and
-// at the last level, into the done list with the id of the node the row ended in).
+// Stable scatter of the records into the child segments; records of nodes that stopped splitting are dropped.
 static __global__ void __launch_bounds__(PART_THREADS)
-k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
+k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin,
                const int *__restrict__ seg_cnt, const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl,
                const int *__restrict__ rec_idx, const int2 *__restrict__ rec_gh, const unsigned *__restrict__ bits,
-               const int *__restrict__ tile_left, const int *__restrict__ next_begin, const int *__restrict__ node_done_base,
-               int *__restrict__ out_idx, int2 *__restrict__ out_gh, int *__restrict__ done_idx, int *__restrict__ done_nid) {
+               const int *__restrict__ tile_left, const int *__restrict__ next_begin,
+               int *__restrict__ out_idx, int2 *__restrict__ out_gh) {
     constexpr int WORDS = PART_TILE / 32;  // 128
     __shared__ int wpre[WORDS];
     __shared__ int wtot[4];
     __shared__ int sh_n;
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
-    const bool last = level == depth - 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = blockIdx.x; t < nt; t += gridDim.x) {
         __syncthreads();
         if (threadIdx.x == 0) sh_n = tile_owner(node_tile0, nl, t);
         __syncthreads();
         const int n = sh_n;
-        const int nid = nl - 1 + n;
-        const TreeNode nd = nodes[nid];
+        const TreeNode nd = nodes[nl - 1 + n];
         const int b = seg_begin[n], end = b + seg_cnt[n];
         const int t0 = node_tile0[n];
         const int p0 = b + (t - t0) * PART_TILE;
-        if (!(nd.is_valid && !nd.is_leaf)) {  // finished node: its rows go to the done list
-            const int base = node_done_base[n];
-#pragma unroll
-            for (int j = 0; j < PART_RPT; ++j) {
-                const int p = p0 + j * PART_THREADS + threadIdx.x;
-                if (p < end) { done_idx[base + (p - b)] = rec_idx ? rec_idx[p] : p; done_nid[base + (p - b)] = nid; }
-            }
-            continue;
-        }
+        if (!(nd.is_valid && !nd.is_leaf)) continue;  // finished node
         // loads first, so that they overlap with the rank computation
         int r[PART_RPT];
         int2 g[PART_RPT];
@@ -1094,7 +1074,7 @@ k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const i
         for (int j = 0; j < PART_RPT; ++j) {
             const int p = p0 + j * PART_THREADS + threadIdx.x;
             r[j] = p < end ? (rec_idx ? rec_idx[p] : p) : -1;
-            if (!last && p < end) g[j] = rec_gh[p];
+            if (p < end) g[j] = rec_gh[p];
             m[j] = bits[(size_t)t * WORDS + j * 32 + warp];
         }
         // exclusive prefix of the left counts over the tile's 128 ballot words (record order = word order)
@@ -1107,10 +1087,8 @@ k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const i
             if (lane == 31) wtot[warp] = v;
         }
         __syncthreads();
-        const int t1 = node_tile0[n + 1];
         const int node_l0 = t0 > 0 ? tile_left[t0 - 1] : 0;
         const int lefts_before_tile = (t > 0 ? tile_left[t - 1] : 0) - node_l0;
-        const int n_left = tile_left[t1 - 1] - node_l0;
 #pragma unroll
         for (int j = 0; j < PART_RPT; ++j) {
             if (r[j] < 0) continue;
@@ -1121,15 +1099,9 @@ k_part_scatter(int level, int depth, const TreeNode *__restrict__ nodes, const i
             const bool left = (m[j] >> lane) & 1u;
             const int lefts_before = lefts_before_tile + pre + __popc(m[j] & ((1u << lane) - 1u));
             const int rank = left ? lefts_before : (p - b) - lefts_before;
-            if (last) {
-                const int d = node_done_base[n] + (left ? rank : n_left + rank);
-                done_idx[d] = r[j];
-                done_nid[d] = left ? nd.lch_index : nd.rch_index;
-            } else {
-                const int d = (left ? next_begin[2 * n] : next_begin[2 * n + 1]) + rank;
-                out_idx[d] = r[j];
-                out_gh[d] = g[j];
-            }
+            const int d = (left ? next_begin[2 * n] : next_begin[2 * n + 1]) + rank;
+            out_idx[d] = r[j];
+            out_gh[d] = g[j];
         }
     }
 }
