@@ -375,8 +375,9 @@ void Booster::init(const DataSet &ds) {
     m.hist_smem = 2 * 256 * 32 * 4 + 2 * 256 * 32 * 8;  // int32 accumulators + int64 totals, both [2][256 bins][32 features]
     TGBM_CUDA(cudaFuncSetAttribute(k_hist<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, m.hist_smem));
-    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+    TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
     if (sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
@@ -516,17 +517,21 @@ void BoosterImpl::build_tree(int round, int k) {
     }
     k_prune<<<1, 1024, sizeof(TreeNode) * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, depth, p.gamma);
     if (N) {
-        const int in_smem = sizeof(WalkNode) * (size_t)n_nodes <= 160 * 1024;
-        const size_t walk_smem = in_smem ? sizeof(WalkNode) * (size_t)n_nodes : 0;
+        const size_t per_node = sizeof(WalkNode) + (sparse ? sizeof(WalkSpan) : 0);
+        const int in_smem = per_node * (size_t)n_nodes <= 160 * 1024;
+        const size_t walk_smem = in_smem ? per_node * (size_t)n_nodes : 0;
         float *yp = ypred.p + (size_t)k * N;
         int *nid_out = p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr;
         const int walk_ctas = std::min(ceil_div(N, 256), num_sms * 8);
         if (sparse)
-            k_predict_walk<true><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, nullptr, Fpad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, N,
-                                                                        p.learning_rate, yp, nid_out);
+            k_predict_walk<2><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, nullptr, Fpad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, N,
+                                                                     p.learning_rate, yp, nid_out);
+        else if (Fpad == 32)
+            k_predict_walk<0><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
+                                                                     p.learning_rate, yp, nid_out);
         else
-            k_predict_walk<false><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
-                                                                         p.learning_rate, yp, nid_out);
+            k_predict_walk<1><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
+                                                                     p.learning_rate, yp, nid_out);
     }
     launches += 2;
     TGBM_CUDA(cudaMemcpyAsync(model.p + (size_t)tree_index * n_nodes, nodes.p, sizeof(TreeNode) * n_nodes, cudaMemcpyDeviceToDevice, stream));

@@ -1143,56 +1143,81 @@ k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma) {
 // A node was split iff its children are valid; pruning only marks nodes, so the walk goes on below a pruned
 // parent to find the node the reference's table would hold (`nid_out`) while the score takes the weight of the
 // deepest node on the path that survived pruning.
-struct WalkNode { int x, flags, end; float weight; };  // x: split feature (CSR layout: first global bin of it, `end` one past its last)
+// Walk table entry: flags = split bin (bits 0-7) | default right (8) | was split (9) | pruned (10) | feature << 16
+struct WalkNode { int flags; float weight; };
+struct WalkSpan { int c0, c1; };  // CSR layout: global bins [c0, c1) of the split feature
 
-template <bool SPARSE>
-__device__ __forceinline__ WalkNode walk_node(const TreeNode *__restrict__ nodes, const int *__restrict__ cut_ptr, int i) {
+__device__ __forceinline__ WalkNode walk_node(const TreeNode *__restrict__ nodes, int i) {
     const TreeNode nd = nodes[i];
     const bool split = nd.is_valid && nd.lch_index >= 0 && nodes[nd.lch_index].is_valid;
-    const int f = split ? nd.split_feature_id : 0;
     WalkNode w;
-    w.x = SPARSE ? cut_ptr[f] : f;
-    w.end = SPARSE ? cut_ptr[f + 1] : 0;
-    w.flags = (int)nd.split_bid | (nd.default_right ? 0x100 : 0) | (split ? 0x200 : 0) | (nd.is_pruned ? 0x400 : 0);
+    w.flags = (int)nd.split_bid | (nd.default_right ? 0x100 : 0) | (split ? 0x200 : 0) | (nd.is_pruned ? 0x400 : 0) |
+              (split ? (int)((unsigned)nd.split_feature_id << 16) : 0);
     w.weight = nd.base_weight;
     return w;
 }
+__device__ __forceinline__ WalkSpan walk_span(const TreeNode *__restrict__ nodes, const int *__restrict__ cut_ptr, int i) {
+    const TreeNode nd = nodes[i];
+    const bool split = nd.is_valid && nd.lch_index >= 0 && nodes[nd.lch_index].is_valid;
+    const int f = split ? nd.split_feature_id : 0;
+    return WalkSpan{cut_ptr[f], cut_ptr[f + 1]};
+}
 
+// LAYOUT 0: dense rows of exactly 32 bytes, held in registers (two 16-byte loads per row; the byte of the split
+// feature is picked with selects, so that a step costs no memory access); 1: dense rows of any width, one byte load
+// per step; 2: CSR of global bin ids, binary search per step (the feature id does not fit the packed flags there).
 // `table_in_smem` = 0 for trees too large for shared memory (depth 13 and 14): the nodes are then decoded from global
 // memory at every step.
-template <bool SPARSE>
+template <int LAYOUT>
 static __global__ void __launch_bounds__(256)
 k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_smem, const unsigned char *__restrict__ bins, int Fpad,
                const int *__restrict__ sp_row_ptr, const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr,
                int n, float lr, float *__restrict__ yp, int *__restrict__ nid_out) {
     extern __shared__ __align__(16) unsigned char walk_sm[];
     WalkNode *wn = reinterpret_cast<WalkNode *>(walk_sm);
+    WalkSpan *ws = reinterpret_cast<WalkSpan *>(walk_sm + sizeof(WalkNode) * n_nodes);
     if (table_in_smem) {
-        for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) wn[i] = walk_node<SPARSE>(nodes, cut_ptr, i);
+        for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) {
+            wn[i] = walk_node(nodes, i);
+            if (LAYOUT == 2) ws[i] = walk_span(nodes, cut_ptr, i);
+        }
         __syncthreads();
     }
     for (int r = blockIdx.x * blockDim.x + threadIdx.x; r < n; r += gridDim.x * blockDim.x) {
         int lo0 = 0, hi0 = 0;
-        if (SPARSE) { lo0 = sp_row_ptr[r]; hi0 = sp_row_ptr[r + 1]; }
-        const unsigned char *row = SPARSE ? nullptr : bins + (size_t)r * Fpad;
+        uint32_t w[8];
+        const unsigned char *row = bins + (size_t)r * Fpad;
+        if (LAYOUT == 2) { lo0 = sp_row_ptr[r]; hi0 = sp_row_ptr[r + 1]; }
+        if (LAYOUT == 0) {
+            const uint4 a = reinterpret_cast<const uint4 *>(row)[0], b = reinterpret_cast<const uint4 *>(row)[1];
+            w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+        }
         int nid = 0;
         float weight = 0.f;
+#pragma unroll 1
         for (;;) {
-            const WalkNode w = table_in_smem ? wn[nid] : walk_node<SPARSE>(nodes, cut_ptr, nid);
-            if (!(w.flags & 0x400)) weight = w.weight;
-            if (!(w.flags & 0x200)) break;
+            const WalkNode wk = table_in_smem ? wn[nid] : walk_node(nodes, nid);
+            if (!(wk.flags & 0x400)) weight = wk.weight;
+            if (!(wk.flags & 0x200)) break;
             int b = MISSING_BIN;
-            if (SPARSE) {
+            if (LAYOUT == 2) {
+                const WalkSpan sp = table_in_smem ? ws[nid] : walk_span(nodes, cut_ptr, nid);
                 int lo = lo0, hi = hi0;
                 while (lo < hi) {  // bin ids ascend inside a row
                     const int mid = lo + (hi - lo) / 2, v = sp_bin[mid];
-                    if (v >= w.x && v < w.end) { b = v - w.x; break; }
-                    if (v < w.x) lo = mid + 1; else hi = mid;
+                    if (v >= sp.c0 && v < sp.c1) { b = v - sp.c0; break; }
+                    if (v < sp.c0) lo = mid + 1; else hi = mid;
                 }
+            } else if (LAYOUT == 1) {
+                b = row[(unsigned)wk.flags >> 16];
             } else {
-                b = row[w.x];
+                const unsigned f = (unsigned)wk.flags >> 16;
+                const uint32_t a0 = (f & 16) ? w[4] : w[0], a1 = (f & 16) ? w[5] : w[1], a2 = (f & 16) ? w[6] : w[2],
+                               a3 = (f & 16) ? w[7] : w[3];
+                const uint32_t b0 = (f & 8) ? a2 : a0, b1 = (f & 8) ? a3 : a1;
+                b = (((f & 4) ? b1 : b0) >> (8 * (f & 3))) & 0xffu;
             }
-            const bool left = (b == MISSING_BIN) ? !(w.flags & 0x100) : (b < (w.flags & 0xff));
+            const bool left = (b == MISSING_BIN) ? !(wk.flags & 0x100) : (b < (wk.flags & 0xff));
             nid = 2 * nid + (left ? 1 : 2);
         }
         if (nid_out) nid_out[r] = nid;
