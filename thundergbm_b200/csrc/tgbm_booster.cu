@@ -57,6 +57,8 @@ struct BoosterImpl {
     DevBuf<long long> hist_full, hist_built;
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
+    DevBuf<int> hist_cta_off;  // dense histogram kernel: tile sequence of every CTA
+    DevBuf<int4> hist_seq;
     DevBuf<SplitRec> recs;
     DevBuf<int> node_tile0[2], tile_left;
     DevBuf<unsigned> bits;
@@ -362,6 +364,8 @@ void Booster::init(const DataSet &ds) {
     m.hist_built.alloc(std::max<size_t>(1, (size_t)1 << std::max(0, depth - 2)) * B1 * 2);
     const int max_pairs = std::max(1, 1 << std::max(0, depth - 2));
     m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
+    m.hist_cta_off.alloc((size_t)m.num_sms + 1);
+    m.hist_seq.alloc((size_t)ceil_div(std::max(N, 1), HIST_THREADS) + max_pairs + 16);
     m.recs.alloc(((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
     m.tile_left.alloc(m.max_tiles);
@@ -444,13 +448,13 @@ void BoosterImpl::init_base_score() {
 void BoosterImpl::build_tree(int round, int k) {
     const int tree_index = round * K + k;
     const int2 *gq = ghq.p + (size_t)k * N;
+    const int hist_ctas = num_sms;
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
-                                        node_tile0[0].p, ctl.p);
+                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
-    const int hist_ctas = num_sms;
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * 2));
     for (int level = 0; level < depth; ++level) {
         const int cur = level & 1, nxt = cur ^ 1;
@@ -476,11 +480,11 @@ void BoosterImpl::build_tree(int round, int k) {
                 k_hist_sparse<true><<<sp_ctas, SPARSE_THREADS, sp_smem, stream>>>(sp_row_ptr.p, sp_bin.p, idx_in, gh_in, hist_work.p,
                                                                                   hist_tile_base.p, ctl.p, built, B);
         } else if (level == 0)
-            k_hist<false><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, nullptr, gh_in, hist_work.p, hist_tile_base.p,
-                                                                                   ctl.p, cut_ptr.p, cut_fid.p, built, B, window_rows);
+            k_hist<false><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, nullptr, gh_in, hist_cta_off.p, hist_seq.p,
+                                                                                   cut_ptr.p, cut_fid.p, built, B, window_rows);
         else
-            k_hist<true><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, idx_in, gh_in, hist_work.p, hist_tile_base.p,
-                                                                                  ctl.p, cut_ptr.p, cut_fid.p, built, B, window_rows);
+            k_hist<true><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, idx_in, gh_in, hist_cta_off.p, hist_seq.p,
+                                                                                  cut_ptr.p, cut_fid.p, built, B, window_rows);
         if (profile_on) { cudaEventRecord(ev.b, stream); events.push_back(ev); }
         if (comm && comm->active()) comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
         // -- split selection and tree update
@@ -508,7 +512,7 @@ void BoosterImpl::build_tree(int round, int k) {
                                                                         idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p);
         k_part_scan<<<1, 1024, 0, stream>>>(level, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
                                             seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p,
-                                            by_hessian, built_right.p, hist_work.p, hist_tile_base.p, node_tile0[nxt].p);
+                                            by_hessian, built_right.p, hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p);
         k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
                                                                idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p,
                                                                rec_idx[nxt].p, rec_gh[nxt].p);
