@@ -20,6 +20,8 @@ struct BoosterImpl {
     GBMParam p;
     const Comm *comm = nullptr;
     cudaStream_t stream = nullptr;
+    cudaStream_t stream2 = nullptr;          // side stream for planning kernels that run beside the scatter
+    cudaEvent_t ev_scan = nullptr, ev_plan = nullptr;
     int objective = REG_LINEAR;
     int N = 0, F = 0, Fpad = 0, G = 0, B = 0, K = 1, n_nodes = 0, depth = 0;
     long long N_global = 0;
@@ -74,6 +76,9 @@ struct BoosterImpl {
 
     ~BoosterImpl() {
         for (auto &e : events) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
+        if (ev_scan) cudaEventDestroy(ev_scan);
+        if (ev_plan) cudaEventDestroy(ev_plan);
+        if (stream2) cudaStreamDestroy(stream2);
         if (stream) cudaStreamDestroy(stream);
     }
 
@@ -284,6 +289,9 @@ void Booster::init(const DataSet &ds) {
     TGBM_CUDA(cudaGetDevice(&dev));
     TGBM_CUDA(cudaDeviceGetAttribute(&m.num_sms, cudaDevAttrMultiProcessorCount, dev));
     TGBM_CUDA(cudaStreamCreateWithFlags(&m.stream, cudaStreamNonBlocking));
+    TGBM_CUDA(cudaStreamCreateWithFlags(&m.stream2, cudaStreamNonBlocking));
+    TGBM_CUDA(cudaEventCreateWithFlags(&m.ev_scan, cudaEventDisableTiming));
+    TGBM_CUDA(cudaEventCreateWithFlags(&m.ev_plan, cudaEventDisableTiming));
     m.N = ds.n_rows;
     m.F = ds.n_features;
     m.depth = p.depth;
@@ -448,7 +456,7 @@ void BoosterImpl::init_base_score() {
 void BoosterImpl::build_tree(int round, int k) {
     const int tree_index = round * K + k;
     const int2 *gq = ghq.p + (size_t)k * N;
-    const int hist_ctas = num_sms;
+    const int hist_ctas = std::min(num_sms, HIST_MAX_CTAS);
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
@@ -511,13 +519,20 @@ void BoosterImpl::build_tree(int round, int k) {
             k_part_count<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
                                                                         idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p);
         k_part_scan<<<1, 1024, 0, stream>>>(level, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
-                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p,
-                                            by_hessian, built_right.p, hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p);
-        k_part_scatter<<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                               idx_in, gh_in, bits.p, tile_left.p, seg_begin[nxt].p,
-                                                               rec_idx[nxt].p, rec_gh[nxt].p);
+                                            seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p);
+        // the next level's plan runs beside the scatter: launched first so that it gets its SM slot, while the
+        // scatter leaves one of its 2 x SMs block slots free
+        TGBM_CUDA(cudaEventRecord(ev_scan, stream));
+        TGBM_CUDA(cudaStreamWaitEvent(stream2, ev_scan, 0));
+        k_plan_next<<<1, 1024, 0, stream2>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, nodes.p, ctl.p, by_hessian, built_right.p,
+                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p);
+        TGBM_CUDA(cudaEventRecord(ev_plan, stream2));
+        k_part_scatter<<<std::max(1, part_ctas - 1), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
+                                                                                node_tile0[cur].p, ctl.p, idx_in, gh_in, bits.p, tile_left.p,
+                                                                                seg_begin[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p);
+        TGBM_CUDA(cudaStreamWaitEvent(stream, ev_plan, 0));
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
-        launches += 3;
+        launches += 4;
     }
     k_prune<<<1, 1024, sizeof(TreeNode) * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, depth, p.gamma);
     if (N) {
@@ -590,7 +605,7 @@ HistProfile Booster::profile() {
     for (auto &e : m.events) {
         float ms = 0;
         cudaEventElapsedTime(&ms, e.a, e.b);
-        if (e.kind == 2) { r.partition_ms += ms; r.partition_launches += 3; }
+        if (e.kind == 2) { r.partition_ms += ms; r.partition_launches += 4; }
         else {
             r.hist_ms += ms; r.hist_launches += 1;
             if (e.kind == 0) { r.hist_root_ms += ms; r.hist_root_launches += 1; }

@@ -31,6 +31,7 @@ struct HistWork {  // one histogram to build at a level
 // Shares of the level's tiles per CTA of the dense histogram kernel.  More shares balance the CTAs better but widen the
 // window of rows the GPU works on at a time; 1 to 4 measure the same on 10.5 M rows, 16 is 10 % slower.
 constexpr int HIST_SHARES = 2;
+constexpr int HIST_MAX_CTAS = 256;  // grid.x limit of the dense histogram kernel (one CTA per SM)
 
 struct TreeCtl {  // device-side scalars of the tree being built
     int n_hist_tiles;
@@ -326,39 +327,58 @@ __device__ inline void hist_sequence(int nw, int tiles, HistWork *__restrict__ w
         work[w].vk = v0 | (k << 16);
     }
     __syncthreads();
-    // visit(c, f): calls f(item, tile) for the tiles of CTA c in its visiting order
-    auto visit = [&](int c, auto f) {
-        const int va = c * HIST_SHARES, vb = va + HIST_SHARES;  // the CTA's shares
-        // items with a share in [va, vb): first item whose last share is >= va ... first item whose first share is >= vb
+    // items with a share among the CTA's: first item whose last share is >= va ... first item whose first share is >= vb
+    auto items_of = [&](int c, int &ib, int &ie) {
+        const int va = c * HIST_SHARES, vb = va + HIST_SHARES;
         int lo = 0, hi = nw;
         while (lo < hi) {
             const int mid = (lo + hi) / 2, vk = work[mid].vk;
             if ((vk & 0xffff) + (vk >> 16) - 1 >= va) hi = mid; else lo = mid + 1;
         }
-        const int ib = lo;
+        ib = lo;
         hi = nw;
         while (lo < hi) {
             const int mid = (lo + hi) / 2;
             if ((work[mid].vk & 0xffff) >= vb) hi = mid; else lo = mid + 1;
         }
-        for (int w = ib; w < lo; ++w) {
-            const int vk = work[w].vk, v0 = vk & 0xffff, k = vk >> 16, T = tile_base[w + 1] - tile_base[w];
-            const int ra = max(va, v0) - v0, rb = min(vb, v0 + k) - v0;  // residues mod k that belong to the CTA
-            for (int t0 = 0; t0 < T; t0 += k)
-                for (int t = t0 + ra; t < min(t0 + rb, T); ++t) f(w, t);
-        }
+        ie = lo;
     };
+    // the CTA's part of item w: residues [ra, ra + width) mod k, `count` tiles
+    auto part_of = [&](int c, int w, int &k, int &ra, int &width) {
+        const int va = c * HIST_SHARES, vb = va + HIST_SHARES;
+        const int vk = work[w].vk, v0 = vk & 0xffff, T = tile_base[w + 1] - tile_base[w];
+        k = vk >> 16;
+        ra = max(va, v0) - v0;
+        width = min(vb, v0 + k) - v0 - ra;
+        return (T / k) * width + min(max(T % k - ra, 0), width);
+    };
+    __shared__ int sh_ib[HIST_MAX_CTAS], sh_ie[HIST_MAX_CTAS];  // the searches are chains of dependent loads: done once
     block_scan_excl(n_ctas,
-                    [&](int c) { int n = 0; visit(c, [&](int, int) { ++n; }); return n; },
+                    [&](int c) {
+                        int ib, ie, n = 0, k, ra, width;
+                        items_of(c, ib, ie);
+                        sh_ib[c] = ib; sh_ie[c] = ie;
+                        for (int w = ib; w < ie; ++w) n += part_of(c, w, k, ra, width);
+                        return n;
+                    },
                     [&](int c, int excl) { cta_off[c] = excl; }, scratch);
     if (threadIdx.x == 0) cta_off[n_ctas] = tiles;
     __syncthreads();
-    for (int c = threadIdx.x; c < n_ctas; c += 1024) {
+    // one warp writes the sequence of one CTA, 32 tiles at a time
+    const int lane = threadIdx.x & 31;
+    for (int c = threadIdx.x >> 5; c < n_ctas; c += 32) {
+        const int ib = sh_ib[c], ie = sh_ie[c];
         int pos = cta_off[c];
-        visit(c, [&](int w, int t) {
+        for (int w = ib; w < ie; ++w) {
+            int k, ra, width;
+            const int count = part_of(c, w, k, ra, width);
             const HistWork it = work[w];
-            seq[pos++] = make_int4(it.begin + t * HIST_THREADS, min(HIST_THREADS, it.count - t * HIST_THREADS), it.slab, 0);
-        });
+            for (int n = lane; n < count; n += 32) {
+                const int t = (n / width) * k + ra + n % width;
+                seq[pos + n] = make_int4(it.begin + t * HIST_THREADS, min(HIST_THREADS, it.count - t * HIST_THREADS), it.slab, 0);
+            }
+            pos += count;
+        }
     }
 }
 
@@ -1061,14 +1081,12 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
     }
 }
 
-// Prefix of the left counts over the tiles of every node, child segment table and work lists of the next level.
+// Prefix of the left counts over the tiles of every node and the child segment table of the next level.
 // Rows of nodes that stopped splitting simply drop out of the record lists.  One block of 1024 threads.
 static __global__ void __launch_bounds__(1024)
 k_part_scan(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_cnt,
             const int *__restrict__ node_tile0, int *__restrict__ tile_left, int *__restrict__ next_begin,
-            int *__restrict__ next_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl,
-            int by_hessian, int *__restrict__ built_right, HistWork *__restrict__ work, int *__restrict__ hist_tile_base,
-            int *__restrict__ next_node_tile0, int n_ctas, int *__restrict__ cta_off, int4 *__restrict__ seq) {
+            int *__restrict__ next_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl) {
     __shared__ int scratch[33];
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     // tile_left becomes the inclusive prefix over all tiles
@@ -1087,8 +1105,16 @@ k_part_scan(int level, const TreeNode *__restrict__ nodes, const int *__restrict
     __syncthreads();
     const int alive = block_scan_excl(2 * nl, [&](int c) { return next_cnt[c]; }, [&](int c, int pos) { next_begin[c] = pos; }, scratch);
     if (threadIdx.x == 0) ctl->n_records = alive;
-    // work lists of the next level, so that it needs no planning launches of its own
-    __syncthreads();
+}
+
+// Work lists of the next level (which sibling to build, tile sequences, partition tiles), from the child segment
+// table k_part_scan left.  Nothing in the scatter of the current level needs them, so the host launches this on a
+// second stream beside the scatter.  One block of 1024 threads.
+static __global__ void __launch_bounds__(1024)
+k_plan_next(int level, const int *__restrict__ next_begin, const int *__restrict__ next_cnt, const int *__restrict__ gcnt,
+            const TreeNode *__restrict__ nodes, TreeCtl *__restrict__ ctl, int by_hessian, int *__restrict__ built_right,
+            HistWork *__restrict__ work, int *__restrict__ hist_tile_base, int *__restrict__ next_node_tile0, int n_ctas,
+            int *__restrict__ cta_off, int4 *__restrict__ seq) {
     hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
     part_plan(level + 1, next_cnt, next_node_tile0, ctl);
