@@ -76,11 +76,39 @@ def test_low_cardinality_collisions(gpu, orc):
     b.close()
 
 
-@pytest.mark.parametrize('depth', [1, 2, 10])
+@pytest.mark.parametrize('depth', [1, 2, 10, 12, 14])
 def test_depth_extremes(gpu, orc, depth):
+    """Depth 14 is the limit; its node table no longer fits the shared memory of the kernel that applies a tree."""
     d = _rand_csr(6000, 6, 1.0, seed=depth)
     p = dict(objective='reg:linear', depth=depth, n_trees=2, max_num_bin=64, learning_rate=0.5, gamma=0.0)
     o, b = _pair(orc, d, **p)
+    assert b.trees().tobytes() == o.trees.tobytes() and np.array_equal(b.ypred(), o.ypred)
+    b.close()
+
+
+@pytest.mark.parametrize('n,f,density', [(1, 3, 1.0), (33, 5, 0.5), (1025, 31, 1.0), (3000, 300, 0.05), (5000, 70, 0.9)])
+def test_csr_layout_ragged_shapes(gpu, orc, n, f, density, monkeypatch):
+    """The same ragged inputs through the CSR-of-bin-ids layout, with some rows emptied."""
+    monkeypatch.setenv('TGBM_LAYOUT', 'sparse')
+    d = _rand_csr(n, f, density, seed=n + f)
+    if d.nnz == 0:
+        d = _rand_csr(n, f, 1.0, seed=n + f + 1)
+    p = dict(objective='reg:linear', depth=5, n_trees=3, max_num_bin=255, learning_rate=0.5)
+    o, b = _pair(orc, d, **p)
+    assert b.info.csr_layout == 1
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid) and np.array_equal(b.ypred(), o.ypred)
+    b.close()
+
+
+def test_csr_layout_many_bins_per_feature(gpu, orc, monkeypatch):
+    """Features with 255 bins each: every evaluation chunk holds one feature; 40 features = 10k bins, more than the
+    shared-memory part of the sparse histogram."""
+    monkeypatch.setenv('TGBM_LAYOUT', 'sparse')
+    d = _rand_csr(20000, 40, 0.6, seed=11)
+    p = dict(objective='reg:linear', depth=6, n_trees=3, max_num_bin=255, learning_rate=0.3)
+    o, b = _pair(orc, d, **p)
+    assert b.info.csr_layout == 1 and b.info.n_bins > 6144
     assert b.trees().tobytes() == o.trees.tobytes() and np.array_equal(b.ypred(), o.ypred)
     b.close()
 

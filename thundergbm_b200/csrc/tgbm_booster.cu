@@ -59,6 +59,7 @@ struct BoosterImpl {
     DevBuf<long long> hist_full, hist_built;
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
+    bool prune_in_smem = true;
     DevBuf<int> hist_cta_off;  // dense histogram kernel: tile sequence of every CTA
     DevBuf<int4> hist_seq;
     DevBuf<SplitRec> recs;
@@ -392,7 +393,8 @@ void Booster::init(const DataSet &ds) {
     TGBM_CUDA(cudaFuncSetAttribute(k_predict_walk<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
     TGBM_CUDA(cudaFuncSetAttribute(k_hist_sparse<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SPARSE_SMEM_BINS * 16));
-    if (sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
+    m.prune_in_smem = sizeof(TreeNode) * (size_t)m.n_nodes <= 200 * 1024;  // up to depth 11
+    if (m.prune_in_smem && sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
         TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(TreeNode) * (size_t)m.n_nodes)));
     if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream);
     lap("training buffers");
@@ -534,7 +536,7 @@ void BoosterImpl::build_tree(int round, int k) {
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
         launches += 4;
     }
-    k_prune<<<1, 1024, sizeof(TreeNode) * (size_t)n_nodes, stream>>>(nodes.p, n_nodes, depth, p.gamma);
+    k_prune<<<1, 1024, prune_in_smem ? sizeof(TreeNode) * (size_t)n_nodes : 0, stream>>>(nodes.p, n_nodes, depth, p.gamma, prune_in_smem ? 1 : 0);
     if (N) {
         const size_t per_node = sizeof(WalkNode) + (sparse ? sizeof(WalkSpan) : 0);
         const int in_smem = per_node * (size_t)n_nodes <= 160 * 1024;

@@ -1199,12 +1199,15 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
 // leaves in index order and climbs while a parent has two leaf children and gain < gamma; the fixed point of that
 // walk does not depend on the order, so the levels are processed bottom-up with one thread per node.  One block.
 static __global__ void __launch_bounds__(1024)
-k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma) {
+k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma, int table_in_smem) {
     extern __shared__ __align__(16) unsigned char sm[];
     __shared__ int scratch[33];
-    TreeNode *sn = reinterpret_cast<TreeNode *>(sm);
-    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) sn[i] = nodes[i];
-    __syncthreads();
+    // trees too large for shared memory (depth 12 to 14) are pruned in place in global memory
+    TreeNode *sn = table_in_smem ? reinterpret_cast<TreeNode *>(sm) : nodes;
+    if (table_in_smem) {
+        for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) sn[i] = nodes[i];
+        __syncthreads();
+    }
     for (int level = depth - 1; level >= 0; --level) {
         const int nl = 1 << level, off = nl - 1;
         for (int n = threadIdx.x; n < nl; n += blockDim.x) {
@@ -1220,7 +1223,8 @@ k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma) {
     }
     block_scan_excl(n_nodes, [&](int i) { return (sn[i].is_valid && !sn[i].is_pruned) ? 1 : 0; },
                     [&](int i, int id) { if (sn[i].is_valid && !sn[i].is_pruned) sn[i].final_id = id; }, scratch);
-    for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) nodes[i] = sn[i];
+    if (table_in_smem)
+        for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) nodes[i] = sn[i];
 }
 
 // TreeBuilder::predict_in_training (src/thundergbm/builder/tree_builder.cu:62-74); nvcc contracts the
