@@ -60,6 +60,9 @@ struct BoosterImpl {
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     bool prune_in_smem = true;
+    bool grad_max_ready = false;        // maxbits holds the maxima of the next round's gradients
+    bool metric_partial_ready = false;  // metric_partial holds the finished round's partial sums
+    int metric_blocks() const { return std::max(1, std::min((N + 255) / 256, 1024)); }
     DevBuf<int> hist_cta_off;  // dense histogram kernel: tile sequence of every CTA
     DevBuf<int4> hist_seq;
     DevBuf<SplitRec> recs;
@@ -407,25 +410,31 @@ void Booster::init(const DataSet &ds) {
 // ------------------------------------------------------------------------------------------------
 void BoosterImpl::gradient(int round) {
     const int tb = 256;
-    maxbits.zero(stream);
+    const bool pointwise = objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC;
+    const int logistic = objective == REG_LINEAR ? 0 : 1;
+    // the pass that applied the previous tree has already found this round's gradient maxima
+    const bool have_max = pointwise && grad_max_ready && round >= 0;
+    grad_max_ready = false;
     root_sum.zero(stream);
-    if (N) {
-        const int gb = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
-        switch (objective) {
-        case REG_LINEAR:
-            k_grad_pointwise<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, 0, gh.p, maxbits.p); break;
-        case REG_LOGISTIC: case BINARY_LOGISTIC:
-            k_grad_pointwise<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, 1, gh.p, maxbits.p); break;
-        case MULTI_SOFTMAX: case MULTI_SOFTPROB:
-            k_grad_softmax<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, K, gh.p, maxbits.p); break;
-        case RANK_PAIRWISE: case RANK_NDCG:
-            rank.gradient(round, p.rank_seed, ypred.p, gh.p, maxbits.p, stream); break;
+    if (!have_max) {
+        maxbits.zero(stream);
+        if (N) {
+            const int gb = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
+            switch (objective) {
+            case REG_LINEAR: case REG_LOGISTIC: case BINARY_LOGISTIC:
+                k_grad_pointwise<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, logistic, gh.p, maxbits.p); break;
+            case MULTI_SOFTMAX: case MULTI_SOFTPROB:
+                k_grad_softmax<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, K, gh.p, maxbits.p); break;
+            case RANK_PAIRWISE: case RANK_NDCG:
+                rank.gradient(round, p.rank_seed, ypred.p, gh.p, maxbits.p, stream); break;
+            }
+            ++launches;
         }
-        ++launches;
     }
     if (comm && comm->active()) comm->allreduce(maxbits.p, 2, Comm::U32, Comm::MAX, stream);
     const int blocks = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
-    k_quantize<<<dim3(blocks, K), tb, 0, stream>>>(gh.p, N, maxbits.p, p.quant_bits, (uint32_t)round, (uint32_t)row_offset, ghq.p, root_sum.p, qinfo.p);
+    k_quantize<<<dim3(blocks, K), tb, 0, stream>>>(have_max ? nullptr : gh.p, N, maxbits.p, p.quant_bits, (uint32_t)round, (uint32_t)row_offset,
+                                                   ghq.p, root_sum.p, qinfo.p, y.p, ypred.p, logistic);
     ++launches;
     if (comm && comm->active()) comm->allreduce(root_sum.p, 2 * (size_t)K, Comm::I64, Comm::SUM, stream);
     if (round >= 0 && round < (int)qinfo_log.n)
@@ -543,16 +552,22 @@ void BoosterImpl::build_tree(int round, int k) {
         const size_t walk_smem = in_smem ? per_node * (size_t)n_nodes : 0;
         float *yp = ypred.p + (size_t)k * N;
         int *nid_out = p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr;
-        const int walk_ctas = std::min(ceil_div(N, 256), num_sms * 8);
+        // One tree per round and a pointwise objective: the walk also adds up the round's metric and finds the maxima
+        // of the next round's gradients (grid and order of additions are those of k_metric_partial).
+        const bool fuse = K == 1 && (objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC);
+        const int walk_ctas = fuse ? metric_blocks() : std::min(ceil_div(N, 256), num_sms * 8);
+        const int fo = fuse ? objective : -1;
+        if (fuse) maxbits.zero(stream);
         if (sparse)
             k_predict_walk<2><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, nullptr, Fpad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, N,
-                                                                     p.learning_rate, yp, nid_out);
+                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p);
         else if (Fpad == 32)
             k_predict_walk<0><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
-                                                                     p.learning_rate, yp, nid_out);
+                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p);
         else
             k_predict_walk<1><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
-                                                                     p.learning_rate, yp, nid_out);
+                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p);
+        grad_max_ready = metric_partial_ready = fuse;
     }
     launches += 2;
     TGBM_CUDA(cudaMemcpyAsync(model.p + (size_t)tree_index * n_nodes, nodes.p, sizeof(TreeNode) * n_nodes, cudaMemcpyDeviceToDevice, stream));
@@ -563,12 +578,16 @@ void BoosterImpl::round_metric(int round) {
         rank.metric(objective, ypred.p, metric.p + round, comm, N_global, stream);
         return;
     }
-    const int blocks = std::max(1, std::min(ceil_div(N, 256), 1024));
-    k_metric_partial<<<blocks, 256, 0, stream>>>(objective, y.p, ypred.p, N, K, metric_partial.p);
+    const int blocks = metric_blocks();
+    if (!metric_partial_ready) {  // else the walk that applied the round's tree has left the partial sums
+        k_metric_partial<<<blocks, 256, 0, stream>>>(objective, y.p, ypred.p, N, K, metric_partial.p);
+        ++launches;
+    }
+    metric_partial_ready = false;
     k_metric_sum<<<1, 32, 0, stream>>>(metric_partial.p, blocks, metric_sum.p);
     if (comm && comm->active()) comm->allreduce(metric_sum.p, 1, Comm::F64, Comm::SUM, stream);
     k_metric_final<<<1, 32, 0, stream>>>(objective, metric_sum.p, N_global, metric.p + round);
-    launches += 3;
+    launches += 2;
 }
 
 void Booster::boost(int n_rounds) {

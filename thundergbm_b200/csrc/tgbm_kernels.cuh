@@ -173,19 +173,32 @@ __device__ inline void track_max(float ag, float h, unsigned *maxbits) {
 }
 
 // SquareLoss / LogisticLoss gradients (include/thundergbm/objective/regression_obj.h:129-154)
+__device__ __forceinline__ float2 pointwise_gh(int logistic, float y, float yp) {
+    if (logistic) {
+        const float p = __fdiv_rn(1.0f, __fadd_rn(1.0f, portable_expf(-yp)));
+        return make_float2(__fsub_rn(p, y), fmaxf(__fmul_rn(p, __fsub_rn(1.0f, p)), 1e-16f));
+    }
+    return make_float2(__fsub_rn(yp, y), 1.0f);
+}
+
+// one row's term of the training metric: squared error (pointwise_metric.cu:8-22), or 1 for a correct binary
+// prediction (multiclass_metric.cu:9-46: sigmoid evaluated in double, class 1 above 0.5)
+__device__ __forceinline__ double pointwise_metric_term(int objective, float y, float yp) {
+    if (objective == BINARY_LOGISTIC) {
+        // sigmoid(x) > 0.5 is decided by the sign of x except within rounding distance of zero
+        const int k = fabsf(yp) > 1e-8f ? (yp > 0.f ? 1 : 0) : ((1.0 / (1.0 + exp(-(double)yp)) > 0.5) ? 1 : 0);
+        return ((float)k == y) ? 1.0 : 0.0;
+    }
+    const float e = __fsub_rn(yp, y);
+    return (double)__fmul_rn(e, e);
+}
+
 static __global__ void k_grad_pointwise(const float *__restrict__ y, const float *__restrict__ yp, int n, int logistic,
                                  float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
     float mg = 0.f, mh = 0.f;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        float g, h;
-        if (logistic) {
-            const float p = __fdiv_rn(1.0f, __fadd_rn(1.0f, portable_expf(-yp[i])));
-            g = __fsub_rn(p, y[i]);
-            h = fmaxf(__fmul_rn(p, __fsub_rn(1.0f, p)), 1e-16f);
-        } else {
-            g = __fsub_rn(yp[i], y[i]);
-            h = 1.0f;
-        }
+        const float2 v = pointwise_gh(logistic, y[i], yp[i]);
+        const float g = v.x, h = v.y;
         gh[i] = make_float2(g, h);
         mg = fmaxf(mg, fabsf(g)); mh = fmaxf(mh, h);
     }
@@ -220,9 +233,13 @@ static __global__ void k_grad_softmax(const float *__restrict__ y, const float *
 // The rounding is dithered, q = floor(v * scale + u) with u in [0,1) a hash of (round, class, global row):
 // round-to-nearest would move every row that carries the same gradient the same way (in the first round all rows
 // of a class do), and those shifts would add up coherently in the histogram sums.
+//
+// `gh` null: the gradients are those of a pointwise objective (`logistic` 0/1) and are computed again from y and the
+// scores here -- the pass that found their maxima (k_predict_walk) did not store them.
 static __global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned *__restrict__ maxbits, int quant_bits,
                            uint32_t round, uint32_t row_offset, int2 *__restrict__ ghq,
-                           unsigned long long *__restrict__ root_sum, QuantInfo *__restrict__ qinfo) {
+                           unsigned long long *__restrict__ root_sum, QuantInfo *__restrict__ qinfo,
+                           const float *__restrict__ y, const float *__restrict__ yp, int logistic) {
     const int k = blockIdx.y;
     const int eg = exp_above(__uint_as_float(maxbits[0])), eh = exp_above(__uint_as_float(maxbits[1]));
     const double sg = pow2d(quant_bits - eg), sh = pow2d(quant_bits - eh);
@@ -232,7 +249,7 @@ static __global__ void k_quantize(const float2 *__restrict__ gh, int n, const un
     }
     long long tg = 0, th = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        const float2 v = gh[(size_t)k * n + i];
+        const float2 v = gh ? gh[(size_t)k * n + i] : pointwise_gh(logistic, y[i], yp[i]);
         const uint32_t row = row_offset + (uint32_t)i;
         const double ug = (double)mix32(0x9E3779B9u, round, (uint32_t)k, row) * (1.0 / 4294967296.0);
         const double uh = (double)mix32(0x9E3779B9u + 1u, round, (uint32_t)k, row) * (1.0 / 4294967296.0);
@@ -1264,7 +1281,16 @@ template <int LAYOUT>
 static __global__ void __launch_bounds__(256)
 k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_smem, const unsigned char *__restrict__ bins, int Fpad,
                const int *__restrict__ sp_row_ptr, const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr,
-               int n, float lr, float *__restrict__ yp, int *__restrict__ nid_out) {
+               int n, float lr, float *__restrict__ yp, int *__restrict__ nid_out,
+               const float *__restrict__ y, int fuse_objective, double *__restrict__ metric_partial,
+               unsigned *__restrict__ maxbits) {
+    // fuse_objective >= 0 (a pointwise objective, one tree per round): the same pass adds up the round's training
+    // metric (same grid, same order of additions as k_metric_partial) and finds the maxima of the next round's
+    // gradients, so that neither needs a pass of its own over y and the scores.
+    const bool fuse = fuse_objective >= 0;
+    const int fuse_logistic = fuse_objective == REG_LINEAR ? 0 : 1;
+    double msum = 0;
+    float mg = 0.f, mh = 0.f;
     extern __shared__ __align__(16) unsigned char walk_sm[];
     WalkNode *wn = reinterpret_cast<WalkNode *>(walk_sm);
     WalkSpan *ws = reinterpret_cast<WalkSpan *>(walk_sm + sizeof(WalkNode) * n_nodes);
@@ -1313,7 +1339,27 @@ k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_sme
             nid = 2 * nid + (left ? 1 : 2);
         }
         if (nid_out) nid_out[r] = nid;
-        yp[r] = __fmaf_rn(lr, weight, yp[r]);
+        const float score = __fmaf_rn(lr, weight, yp[r]);
+        yp[r] = score;
+        if (fuse) {
+            const float yr = y[r];
+            msum += pointwise_metric_term(fuse_objective, yr, score);
+            const float2 v = pointwise_gh(fuse_logistic, yr, score);
+            mg = fmaxf(mg, fabsf(v.x)); mh = fmaxf(mh, v.y);
+        }
+    }
+    if (fuse) {
+        __shared__ double ws[8];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) msum += __shfl_xor_sync(0xffffffffu, msum, o);
+        if ((threadIdx.x & 31) == 0) ws[threadIdx.x >> 5] = msum;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double t = 0;
+            for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += ws[w];
+            metric_partial[blockIdx.x] = t;
+        }
+        track_max(mg, mh, maxbits);
     }
 }
 
@@ -1325,12 +1371,8 @@ static __global__ void k_metric_partial(int objective, const float *__restrict__
     __shared__ double ws[32];
     double s = 0;
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
-        if (objective == REG_LINEAR || objective == REG_LOGISTIC) {
-            const float e = __fsub_rn(yp[i], y[i]);
-            s += (double)__fmul_rn(e, e);
-        } else if (objective == BINARY_LOGISTIC) {
-            const int k = (1.0 / (1.0 + exp(-(double)yp[i])) > 0.5) ? 1 : 0;
-            s += ((float)k == y[i]) ? 1.0 : 0.0;
+        if (objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC) {
+            s += pointwise_metric_term(objective, y[i], yp[i]);
         } else {
             int mk = 0;
             float mp = yp[i];
