@@ -504,7 +504,6 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
     const int group = blockIdx.y;
     const int f0 = group * 32;
     const int nf = min(32, F - f0);
-    const int bin_lo = cut_ptr[f0], bin_hi = cut_ptr[f0 + nf];
     const int lane = threadIdx.x & 31;
     const int i2 = cta_off[blockIdx.x], i_end = cta_off[blockIdx.x + 1];  // the CTA's tiles in seq[], see hist_sequence
     if (i2 >= i_end) return;
@@ -520,15 +519,23 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
         }
         __syncthreads();
     };
-    auto flush = [&](int slab_idx) {  // totals -> the node's histogram (global bin order)
-        drain();
-        long long *dst = slab + (size_t)slab_idx * B * 2;
-        for (int b = bin_lo + threadIdx.x; b < bin_hi; b += HIST_THREADS) {
-            const int f = cut_fid[b];
-            const int s = (b - cut_ptr[f]) * 32 + (f - f0);
-            const long long vg = tot[s], vh = tot[256 * 32 + s];
-            if (vg) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b), (unsigned long long)vg); tot[s] = 0; }
-            if (vh) { atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b + 1), (unsigned long long)vh); tot[256 * 32 + s] = 0; }
+    // totals + open window -> the node's histogram.  A thread keeps one feature (its bank) and walks the local bins,
+    // so the loop has no dependent loads; everything it reads is zeroed for the next node.
+    const int flush_f = threadIdx.x & 31;
+    const int flush_b0 = flush_f < nf ? cut_ptr[f0 + flush_f] : 0;
+    const int flush_nb = flush_f < nf ? cut_ptr[f0 + flush_f + 1] - flush_b0 : 0;
+    auto flush = [&](int slab_idx) {
+        __syncthreads();
+        unsigned long long *dst = reinterpret_cast<unsigned long long *>(slab + ((size_t)slab_idx * B + flush_b0) * 2);
+#pragma unroll 2
+        for (int i = threadIdx.x >> 5; i < 256; i += HIST_THREADS / 32) {
+            const int s = i * 32 + flush_f;
+            const long long vg = tot[s] + acc[s], vh = tot[256 * 32 + s] + acc[256 * 32 + s];
+            tot[s] = 0; tot[256 * 32 + s] = 0; acc[s] = 0; acc[256 * 32 + s] = 0;
+            if (i < flush_nb) {
+                if (vg) atomicAdd(dst + 2 * i, (unsigned long long)vg);
+                if (vh) atomicAdd(dst + 2 * i + 1, (unsigned long long)vh);
+            }
         }
         __syncthreads();
     };
