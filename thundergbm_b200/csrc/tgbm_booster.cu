@@ -60,6 +60,7 @@ struct BoosterImpl {
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     bool prune_in_smem = true;
+    DevBuf<int> eval_ticket;  // k_eval: finished blocks per sibling pair, zero between launches
     bool grad_max_ready = false;        // maxbits holds the maxima of the next round's gradients
     bool metric_partial_ready = false;  // metric_partial holds the finished round's partial sums
     int metric_blocks() const { return std::max(1, std::min((N + 255) / 256, 1024)); }
@@ -377,6 +378,8 @@ void Booster::init(const DataSet &ds) {
     const int max_pairs = std::max(1, 1 << std::max(0, depth - 2));
     m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
     m.hist_cta_off.alloc((size_t)m.num_sms + 1);
+    m.eval_ticket.alloc(max_pairs);
+    m.eval_ticket.zero(m.stream);
     m.hist_seq.alloc((size_t)ceil_div(std::max(N, 1), HIST_THREADS) + max_pairs + 16);
     m.recs.alloc(((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
@@ -515,11 +518,11 @@ void BoosterImpl::build_tree(int round, int k) {
             k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
         } else {
             k_eval<<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built, parent_hist,
-                                                      hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p);
-            k_best_apply<<<nl, 32, 0, stream>>>(level, F, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 0);
+                                                      hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p,
+                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p);
         }
         // -- move the rows (not after the last level: the finished tree is applied by walking it, see k_predict_walk)
-        launches += 3;
+        launches += sparse ? 3 : 2;
         if (level == depth - 1) break;
         TimedEvent pv{};
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }

@@ -718,10 +718,10 @@ __device__ __forceinline__ float split_gain(float pg, float ph, float lg, float 
 // Sibling subtraction, per-feature prefix scan, missing sums, gains and per-feature argmax
 // (hist_tree_builder_single.cu:257-347 for the root, :538-540 and :614-704 for sibling pairs).
 // grid = (F, pairs); block = 64: warp 0 evaluates the left child, warp 1 the right child.
-static __global__ void __launch_bounds__(64)
-k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode *__restrict__ nodes,
-       const int *__restrict__ built_right, const long long *__restrict__ built, const long long *__restrict__ parent,
-       long long *__restrict__ full, const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs) {
+__device__ __forceinline__ void eval_feature(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode *nodes,
+                                             const int *__restrict__ built_right, const long long *__restrict__ built,
+                                             const long long *__restrict__ parent, long long *__restrict__ full,
+                                             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs) {
     __shared__ long long sg[2][256], sh[2][256];
     const int f = blockIdx.x, j = blockIdx.y;
     const int b0 = cut_ptr[f], nb = cut_ptr[f + 1] - b0;
@@ -929,20 +929,26 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
 }
 
 // Per-node argmax over the features, SplitPoint decode and update_tree
-// (hist_tree_builder_single.cu:365-389 and :847-902).  One warp per node of the level.
-static __global__ void __launch_bounds__(32)
-k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
-             const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam,
-             const int *__restrict__ cut_fid, int chunked) {
+// (hist_tree_builder_single.cu:365-389 and :847-902).  Called by one whole warp for node n of the level.  The records
+// may have been written by other blocks of the running kernel: they are read past L1.
+__device__ __forceinline__ SplitRec load_rec(const SplitRec *p) {
+    SplitRec r;
+    r.gain = __ldcg(&p->gain); r.bin = __ldcg(&p->bin);
+    r.lg = __ldcg(&p->lg); r.lh = __ldcg(&p->lh); r.mg = __ldcg(&p->mg); r.mh = __ldcg(&p->mh);
+    return r;
+}
+__device__ __forceinline__ void best_apply_node(int level, int n, int F, const int *__restrict__ cut_ptr,
+                                                const float *__restrict__ cut_val, const SplitRec *recs, TreeNode *nodes,
+                                                float rt_eps, float lam, const int *__restrict__ cut_fid, int chunked) {
     // chunked: F is the number of chunks and a record's bin is a global bin index (k_eval_chunk);
     // otherwise one record per feature with a feature-local bin (k_eval).  Ties go to the smaller global bin either way.
-    const int n = blockIdx.x, lane = threadIdx.x;
+    const int lane = threadIdx.x & 31;
     const int nid = (1 << level) - 1 + n;
     if (!nodes[nid].is_valid) return;
     unsigned long long key = 0;
     int key_col = 0;  // record column (feature or chunk) of this lane's best key
     for (int f = lane; f < F; f += 32) {
-        const SplitRec r = recs[(size_t)n * F + f];
+        const SplitRec r = load_rec(recs + (size_t)n * F + f);
         if (r.bin < 0) continue;
         const unsigned long long k = ((unsigned long long)__float_as_uint(fabsf(r.gain)) << 32) |
                                      (unsigned)(0x7fffffff - (chunked ? r.bin : f));
@@ -970,10 +976,10 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
     if (chunked) {
         const int gbin = f;
         f = cut_fid[gbin];
-        r = recs[(size_t)n * F + win_col];
+        r = load_rec(recs + (size_t)n * F + win_col);
         r.bin = gbin - cut_ptr[f];
     } else {
-        r = recs[(size_t)n * F + f];
+        r = load_rec(recs + (size_t)n * F + f);
     }
     const float gain = fabsf(r.gain);
     if (gain > rt_eps) {
@@ -1002,6 +1008,38 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
         nodes[nd.lch_index].is_valid = 0;
         nodes[nd.rch_index].is_valid = 0;
     }
+}
+
+// CSR layout: one warp per node of the level, after k_eval_chunk
+static __global__ void __launch_bounds__(32)
+k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
+             const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam,
+             const int *__restrict__ cut_fid, int chunked) {
+    best_apply_node(level, blockIdx.x, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, chunked);
+}
+
+// Dense layout: evaluation of every (pair, feature) and, by the block that finishes a pair last, the choice among the
+// features and the tree update of the pair's two nodes -- one launch per level instead of two.
+// `ticket[pair]` counts the finished blocks of a pair and is left at zero.
+static __global__ void __launch_bounds__(64)
+k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes, const int *__restrict__ built_right,
+       const long long *__restrict__ built, const long long *__restrict__ parent, long long *__restrict__ full,
+       const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, const float *__restrict__ cut_val,
+       float rt_eps, const int *__restrict__ cut_fid, int *__restrict__ ticket) {
+    eval_feature(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs);
+    __shared__ int last;
+    __threadfence();  // the block's records are visible before its ticket is
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        last = atomicAdd(&ticket[blockIdx.y], 1) == (int)gridDim.x - 1;
+        if (last) ticket[blockIdx.y] = 0;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence();
+    const int warp = threadIdx.x >> 5;
+    if (level == 0) { if (warp == 0) best_apply_node(0, 0, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, 0); }
+    else best_apply_node(level, 2 * blockIdx.y + warp, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, 0);
 }
 
 // ------------------------------------------------------------------ instance partition
