@@ -38,6 +38,8 @@ struct BoosterImpl {
     std::vector<int> h_cut_ptr;
     std::vector<float> label;
 
+    DevBuf<int> d_row_ptr, d_col;  // the input CSR on the device, held from upload_csr() to the end of binning
+    DevBuf<float> d_val;
     DevBuf<unsigned char> bins, binsT;
     // wide sparse data: CSR of global bin ids instead of the two dense matrices
     bool sparse = false;
@@ -88,6 +90,7 @@ struct BoosterImpl {
     }
 
     // ---------------------------------------------------------------- init helpers
+    void upload_csr(const DataSet &ds);
     void find_cuts_and_bins(const DataSet &ds);
     void init_base_score();
     void gradient(int round);
@@ -97,6 +100,33 @@ struct BoosterImpl {
 };
 
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// Host CSR -> device (asynchronous).  When the caller did not count the features (DataSet::n_features < 0) the largest
+// column index is found here, at HBM speed, instead of by a pass over the host copy.
+void BoosterImpl::upload_csr(const DataSet &ds) {
+    const size_t nnz = (size_t)ds.rp[N];
+    d_row_ptr.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1));
+    TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
+    if (F < 0) {
+        F = 1;  // dataset.cpp:54-57: largest column index + 1
+        if (nnz) {
+            DevBuf<int> d_max;
+            d_max.alloc(1);
+            size_t tb = 0;
+            TGBM_CUDA(cub::DeviceReduce::Max(nullptr, tb, d_col.p, d_max.p, (int)nnz, stream));
+            DevBuf<unsigned char> tmp;
+            tmp.alloc(std::max<size_t>(tb, 1));
+            TGBM_CUDA(cub::DeviceReduce::Max(tmp.p, tb, d_col.p, d_max.p, (int)nnz, stream));
+            int h_max = 0;
+            TGBM_CUDA(cudaMemcpyAsync(&h_max, d_max.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
+            TGBM_CUDA(cudaStreamSynchronize(stream));
+            TGBM_CHECK(h_max >= 0, "negative column index in the CSR input");
+            F = h_max + 1;
+        }
+    }
+}
 
 // ------------------------------------------------------------------------------------------------
 // Cut points (HistCut::get_cut_points_single, src/thundergbm/hist_cut.cu:205-286) and the bin matrix.
@@ -114,14 +144,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         t_prev = t;
     };
     const size_t nnz = (size_t)ds.rp[N];
-    DevBuf<int> d_row_ptr, d_col;
-    DevBuf<float> d_val;
-    d_row_ptr.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1));
-    TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
-    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
-    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
-
-    lap("alloc + H2D of the CSR");
+    lap("H2D of the CSR");
     long long nu = 0;
     DevBuf<unsigned long long> ukeys;
     {
@@ -270,6 +293,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     }
     TGBM_CUDA(cudaStreamSynchronize(stream));
     TGBM_CUDA(cudaGetLastError());
+    d_row_ptr.release(); d_col.release(); d_val.release();
     lap("binning");
 }
 
@@ -299,6 +323,7 @@ void Booster::init(const DataSet &ds) {
     TGBM_CUDA(cudaEventCreateWithFlags(&m.ev_plan, cudaEventDisableTiming));
     m.N = ds.n_rows;
     m.F = ds.n_features;
+    m.upload_csr(ds);
     m.depth = p.depth;
     m.n_nodes = (1 << (p.depth + 1)) - 1;
     m.label = ds.label;
@@ -357,7 +382,14 @@ void Booster::init(const DataSet &ds) {
     const int N = m.N, K = m.K, depth = m.depth;
     const size_t n1 = std::max<size_t>(N, 1);
     m.y.alloc(n1); m.ypred.alloc(n1 * K); m.gh.alloc(n1 * K); m.ghq.alloc(n1 * K);
-    TGBM_CUDA(cudaMemcpyAsync(m.y.p, ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice, m.stream));
+    TGBM_CUDA(cudaMemcpyAsync(m.y.p, ds.yv ? ds.yv : ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice, m.stream));
+    if (ds.labels_raw && N) {  // label value -> class index (dataset.cpp:83-101), on the device
+        DevBuf<float> d_label;
+        d_label.alloc(std::max<size_t>(ds.label.size(), 1));
+        TGBM_CUDA(cudaMemcpyAsync(d_label.p, ds.label.data(), sizeof(float) * ds.label.size(), cudaMemcpyHostToDevice, m.stream));
+        k_map_labels<<<std::min(ceil_div(N, 256), m.num_sms * 8), 256, 0, m.stream>>>(m.y.p, N, d_label.p, (int)ds.label.size());
+        TGBM_CUDA(cudaStreamSynchronize(m.stream));
+    }
     m.ypred.zero(m.stream);
     m.maxbits.alloc(2); m.root_sum.alloc(2 * (size_t)K); m.qinfo.alloc(1);
     m.qinfo_log.alloc(std::max(p.n_trees, 1) + 1);

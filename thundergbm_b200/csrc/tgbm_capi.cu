@@ -54,11 +54,13 @@ std::vector<std::vector<tgbm::Tree>> wrap_model(::Tree *model, int n_trees, int 
 
 // TreeTrainer::train (src/thundergbm/trainer.cu:18-57) for the histogram path
 std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSet &ds, const tgbm::Comm *comm) {
-    if (p.tree_method == "auto") p.tree_method = ds.n_features > 20000 ? "exact" : "hist";  // trainer.cu:19-23
-    TGBM_CHECK(p.tree_method == "hist", "tree_method=" + p.tree_method +
+    TGBM_CHECK(p.tree_method == "hist" || p.tree_method == "auto", "tree_method=" + p.tree_method +
                " is outside this library: only the histogram builder (tree_method=hist) is implemented");
     tgbm::Booster booster(p, comm);
-    booster.init(ds);
+    booster.init(ds);  // counts the features when the data set has not
+    if (p.tree_method == "auto") p.tree_method = booster.n_features() > 20000 ? "exact" : "hist";  // trainer.cu:19-23
+    TGBM_CHECK(p.tree_method == "hist", "tree_method=auto resolves to exact above 20000 features"
+               " (src/thundergbm/trainer.cu:19-23), which is outside this library: ask for tree_method=hist");
     const auto t0 = std::chrono::high_resolution_clock::now();
     booster.boost(p.n_trees);
     booster.sync();
@@ -137,8 +139,8 @@ void sparse_train_scikit(int row_size, float *val, int *row_ptr, int *col_ptr, f
         TGBM_CHECK(n_device == 1, "one process drives one GPU here; multi-GPU training goes through tgbm_comm_create / "
                                   "tgbm_booster_create with one process per GPU");
         tgbm::DataSet ds;
-        ds.load_from_sparse(row_size, val, row_ptr, col_ptr, label, group, num_group, p);
-        tgbm::log_info("#instances = %d, #features = %d", ds.n_rows, ds.n_features);
+        ds.load_from_sparse(row_size, val, row_ptr, col_ptr, label, group, num_group, p, /*lazy=*/true);
+        tgbm::log_info("#instances = %d", ds.n_rows);
         *num_class = p.num_class;
         auto m = train(p, ds, nullptr);
         *num_class = p.num_class;
@@ -315,7 +317,7 @@ TgbmBooster *tgbm_booster_create(int n_rows, const float *val, const int *row_pt
             ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, tmp);
             group_label_global(ds, b->param, c);
         } else {
-            ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, b->param);
+            ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, b->param, /*lazy=*/true);
         }
         lap("host view of the data");
         b->label = ds.label;
@@ -401,6 +403,7 @@ int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, co
         tgbm::DataSet ds;
         ds.n_rows = n_rows;
         ds.y.assign(label, label + n_rows);
+        ds.yv = ds.y.data();
         if (group) ds.group.assign(group, group + num_group);
         std::vector<float> r(raw, raw + (size_t)n_rows * trees_per_round);
         *out = tgbm::metric_score(o, ds, trees_per_round, r);

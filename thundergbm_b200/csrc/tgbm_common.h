@@ -103,8 +103,16 @@ struct DataSet {
     std::vector<float> val, y;
     std::vector<int> group;
     std::vector<float> label;  // distinct class labels after group_label()
+    // Labels as the booster reads them: `y` (owned) or the caller's array (borrowed).  labels_raw: the objective
+    // groups its labels (dataset.cpp:83-101) but `yv` still holds the caller's values -- `label` is complete and the
+    // booster maps y -> index on the device.
+    const float *yv = nullptr;
+    bool labels_raw = false;
+    // lazy = true does on the host only what needs no pass that writes: n_features stays -1 (the booster finds it on
+    // the device after the upload) and the labels are borrowed instead of copied.
     void load_from_sparse(int n, const float *v, const int *rp, const int *ci, const float *yy, const int *grp,
-                          int num_group, GBMParam &param);
+                          int num_group, GBMParam &param, bool lazy = false);
+    void distinct_labels(const float *yy, size_t n);
     void load_from_file(const std::string &file, GBMParam &param);
     void load_group_file(const std::string &file);
     void group_label();

@@ -29,19 +29,23 @@ void log_info(const char *fmt, ...) {
 // src/thundergbm/dataset.cpp:20-69.  The CSR arrays are copied; n_features = max column + 1;
 // classification objectives regroup the labels; ranking objectives take the query group sizes.
 void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *ci, const float *yy, const int *grp,
-                               int num_group, GBMParam &param) {
+                               int num_group, GBMParam &param, bool lazy) {
     TGBM_CHECK(n >= 0 && rp != nullptr, "bad CSR input");
     const long long nnz = rp[n];
     TGBM_CHECK(nnz >= 0, "bad CSR row_ptr");
     n_rows = n;
     row_ptr.clear(); col.clear(); val.clear();
     this->rp = rp; this->ci = ci; this->vv = v;  // borrowed: the 2.4 GB of a Higgs-sized CSR are not copied on the host
-    y.assign(n, 0.f);
-    if (yy) y.assign(yy, yy + n);
+    const bool borrow = lazy && yy != nullptr;
+    y.clear();
+    if (!borrow) { if (yy) y.assign(yy, yy + n); else y.assign(n, 0.f); }
+    yv = borrow ? yy : y.data();
+    labels_raw = false;
     label.clear();
     group.clear();
     // n_features = largest column index + 1 (dataset.cpp:54-57), scanned by a few threads
-    {
+    n_features = -1;
+    if (!lazy) {
         const int nt = (int)std::max<long long>(1, std::min<long long>(16, nnz / (1 << 22)));
         std::vector<int> part(nt, 0);
         std::vector<std::thread> th;
@@ -57,7 +61,8 @@ void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *
     }
     const int o = objective_from_name(param.objective);
     if (yy && need_group_label(o)) {
-        group_label();
+        if (borrow) { distinct_labels(yy, (size_t)n); labels_raw = true; }
+        else group_label();
         param.num_class = (int)label.size();
     }
     if (need_group_file(o))
@@ -65,25 +70,27 @@ void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *
 }
 
 // src/thundergbm/dataset.cpp:83-101: labels cast to int, sorted, uniqued; y -> index of its value
-void DataSet::group_label() {
-    // distinct int(label) values, found by a few threads (each keeps a small sorted set and a last-value cache)
-    const size_t n = y.size();
+void DataSet::distinct_labels(const float *yy, size_t n) {
+    // distinct int(label) values, found by a few threads; a thread keeps what it has seen in a small unsorted array
+    // (two or a handful of classes is the rule) and falls back to a sorted vector beyond that
     const int nt = (int)std::max<size_t>(1, std::min<size_t>(16, n / (1 << 20)));
     std::vector<std::vector<int>> found(nt);
     {
         std::vector<std::thread> th;
         for (int t = 0; t < nt; ++t)
             th.emplace_back([&, t] {
-                std::vector<int> &set = found[t];
-                bool have = false;
-                int last = 0;
+                int small[16], ns = 0;
+                std::vector<int> &big = found[t];
                 for (size_t i = n * t / nt; i < n * (t + 1) / nt; ++i) {
-                    const int v = (int)y[i];
-                    if (have && v == last) continue;
-                    have = true; last = v;
-                    auto it = std::lower_bound(set.begin(), set.end(), v);
-                    if (it == set.end() || *it != v) set.insert(it, v);
+                    const int v = (int)yy[i];
+                    bool hit = false;
+                    for (int k = 0; k < ns; ++k) hit |= small[k] == v;
+                    if (hit) continue;
+                    if (ns < 16) { small[ns++] = v; continue; }
+                    auto it = std::lower_bound(big.begin(), big.end(), v);
+                    if (it == big.end() || *it != v) big.insert(it, v);
                 }
+                big.insert(big.end(), small, small + ns);
             });
         for (auto &x : th) x.join();
     }
@@ -93,14 +100,27 @@ void DataSet::group_label() {
     t.erase(std::unique(t.begin(), t.end()), t.end());
     label.clear();
     for (int v : t) label.push_back((float)v);
+}
+
+void DataSet::group_label() {
+    const size_t n = y.size();
+    distinct_labels(y.data(), n);
+    const int nt = (int)std::max<size_t>(1, std::min<size_t>(16, n / (1 << 20)));
     // y -> index of its value among the labels; a label that is not an integer maps to 0
+    const int nl = (int)label.size();
     std::vector<std::thread> th;
     for (int k = 0; k < nt; ++k)
         th.emplace_back([&, k] {
             for (size_t i = n * k / nt; i < n * (k + 1) / nt; ++i) {
                 const float v = y[i];
-                auto it = std::lower_bound(label.begin(), label.end(), v);
-                y[i] = (it != label.end() && *it == v) ? (float)(it - label.begin()) : 0.f;
+                int idx = 0;
+                if (nl <= 16) {
+                    for (int j = 0; j < nl; ++j) idx = label[j] == v ? j : idx;
+                } else {
+                    auto it = std::lower_bound(label.begin(), label.end(), v);
+                    idx = (it != label.end() && *it == v) ? (int)(it - label.begin()) : 0;
+                }
+                y[i] = (float)idx;
             }
         });
     for (auto &x : th) x.join();
@@ -162,7 +182,8 @@ void DataSet::load_from_file(const std::string &file, GBMParam &param) {
     }
     n_rows = (int)y.size();
     n_features = maxf;
-    rp = row_ptr.data(); ci = col.data(); vv = val.data();
+    rp = row_ptr.data(); ci = col.data(); vv = val.data(); yv = y.data();
+    labels_raw = false;
     log_info("#instances = %d, #features = %d", n_rows, n_features);
     const int o = objective_from_name(param.objective);
     if (need_group_file(o)) load_group_file(file + ".group");

@@ -146,6 +146,20 @@ static __global__ void k_rows_unsorted(const int *__restrict__ row_ptr, const in
     }
 }
 
+// y[i] <- index of y[i] among the ascending `label` values, 0 when it is not one of them
+// (DataSet::group_label, src/thundergbm/dataset.cpp:83-101)
+static __global__ void k_map_labels(float *__restrict__ y, int n, const float *__restrict__ label, int n_label) {
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        const float v = y[i];
+        int lo = 0, hi = n_label;
+        while (lo < hi) {
+            const int mid = (lo + hi) / 2;
+            if (label[mid] < v) lo = mid + 1; else hi = mid;
+        }
+        y[i] = (lo < n_label && label[lo] == v) ? (float)lo : 0.f;
+    }
+}
+
 // ------------------------------------------------------------------ objectives
 // block-wide maximum of |g| and h, then one atomic pair per block (every thread of the block must call it)
 __device__ inline void track_max(float ag, float h, unsigned *maxbits) {

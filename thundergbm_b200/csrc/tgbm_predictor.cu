@@ -191,7 +191,7 @@ float metric_score(int objective, const DataSet &ds, int num_class, const std::v
     (void)num_class;
     DevBuf<float> d_y, d_raw, d_out;
     d_y.alloc(N); d_raw.alloc(raw.size()); d_out.alloc(1);
-    TGBM_CUDA(cudaMemcpy(d_y.p, ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice));
+    TGBM_CUDA(cudaMemcpy(d_y.p, ds.yv ? ds.yv : ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice));
     TGBM_CUDA(cudaMemcpy(d_raw.p, raw.data(), sizeof(float) * raw.size(), cudaMemcpyHostToDevice));
     if (need_group_file(objective)) {
         RankState rs;

@@ -179,6 +179,7 @@ struct RankState {
 
     void init(const DataSet &ds, int objective, int n_rows, cudaStream_t stream) {
         N = n_rows;
+        const float *labels = ds.yv ? ds.yv : ds.y.data();
         n_group = (int)ds.group.size();
         std::vector<int> h(n_group + 1, 0);
         for (int i = 0; i < n_group; ++i) { h[i + 1] = h[i] + ds.group[i]; max_len = std::max(max_len, ds.group[i]); }
@@ -190,7 +191,7 @@ struct RankState {
         for (int r = 0; r < (int)ltab.size(); ++r) ltab[r] = log2f((float)(r + 1 + 1));
         if (objective == RANK_NDCG)
             for (int k = 0; k < n_group; ++k) {
-                std::vector<float> s(ds.y.begin() + h[k], ds.y.begin() + h[k + 1]);
+                std::vector<float> s(labels + h[k], labels + h[k + 1]);
                 std::sort(s.begin(), s.end(), std::greater<float>());
                 float v = 0.f;
                 for (size_t i = 0; i < s.size(); ++i) v += (float)((1 << (int)s[i]) - 1) / ltab[i];
@@ -201,7 +202,7 @@ struct RankState {
         TGBM_CUDA(cudaMemcpyAsync(gptr.p, h.data(), sizeof(int) * h.size(), cudaMemcpyHostToDevice, stream));
         TGBM_CUDA(cudaMemcpyAsync(idcg.p, hid.data(), sizeof(float) * hid.size(), cudaMemcpyHostToDevice, stream));
         TGBM_CUDA(cudaMemcpyAsync(log2tab.p, ltab.data(), sizeof(float) * ltab.size(), cudaMemcpyHostToDevice, stream));
-        TGBM_CUDA(cudaMemcpyAsync(y.p, ds.y.data(), sizeof(float) * n_rows, cudaMemcpyHostToDevice, stream));
+        TGBM_CUDA(cudaMemcpyAsync(y.p, labels, sizeof(float) * n_rows, cudaMemcpyHostToDevice, stream));
         TGBM_CUDA(cudaStreamSynchronize(stream));
         n_group_total = n_group;
         idcg_used = objective == RANK_NDCG;
