@@ -115,6 +115,41 @@ def oracle_sample_run(n_trees: int, threads: int):
     return r
 
 
+def reference_gpu_run(n_trees: int):
+    """The reference itself (built by oracle/build_ref.sh into oracle/_ref/, GPU-only code) on the full workload on
+    cuda:0 -- an extra figure beside the CPU arm: its own 'training time' (src/thundergbm/trainer.cu:42-50) and the
+    wall clock of TreeTrainer::train including its set-up.  None when the build is absent or the run fails."""
+    import re
+    import tempfile
+    harness = os.path.join(ROOT, 'oracle', '_ref', 'bin', 'ref_harness')
+    if not os.path.exists(harness):
+        return {'unavailable': 'oracle/_ref/bin/ref_harness not built'}
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return {'unavailable': 'no GPU'}
+        d = synth.higgs_like(N_ROWS, seed=1)
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, 'c2.tgbin')
+            synth.write_tgbin(d, path)
+            del d
+            env = dict(os.environ)
+            env['LD_LIBRARY_PATH'] = os.path.join(ROOT, 'oracle', '_ref', 'lib') + ':' + env.get('LD_LIBRARY_PATH', '')
+            cmd = [harness, path, tmp, 'objective=' + PARAMS['objective'], f"depth={PARAMS['depth']}", f'n_trees={n_trees}',
+                   f"max_num_bin={PARAMS['max_num_bin']}", f"learning_rate={PARAMS['learning_rate']}", 'dump_bins=0']
+            out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+        if out.returncode != 0:
+            return {'unavailable': f'ref_harness exit {out.returncode}'}
+        t_train = float(re.search(r'training time = ([0-9.eE+-]+)', out.stdout).group(1))
+        t_wall = float(re.search(r'train_wall_s ([0-9.eE+-]+)', out.stdout).group(1))
+        errs = re.findall(r'\[(\d+)/\d+\] test error = ([0-9.eE+-]+)', out.stdout)
+        return {'value': t_train * 100.0 / n_trees, 'unit': 's/100 trees', 'trees': n_trees,
+                'e2e_value': t_wall * 100.0 / n_trees, 'final_train_error': float(errs[-1][1]) if errs else None,
+                'kind': 'the reference built for sm_100a by oracle/build_ref.sh, same workload, 1 GPU'}
+    except Exception as e:  # noqa: BLE001 -- an extra figure must never break the arm
+        return {'unavailable': f'{type(e).__name__}: {e}'[:200]}
+
+
 def run_reference(args):
     """Reference arm: the reference's algorithm on the host cores (CPU restatement, all cores)."""
     rank = int(os.environ.get('RANK', '0'))
@@ -138,6 +173,7 @@ def run_reference(args):
         'cpu_baseline': {'value': s_per_100_full, 'unit': 's/100 trees', 'cores': cores, 'kind': 'port', 'sample': sample},
         'e2e': {'value': s_per_100_full, 'unit': 's/100 trees', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
+        'reference_gpu': reference_gpu_run(k),
     }
     print(json.dumps(line), flush=True)
 
