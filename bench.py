@@ -248,6 +248,15 @@ def main():
     prof = b.profile()
     metrics = b.metrics()
     info = b.info
+    # batch predict_raw of the trained trees over this rank's rows (Predictor::predict_raw): device time of the
+    # traversal kernel; algorithmic bytes = nnz * 8 + rows * (4 + 4)
+    predict = None
+    if rank == 0 and not args.no_e2e:
+        from thundergbm_b200.booster import predict_raw
+        trees = b.trees()
+        _, pms = predict_raw(data, trees, PARAMS['learning_rate'], float(info.base_score), timing=True)
+        pbytes = data.nnz * 8.0 + data.n_rows * 8.0
+        predict = {'kernel_ms': pms, 'rows': data.n_rows, 'trees': int(trees.shape[0]), 'gbs': pbytes / (pms * 1e-3) / 1e9 if pms > 0 else None}
     b.close()
 
     # ---- end to end through the C ABI with host buffers -----------------------------------------
@@ -314,7 +323,7 @@ def main():
                      'partition_gbs': part_gbs, 'partition_frac': part_gbs / peak,
                      'hist_share_of_step': prof.hist_ms / ms if ms > 0 else None,
                      'partition_share_of_step': prof.partition_ms / ms if ms > 0 else None},
-        'e2e': e2e, 'gpu_launches': int(prof.kernel_launches), 'clocks': clocks,
+        'e2e': e2e, 'gpu_launches': int(prof.kernel_launches), 'clocks': clocks, 'predict': predict,
     }
     if world == 1 and not args.no_cpu_baseline:
         cores = os.cpu_count() or 1

@@ -132,6 +132,9 @@ void tgbm_booster_free(TgbmBooster *b);
  * tgbm_booster_get_trees: out[t * n_rows + i] */
 int tgbm_predict_raw(int n_rows, const float *val, const int *row_ptr, const int *col, const void *nodes, int n_rounds,
                      int trees_per_round, int n_nodes, float learning_rate, float base_score, float *out);
+/* the same, also returning the device time of the traversal kernel alone (measurement) */
+int tgbm_predict_raw_timed(int n_rows, const float *val, const int *row_ptr, const int *col, const void *nodes, int n_rounds,
+                     int trees_per_round, int n_nodes, float learning_rate, float base_score, float *out, float *kernel_ms);
 
 /* Metric::get_score of the objective's default metric (src/thundergbm/metric/*.cu, rank_metric.cpp) on raw scores
  * raw[t * n_rows + i]: RMSE, binary error, multi-class accuracy, MAP or NDCG.  `label` holds class indices for the

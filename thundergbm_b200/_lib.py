@@ -56,6 +56,7 @@ def load() -> C.CDLL:
     lib.tgbm_booster_get_cuts.argtypes = [vp, vp, vp]
     lib.tgbm_booster_free.argtypes = [vp]
     lib.tgbm_predict_raw.argtypes = [C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, vp]
+    lib.tgbm_predict_raw_timed.argtypes = [C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, vp, vp]
     lib.tgbm_metric_score.argtypes = [C.c_char_p, C.c_int, C.c_int, vp, vp, vp, C.c_int, fp]
     lib.tgbm_metric_score_noalloc.argtypes = [C.c_char_p, C.c_int, C.c_int, vp, vp, vp, vp]
     lib.sparse_train_scikit.argtypes = [C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float,

@@ -156,8 +156,9 @@ class Booster:
             pass
 
 
-def predict_raw(data, trees: np.ndarray, learning_rate: float, base_score: float) -> np.ndarray:
-    """Predictor::predict_raw on CSR rows; `trees` as returned by Booster.trees(); result [K][N]."""
+def predict_raw(data, trees: np.ndarray, learning_rate: float, base_score: float, timing: bool = False):
+    """Predictor::predict_raw on CSR rows; `trees` as returned by Booster.trees(); result [K][N].
+    timing=True returns (result, device milliseconds of the traversal kernel)."""
     lib = _lib.lib()
     val = np.ascontiguousarray(data.val, np.float32)
     rp = np.ascontiguousarray(data.row_ptr, np.int32)
@@ -165,6 +166,7 @@ def predict_raw(data, trees: np.ndarray, learning_rate: float, base_score: float
     trees = np.ascontiguousarray(trees)
     r, k, n = trees.shape
     out = np.empty((k, data.n_rows), np.float32)
-    _lib.check(lib.tgbm_predict_raw(data.n_rows, _ptr(val), _ptr(rp), _ptr(col), _ptr(trees), r, k, n,
-                                    learning_rate, base_score, _ptr(out)))
-    return out
+    ms = C.c_float(0)
+    _lib.check(lib.tgbm_predict_raw_timed(data.n_rows, _ptr(val), _ptr(rp), _ptr(col), _ptr(trees), r, k, n,
+                                          learning_rate, base_score, _ptr(out), C.byref(ms) if timing else None))
+    return (out, float(ms.value)) if timing else out

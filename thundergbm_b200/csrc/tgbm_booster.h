@@ -70,8 +70,9 @@ private:
 };
 
 // batch inference, Predictor::predict_raw (src/thundergbm/predictor.cu:32-189): out[t*N+i]
+// kernel_ms (optional): device time of the traversal kernel alone
 void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model, float learning_rate, float base_score,
-                 std::vector<float> &out);
+                 std::vector<float> &out, float *kernel_ms = nullptr);
 // ObjectiveFunction::predict_transform on raw scores (in place; may shrink `y`)
 void predict_transform(int objective, int num_class, const std::vector<float> &label, int n_rows, std::vector<float> &y);
 // Metric::get_score on raw scores of `ds`

@@ -412,6 +412,12 @@ int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, co
 
 int tgbm_predict_raw(int n_rows, const float *val, const int *row_ptr, const int *col, const void *nodes, int n_rounds,
                      int trees_per_round, int n_nodes, float learning_rate, float base_score, float *out) {
+    return tgbm_predict_raw_timed(n_rows, val, row_ptr, col, nodes, n_rounds, trees_per_round, n_nodes, learning_rate, base_score, out,
+                                  nullptr);
+}
+
+int tgbm_predict_raw_timed(int n_rows, const float *val, const int *row_ptr, const int *col, const void *nodes, int n_rounds,
+                           int trees_per_round, int n_nodes, float learning_rate, float base_score, float *out, float *kernel_ms) {
     return guard([&] {
         tgbm::GBMParam p;
         tgbm::DataSet ds;
@@ -426,7 +432,7 @@ int tgbm_predict_raw(int n_rows, const float *val, const int *row_ptr, const int
             }
         }
         std::vector<float> y;
-        tgbm::predict_raw(ds, m, learning_rate, base_score, y);
+        tgbm::predict_raw(ds, m, learning_rate, base_score, y, kernel_ms);
         std::copy(y.begin(), y.end(), out);
     });
 }

@@ -90,8 +90,44 @@ __global__ void k_predict_csr(const int *__restrict__ row_ptr, const int *__rest
     }
 }
 
+// The CSR path's arithmetic (float accumulator, fused multiply-add per tree) with the lookups of the dense path: the
+// rows of a tile are spread out in shared memory first, so that a visited node costs one shared-memory read instead
+// of a binary search through the row in global memory.  Used when the reference would take its CSR path
+// (F * 128 * 4 > 48 KB) and a tile still fits the 227 KB of a B200 SM.  A slot holding PRED_ABSENT was never stored.
+constexpr unsigned PRED_ABSENT = 0x7fc00b20u;  // a quiet NaN with a payload no computation produces
+__global__ void __launch_bounds__(PRED_ROWS)
+k_predict_csr_staged(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F,
+                     const PNode *__restrict__ model, int n_rounds, int K, int n_nodes, float lr, float base_score,
+                     float *__restrict__ out) {
+    extern __shared__ float dense[];  // [F][PRED_ROWS]
+    const int i = blockIdx.x * PRED_ROWS + threadIdx.x;
+    for (int f = 0; f < F; ++f) dense[f * PRED_ROWS + threadIdx.x] = __uint_as_float(PRED_ABSENT);
+    if (i >= n_rows) return;
+    for (int j = row_ptr[i]; j < row_ptr[i + 1]; ++j) {
+        const int c = col[j];
+        if (c >= 0 && c < F) dense[c * PRED_ROWS + threadIdx.x] = val[j];
+    }
+    for (int t = 0; t < K; ++t) {
+        float sum = base_score;
+        for (int r = 0; r < n_rounds; ++r) {
+            const PNode *nd = model + ((size_t)r * K + t) * n_nodes;
+            PNode cur = nd[0];
+            while (!(cur.fid & 0x80000000)) {
+                const int f = cur.fid & 0x3fffffff;
+                const float fv = f < F ? dense[f * PRED_ROWS + threadIdx.x] : __uint_as_float(PRED_ABSENT);
+                int nx;
+                if (__float_as_uint(fv) != PRED_ABSENT) nx = fv < cur.v ? cur.lch : cur.rch;
+                else nx = (cur.fid & 0x40000000) ? cur.rch : cur.lch;
+                cur = nd[nx];
+            }
+            sum = __fmaf_rn(lr, cur.v, sum);
+        }
+        out[(size_t)t * n_rows + i] = sum;
+    }
+}
+
 void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model, float learning_rate, float base_score,
-                 std::vector<float> &out) {
+                 std::vector<float> &out, float *kernel_ms) {
     const int N = ds.n_rows;
     const int n_rounds = (int)model.size();
     TGBM_CHECK(n_rounds > 0 && !model[0].empty(), "empty model");
@@ -126,16 +162,24 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     TGBM_CUDA(cudaMemcpyAsync(d_model.p, flat.data(), sizeof(PNode) * flat.size(), cudaMemcpyHostToDevice, st));
     const int F = ds.n_features;
     const size_t smem = (size_t)F * PRED_ROWS * sizeof(float);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&e0)); TGBM_CUDA(cudaEventCreate(&e1)); TGBM_CUDA(cudaEventRecord(e0, st)); }
     if (smem <= 48 * 1024) {
         k_predict_dense<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds, K,
                                                                                 n_nodes, learning_rate, base_score, d_out.p);
+    } else if (smem <= 200 * 1024) {
+        TGBM_CUDA(cudaFuncSetAttribute(k_predict_csr_staged, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        k_predict_csr_staged<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds,
+                                                                                     K, n_nodes, learning_rate, base_score, d_out.p);
     } else {
         k_predict_csr<<<(N + 127) / 128, 128, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, d_model.p, n_rounds, K, n_nodes, learning_rate,
                                                        base_score, d_out.p);
     }
     TGBM_CUDA(cudaGetLastError());
+    if (kernel_ms) TGBM_CUDA(cudaEventRecord(e1, st));
     TGBM_CUDA(cudaMemcpyAsync(out.data(), d_out.p, sizeof(float) * out.size(), cudaMemcpyDeviceToHost, st));
     TGBM_CUDA(cudaStreamSynchronize(st));
+    if (kernel_ms) { TGBM_CUDA(cudaEventElapsedTime(kernel_ms, e0, e1)); cudaEventDestroy(e0); cudaEventDestroy(e1); }
     cudaStreamDestroy(st);
 }
 
