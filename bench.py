@@ -284,11 +284,16 @@ def main():
             d2h = k * info.n_nodes * 48
             lib.model_free(C.byref(model))
         else:
+            ta = time.perf_counter()
             b2 = Booster(synth.CsrData(data.n_rows, data.n_cols, rp, col, val, y), comm=comm, n_trees=k, **PARAMS)
+            tb = time.perf_counter()
             b2.boost(k)
             trees = b2.trees()
+            tc = time.perf_counter()
             d2h = trees.nbytes
             b2.close()
+            if os.environ.get('BENCH_DEBUG'):
+                print(f'[rank {rank}] e2e: create {tb - ta:.3f} boost+trees {tc - tb:.3f} close {time.perf_counter() - tc:.3f}', file=sys.stderr)
         barrier()
         e2e_s = time.perf_counter() - t0
         t = torch.tensor([e2e_s], dtype=torch.float64, device='cuda')

@@ -75,15 +75,14 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
     return booster.get_model();
 }
 
-// distinct integer labels over all ranks (DataSet::group_label applied to the union)
-void group_label_global(tgbm::DataSet &ds, tgbm::GBMParam &p, const tgbm::Comm *comm) {
+// distinct integer labels over all ranks (DataSet::group_label applied to the union); the rows keep the caller's
+// label values, the booster maps them to class indices on the device
+void group_label_global(tgbm::DataSet &ds, const float *label, tgbm::GBMParam &p, const tgbm::Comm *comm) {
     constexpr int CAP = 4096;
-    std::vector<int> mine(ds.y.begin(), ds.y.end());
-    std::sort(mine.begin(), mine.end());
-    mine.erase(std::unique(mine.begin(), mine.end()), mine.end());
-    TGBM_CHECK((int)mine.size() <= CAP, "more than 4096 distinct labels");
+    ds.distinct_labels(label, (size_t)ds.n_rows);
+    TGBM_CHECK((int)ds.label.size() <= CAP, "more than 4096 distinct labels");
     std::vector<int> padded(CAP, INT_MAX);
-    std::copy(mine.begin(), mine.end(), padded.begin());
+    for (size_t i = 0; i < ds.label.size(); ++i) padded[i] = (int)ds.label[i];
     tgbm::DevBuf<int> d_in, d_out;
     d_in.alloc(CAP); d_out.alloc((size_t)CAP * comm->world);
     TGBM_CUDA(cudaMemcpy(d_in.p, padded.data(), sizeof(int) * CAP, cudaMemcpyHostToDevice));
@@ -94,10 +93,9 @@ void group_label_global(tgbm::DataSet &ds, tgbm::GBMParam &p, const tgbm::Comm *
     std::sort(all.begin(), all.end());
     all.erase(std::unique(all.begin(), all.end()), all.end());
     if (!all.empty() && all.back() == INT_MAX) all.pop_back();
-    std::map<float, int> m;
     ds.label.clear();
-    for (int v : all) { m[(float)v] = (int)ds.label.size(); ds.label.push_back((float)v); }
-    for (auto &v : ds.y) { auto it = m.find(v); v = it == m.end() ? 0.f : (float)it->second; }
+    for (int v : all) ds.label.push_back((float)v);
+    ds.labels_raw = true;
     p.num_class = (int)ds.label.size();
 }
 
@@ -314,8 +312,9 @@ TgbmBooster *tgbm_booster_create(int n_rows, const float *val, const int *row_pt
         if (c && c->active() && tgbm::need_group_label(tgbm::objective_from_name(b->param.objective))) {
             tgbm::GBMParam tmp = b->param;
             tmp.objective = "reg:linear";  // load without the per-rank label grouping
-            ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, tmp);
-            group_label_global(ds, b->param, c);
+            ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, tmp, /*lazy=*/true);
+            TGBM_CHECK(label != nullptr, "this objective needs labels");
+            group_label_global(ds, label, b->param, c);
         } else {
             ds.load_from_sparse(n_rows, val, row_ptr, col, label, group, num_group, b->param, /*lazy=*/true);
         }

@@ -137,16 +137,50 @@ void DataSet::load_group_file(const std::string &file) {
 }
 
 // src/thundergbm/dataset.cpp:106-320: LibSVM text, `label idx:val ...`, 1-based idx, '#' comments.
-void DataSet::load_from_file(const std::string &file, GBMParam &param) {
-    std::ifstream ifs(file, std::ifstream::binary);
-    TGBM_CHECK(ifs.is_open(), "file not found: " + file);
-    std::stringstream ss;
-    ss << ifs.rdbuf();
-    const std::string buf = ss.str();
-    row_ptr.assign(1, 0);
-    col.clear(); val.clear(); y.clear(); label.clear(); group.clear();
+// The buffer is cut at line ends into one piece per thread; the pieces are parsed independently and joined in order.
+namespace {
+struct SvmPiece {
+    std::vector<float> y, val;
+    std::vector<int> col, row_nnz;
     int maxf = 0;
-    const char *p = buf.data(), *end = p + buf.size();
+};
+// atof for the common short decimals: up to 15 digits and a power of ten up to 22 are exact in double, so one
+// multiplication or division gives the correctly rounded value (Clinger's fast path) -- the same double atof
+// returns.  Anything else (long mantissas, large exponents, inf/nan spellings) goes to atof itself.
+double fast_atof(const char *q, const char *stop) {
+    static const double p10[] = {1e0, 1e1, 1e2, 1e3, 1e4, 1e5, 1e6, 1e7, 1e8, 1e9, 1e10, 1e11,
+                                 1e12, 1e13, 1e14, 1e15, 1e16, 1e17, 1e18, 1e19, 1e20, 1e21, 1e22};
+    const char *c = q;
+    bool neg = false;
+    if (c < stop && (*c == '+' || *c == '-')) { neg = *c == '-'; ++c; }
+    unsigned long long m = 0;
+    int digits = 0, frac = 0;
+    bool any = false;
+    while (c < stop && *c >= '0' && *c <= '9') { m = m * 10 + (unsigned)(*c - '0'); digits += (m != 0); any = true; ++c; if (digits > 15) return atof(q); }
+    if (c < stop && *c == '.') {
+        ++c;
+        while (c < stop && *c >= '0' && *c <= '9') { m = m * 10 + (unsigned)(*c - '0'); digits += (m != 0); ++frac; any = true; ++c; if (digits > 15) return atof(q); }
+    }
+    if (!any) return atof(q);
+    int ex = 0;
+    if (c < stop && (*c == 'e' || *c == 'E')) {
+        ++c;
+        bool eneg = false;
+        if (c < stop && (*c == '+' || *c == '-')) { eneg = *c == '-'; ++c; }
+        if (!(c < stop && *c >= '0' && *c <= '9')) return atof(q);
+        while (c < stop && *c >= '0' && *c <= '9') { ex = ex * 10 + (*c - '0'); ++c; if (ex > 400) return atof(q); }
+        if (eneg) ex = -ex;
+    }
+    if (c < stop && (*c == '+' || *c == '-' || *c == '.' || *c == 'e' || *c == 'E' || *c == 'x' || *c == 'X' || *c == 'p' || *c == 'P'))
+        return atof(q);  // odd token (or a hex float): let atof decide
+    const int e10 = ex - frac;
+    if (e10 < -22 || e10 > 22) return atof(q);
+    double v = (double)m;
+    v = e10 < 0 ? v / p10[-e10] : v * p10[e10];
+    return neg ? -v : v;
+}
+
+void parse_svm_piece(const char *p, const char *end, SvmPiece &o) {
     auto is_num = [](char c) { return (c >= '0' && c <= '9') || c == '+' || c == '-' || c == '.' || c == 'e' || c == 'E'; };
     while (p < end) {
         const char *le = p;
@@ -156,7 +190,8 @@ void DataSet::load_from_file(const std::string &file, GBMParam &param) {
         for (const char *c = p; c < le; ++c) if (*c == '#') { stop = c; break; }
         while (q < stop && !is_num(*q)) ++q;
         if (q < stop) {
-            y.push_back((float)atof(q));
+            o.y.push_back((float)fast_atof(q, stop));
+            const size_t before = o.col.size();
             while (q < stop && is_num(*q)) ++q;
             while (q < stop) {
                 while (q < stop && !is_num(*q)) ++q;
@@ -169,16 +204,52 @@ void DataSet::load_from_file(const std::string &file, GBMParam &param) {
                     const int fid = atoi(a);
                     q = c + 1;
                     while (q < stop && !is_num(*q)) ++q;
-                    const float fv = (float)atof(q);
+                    const float fv = (float)fast_atof(q, stop);
                     while (q < stop && is_num(*q)) ++q;
-                    col.push_back(fid - 1);
-                    val.push_back(fv);
-                    maxf = std::max(maxf, fid);
+                    o.col.push_back(fid - 1);
+                    o.val.push_back(fv);
+                    o.maxf = std::max(o.maxf, fid);
                 }
             }
-            row_ptr.push_back((int)col.size());
+            o.row_nnz.push_back((int)(o.col.size() - before));
         }
         p = le + 1;
+    }
+}
+}  // namespace
+
+void DataSet::load_from_file(const std::string &file, GBMParam &param) {
+    std::ifstream ifs(file, std::ifstream::binary | std::ifstream::ate);
+    TGBM_CHECK(ifs.is_open(), "file not found: " + file);
+    std::string buf((size_t)std::max<std::streamoff>(0, ifs.tellg()), '\0');
+    ifs.seekg(0);
+    ifs.read(&buf[0], (std::streamsize)buf.size());
+    buf.resize((size_t)std::max<std::streamsize>(0, ifs.gcount()));
+    row_ptr.assign(1, 0);
+    col.clear(); val.clear(); y.clear(); label.clear(); group.clear();
+    const char *base = buf.data(), *end = base + buf.size();
+    const int nt = (int)std::max<size_t>(1, std::min<size_t>(16, buf.size() / (4u << 20)));
+    std::vector<const char *> cut(nt + 1, end);
+    cut[0] = base;
+    for (int t = 1; t < nt; ++t) {
+        const char *c = base + buf.size() * t / nt;
+        c = std::max(c, cut[t - 1]);
+        while (c < end && *c != '\n') ++c;
+        cut[t] = c < end ? c + 1 : end;
+    }
+    std::vector<SvmPiece> piece(nt);
+    {
+        std::vector<std::thread> th;
+        for (int t = 0; t < nt; ++t) th.emplace_back([&, t] { parse_svm_piece(cut[t], cut[t + 1], piece[t]); });
+        for (auto &x : th) x.join();
+    }
+    int maxf = 0;
+    for (auto &pc : piece) {
+        y.insert(y.end(), pc.y.begin(), pc.y.end());
+        col.insert(col.end(), pc.col.begin(), pc.col.end());
+        val.insert(val.end(), pc.val.begin(), pc.val.end());
+        for (int c : pc.row_nnz) row_ptr.push_back(row_ptr.back() + c);
+        maxf = std::max(maxf, pc.maxf);
     }
     n_rows = (int)y.size();
     n_features = maxf;
