@@ -235,7 +235,8 @@ def main():
             time.sleep(0.01)
     b.boost(w)
     b.sync()
-    b.set_profile(True)  # per-kernel CUDA events from here on: warm-up launches stay out of the profile
+    if not os.environ.get('BENCH_NO_PROFILE'):
+        b.set_profile(True)  # per-kernel CUDA events from here on: warm-up launches stay out of the profile
     barrier()
     sampler.mark()
     ms = b.boost_timed(k)

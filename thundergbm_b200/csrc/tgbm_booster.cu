@@ -62,6 +62,12 @@ struct BoosterImpl {
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     bool prune_in_smem = true;
+    DevBuf<RoundState> rstate;          // device copy of `rounds`
+    cudaGraph_t round_graph = nullptr;  // one boosting round (gradients, K trees, metric) as captured in its steady state
+    cudaGraphExec_t round_exec = nullptr;
+    long long round_graph_launches = 0;
+    bool graphs_allowed = true;
+    void run_round(int round);
     DevBuf<int> eval_ticket;  // k_eval: finished blocks per sibling pair, zero between launches
     bool grad_max_ready = false;        // maxbits holds the maxima of the next round's gradients
     bool metric_partial_ready = false;  // metric_partial holds the finished round's partial sums
@@ -83,6 +89,8 @@ struct BoosterImpl {
 
     ~BoosterImpl() {
         for (auto &e : events) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
+        if (round_exec) cudaGraphExecDestroy(round_exec);
+        if (round_graph) cudaGraphDestroy(round_graph);
         if (ev_scan) cudaEventDestroy(ev_scan);
         if (ev_plan) cudaEventDestroy(ev_plan);
         if (stream2) cudaStreamDestroy(stream2);
@@ -411,6 +419,9 @@ void Booster::init(const DataSet &ds) {
     m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
     m.hist_cta_off.alloc((size_t)m.num_sms + 1);
     m.eval_ticket.alloc(max_pairs);
+    m.rstate.alloc(1);
+    m.rstate.zero(m.stream);
+    m.graphs_allowed = getenv("TGBM_NO_GRAPH") == nullptr;
     m.eval_ticket.zero(m.stream);
     m.hist_seq.alloc((size_t)ceil_div(std::max(N, 1), HIST_THREADS) + max_pairs + 16);
     m.recs.alloc(((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
@@ -469,11 +480,9 @@ void BoosterImpl::gradient(int round) {
     if (comm && comm->active()) comm->allreduce(maxbits.p, 2, Comm::U32, Comm::MAX, stream);
     const int blocks = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
     k_quantize<<<dim3(blocks, K), tb, 0, stream>>>(have_max ? nullptr : gh.p, N, maxbits.p, p.quant_bits, (uint32_t)round, (uint32_t)row_offset,
-                                                   ghq.p, root_sum.p, qinfo.p, y.p, ypred.p, logistic);
+                                                   ghq.p, root_sum.p, qinfo.p, y.p, ypred.p, logistic, round >= 0 ? rstate.p : nullptr);
     ++launches;
     if (comm && comm->active()) comm->allreduce(root_sum.p, 2 * (size_t)K, Comm::I64, Comm::SUM, stream);
-    if (round >= 0 && round < (int)qinfo_log.n)
-        TGBM_CUDA(cudaMemcpyAsync(qinfo_log.p + round, qinfo.p, sizeof(QuantInfo), cudaMemcpyDeviceToDevice, stream));
 }
 
 // Base score (include/thundergbm/objective/regression_obj.h:35-53 and :95-114): gradients at y_pred = 0,
@@ -605,12 +614,16 @@ void BoosterImpl::build_tree(int round, int k) {
         grad_max_ready = metric_partial_ready = fuse;
     }
     launches += 2;
-    TGBM_CUDA(cudaMemcpyAsync(model.p + (size_t)tree_index * n_nodes, nodes.p, sizeof(TreeNode) * n_nodes, cudaMemcpyDeviceToDevice, stream));
+    k_store_tree<<<std::min(ceil_div(n_nodes, 256), 64), 256, 0, stream>>>(nodes.p, model.p, n_nodes, K, k, rstate.p);
+    ++launches;
 }
 
 void BoosterImpl::round_metric(int round) {
+    const int log_len = (int)qinfo_log.n;
     if (need_group_file(objective)) {
         rank.metric(objective, ypred.p, metric.p + round, comm, N_global, stream);
+        k_round_end<<<1, 32, 0, stream>>>(-1, nullptr, N_global, metric.p, qinfo.p, qinfo_log.p, log_len, rstate.p);
+        ++launches;
         return;
     }
     const int blocks = metric_blocks();
@@ -621,18 +634,53 @@ void BoosterImpl::round_metric(int round) {
     metric_partial_ready = false;
     k_metric_sum<<<1, 32, 0, stream>>>(metric_partial.p, blocks, metric_sum.p);
     if (comm && comm->active()) comm->allreduce(metric_sum.p, 1, Comm::F64, Comm::SUM, stream);
-    k_metric_final<<<1, 32, 0, stream>>>(objective, metric_sum.p, N_global, metric.p + round);
+    k_round_end<<<1, 32, 0, stream>>>(objective, metric_sum.p, N_global, metric.p, qinfo.p, qinfo_log.p, log_len, rstate.p);
     launches += 2;
+}
+
+// One boosting round.  From the second round on the launch sequence no longer changes (which kernels run is decided
+// by the objective and by flags that have reached their steady state; everything that depends on the data is decided
+// on the device), so it is captured once into a CUDA graph and replayed: one launch per round instead of ~60, no
+// gaps between the small per-level kernels.  Not with profiling events, a kept row->node table, ranking objectives
+// (their kernels take the round as a launch argument) or a communicator.
+void BoosterImpl::run_round(int round) {
+    auto direct = [&]() {
+        gradient(round);
+        for (int k = 0; k < K; ++k) build_tree(round, k);
+        round_metric(round);
+    };
+    const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid && !need_group_file(objective) &&
+                          !(comm && comm->active());
+    if (!graph_ok) { direct(); return; }
+    if (!round_exec) {
+        const long long before = launches;
+        TGBM_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        bool ok = true;
+        try { direct(); } catch (...) { ok = false; }
+        cudaGraph_t g = nullptr;
+        const cudaError_t rc = cudaStreamEndCapture(stream, &g);
+        round_graph_launches = launches - before;
+        launches = before;
+        if (!ok || rc != cudaSuccess || !g) {  // fall back to plain launches for good
+            if (g) cudaGraphDestroy(g);
+            cudaGetLastError();
+            graphs_allowed = false;
+            TGBM_CHECK(ok, "capturing a boosting round failed");
+            direct();
+            return;
+        }
+        round_graph = g;
+        TGBM_CUDA(cudaGraphInstantiate(&round_exec, round_graph, 0));
+    }
+    TGBM_CUDA(cudaGraphLaunch(round_exec, stream));
+    launches += round_graph_launches;
 }
 
 void Booster::boost(int n_rounds) {
     BoosterImpl &m = *impl_;
     TGBM_CHECK(m.rounds + n_rounds <= m.p.n_trees, "boost() beyond n_trees");
     for (int i = 0; i < n_rounds; ++i) {
-        const int round = m.rounds;
-        m.gradient(round);
-        for (int k = 0; k < m.K; ++k) m.build_tree(round, k);
-        m.round_metric(round);
+        m.run_round(m.rounds);
         ++m.rounds;
     }
     TGBM_CUDA(cudaGetLastError());

@@ -33,6 +33,12 @@ struct HistWork {  // one histogram to build at a level
 constexpr int HIST_SHARES = 2;
 constexpr int HIST_MAX_CTAS = 256;  // grid.x limit of the dense histogram kernel (one CTA per SM)
 
+// Device copy of the booster's round counter: kernels whose work depends on the round read it here, so that the launch
+// sequence of a round is the same every round and can be replayed as a CUDA graph.
+struct RoundState {
+    int round;
+};
+
 struct TreeCtl {  // device-side scalars of the tree being built
     int n_hist_tiles;
     int n_hist_work;
@@ -253,7 +259,9 @@ static __global__ void k_grad_softmax(const float *__restrict__ y, const float *
 static __global__ void k_quantize(const float2 *__restrict__ gh, int n, const unsigned *__restrict__ maxbits, int quant_bits,
                            uint32_t round, uint32_t row_offset, int2 *__restrict__ ghq,
                            unsigned long long *__restrict__ root_sum, QuantInfo *__restrict__ qinfo,
-                           const float *__restrict__ y, const float *__restrict__ yp, int logistic) {
+                           const float *__restrict__ y, const float *__restrict__ yp, int logistic,
+                           const RoundState *__restrict__ rs) {
+    if (rs) round = (uint32_t)rs->round;  // the booster's rounds; the base-score pass gives its own
     const int k = blockIdx.y;
     const int eg = exp_above(__uint_as_float(maxbits[0])), eh = exp_above(__uint_as_float(maxbits[1]));
     const double sg = pow2d(quant_bits - eg), sh = pow2d(quant_bits - eh);
@@ -1457,13 +1465,33 @@ static __global__ void k_metric_sum(const double *__restrict__ partial, int nb, 
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
     if (threadIdx.x == 0) *out = t;
 }
+__device__ __forceinline__ float metric_from_sum(int objective, double s, long long n_total) {
+    if (objective == REG_LINEAR || objective == REG_LOGISTIC) return sqrtf((float)s / (float)n_total);
+    if (objective == BINARY_LOGISTIC) return 1.0f - (float)(long long)s / (float)n_total;
+    return (float)(long long)s / (float)n_total;
+}
 static __global__ void k_metric_final(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ out) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) *out = metric_from_sum(objective, *sum, n_total);
+}
+
+// End of a boosting round: the round's metric (objective < 0: already written by the ranking metric), the round's
+// fixed-point grid for the log, and the device round counter moves on.  One thread.
+static __global__ void k_round_end(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ metric,
+                                   const QuantInfo *__restrict__ qinfo, QuantInfo *__restrict__ qinfo_log, int log_len,
+                                   RoundState *__restrict__ rs) {
     if (threadIdx.x == 0 && blockIdx.x == 0) {
-        const double s = *sum;
-        if (objective == REG_LINEAR || objective == REG_LOGISTIC) *out = sqrtf((float)s / (float)n_total);
-        else if (objective == BINARY_LOGISTIC) *out = 1.0f - (float)(long long)s / (float)n_total;
-        else *out = (float)(long long)s / (float)n_total;
+        const int r = rs->round;
+        if (objective >= 0) metric[r] = metric_from_sum(objective, *sum, n_total);
+        if (r < log_len) qinfo_log[r] = *qinfo;
+        rs->round = r + 1;
     }
+}
+
+// The finished tree into its slot of the model: tree (round * K + k)
+static __global__ void k_store_tree(const TreeNode *__restrict__ nodes, TreeNode *__restrict__ model, int n_nodes, int K, int k,
+                                    const RoundState *__restrict__ rs) {
+    TreeNode *dst = model + ((size_t)rs->round * K + k) * n_nodes;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n_nodes; i += gridDim.x * blockDim.x) dst[i] = nodes[i];
 }
 
 static __global__ void k_fill(float *p, size_t n, float v) {
