@@ -158,6 +158,48 @@ def test_cli_train_and_predict(gpu, tmp_path):
     assert abs(rmse_pred - rmse_train) < 1e-4
 
 
+def test_cli_text_loader_is_exact(gpu, tmp_path):
+    """The LibSVM loader (threads + a fast path for short decimals) reads every spelling to the float atof gives:
+    the trees trained from the text file equal the trees trained from the same values handed over as CSR."""
+    import subprocess
+    from thundergbm_b200 import synth
+    from thundergbm_b200.booster import Booster
+    from common import NODE_DTYPE
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d = synth.dense_regression(60000, 8, seed=9)     # ~6 MB of text: parsed in several pieces
+    spell = ['%.9g', '%.8e', '%+.9g', '%.17g', '%.9G']
+    data = tmp_path / 'train.txt'
+    with open(data, 'w') as fh:
+        fh.write('# a comment line\n')
+        for i in range(d.n_rows):
+            a, b = d.row_ptr[i], d.row_ptr[i + 1]
+            f = spell[i % len(spell)]
+            fh.write((f % d.y[i]) + ' ' + ' '.join(f'{c + 1}:' + (f % v) for c, v in zip(d.col[a:b], d.val[a:b])))
+            fh.write('  # trailing comment\n' if i % 97 == 0 else ('\r\n' if i % 89 == 0 else '\n'))
+    conf = tmp_path / 'run.conf'
+    conf.write_text(f'data={data}\ndepth=5\nn_trees=4\nlearning_rate=0.5\nobjective=reg:linear\n')
+    out = subprocess.run([os.path.join(root, 'thundergbm_b200', 'bin', 'thundergbm-train'), str(conf)], cwd=tmp_path,
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert f'#instances = {d.n_rows}' in out.stdout
+    b = Booster(d, objective='reg:linear', depth=5, n_trees=4, learning_rate=0.5)
+    b.boost(4)
+    want = b.trees()
+    b.close()
+    # tail of the model file (src/thundergbm/parser.cpp:146-171): i32 rounds, then per round i32 trees and per tree
+    # u64 nodes + the 48-byte node records
+    raw = open(tmp_path / 'tgbm.model', 'rb').read()
+    n_rounds, _, n_nodes = want.shape
+    per_round = 4 + 8 + 48 * n_nodes
+    tail = raw[len(raw) - (4 + n_rounds * per_round):]
+    assert int.from_bytes(tail[:4], 'little') == n_rounds
+    for r in range(n_rounds):
+        rec = tail[4 + r * per_round: 4 + (r + 1) * per_round]
+        assert int.from_bytes(rec[:4], 'little') == 1 and int.from_bytes(rec[4:12], 'little') == n_nodes
+        assert rec[12:] == want[r, 0].tobytes(), f'tree {r} differs'
+
+
+
 def test_metric_score_entry_point(gpu, orc, cases):
     """tgbm_metric_score on the raw training scores reproduces the per-round metric of training."""
     from thundergbm_b200 import _lib

@@ -62,6 +62,7 @@ struct BoosterImpl {
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     bool prune_in_smem = true;
+    TreeCtl stat_base{};  // counters of `ctl` when profiling was switched on
     DevBuf<RoundState> rstate;          // device copy of `rounds`
     cudaGraph_t round_graph = nullptr;  // one boosting round (gradients, K trees, metric) as captured in its steady state
     cudaGraphExec_t round_exec = nullptr;
@@ -515,7 +516,7 @@ void BoosterImpl::build_tree(int round, int k) {
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
-                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p);
+                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * 2));
@@ -580,7 +581,7 @@ void BoosterImpl::build_tree(int round, int k) {
         TGBM_CUDA(cudaEventRecord(ev_scan, stream));
         TGBM_CUDA(cudaStreamWaitEvent(stream2, ev_scan, 0));
         k_plan_next<<<1, 1024, 0, stream2>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, nodes.p, ctl.p, by_hessian, built_right.p,
-                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p);
+                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth);
         TGBM_CUDA(cudaEventRecord(ev_plan, stream2));
         k_part_scatter<<<std::max(1, part_ctas - 1), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
                                                                                 node_tile0[cur].p, ctl.p, idx_in, gh_in, bits.p, tile_left.p,
@@ -700,7 +701,14 @@ int Booster::n_bins() const { return impl_->B; }
 int Booster::n_features() const { return impl_->F; }
 int Booster::fpad() const { return impl_->Fpad; }
 cudaStream_t Booster::stream() const { return impl_->stream; }
-void Booster::set_profile(bool on) { impl_->profile_on = on; }
+void Booster::set_profile(bool on) {
+    BoosterImpl &m = *impl_;
+    if (on && !m.profile_on && m.ctl.p) {  // the byte counters of the plan kernels run all the time: remember where profiling starts
+        sync();
+        TGBM_CUDA(cudaMemcpy(&m.stat_base, m.ctl.p, sizeof(TreeCtl), cudaMemcpyDeviceToHost));
+    }
+    m.profile_on = on;
+}
 
 HistProfile Booster::profile() {
     BoosterImpl &m = *impl_;
@@ -720,9 +728,11 @@ HistProfile Booster::profile() {
     // algorithmic bytes: rows * (F bin bytes + 8 gradient bytes [+ 4 row index]) + histograms * B * 16 written
     // per row: its bin ids (F bytes dense; 4 bytes per stored value + a row pointer in the CSR layout), 8 gradient bytes
     const double row_bytes = m.sparse ? 4.0 * (double)m.nnz_local / std::max(1, m.N) + 4.0 : (double)m.F;
-    r.hist_root_bytes = (double)c.stat_rows_root * (row_bytes + 8);
-    r.hist_bytes = r.hist_root_bytes + (double)c.stat_rows_gather * (row_bytes + 8 + 4) + (double)c.stat_hists * m.B * 16.0;
-    r.partition_bytes = (double)c.stat_part_rows * (4 + 1 + 4);
+    const TreeCtl &c0 = m.stat_base;
+    r.hist_root_bytes = (double)(c.stat_rows_root - c0.stat_rows_root) * (row_bytes + 8);
+    r.hist_bytes = r.hist_root_bytes + (double)(c.stat_rows_gather - c0.stat_rows_gather) * (row_bytes + 8 + 4) +
+                   (double)(c.stat_hists - c0.stat_hists) * m.B * 16.0;
+    r.partition_bytes = (double)(c.stat_part_rows - c0.stat_part_rows) * (4 + 1 + 4);
     r.kernel_launches = m.launches;
     return r;
 }

@@ -1069,7 +1069,7 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
 // Every node of the level that holds records gets ceil(count / PART_TILE) tiles of 4096 records;
 // node_tile0[n] is the first tile of node n.  Called by every thread of a 1024-thread block.
 __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0,
-                                 TreeCtl *__restrict__ ctl) {
+                                 TreeCtl *__restrict__ ctl, bool count_rows = true) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     const int nl = 1 << level;
@@ -1083,7 +1083,7 @@ __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int
     if (threadIdx.x == 0) {
         node_tile0[nl] = total;
         ctl->n_part_tiles[level & 1] = total;
-        ctl->stat_part_rows += rows;
+        if (count_rows) ctl->stat_part_rows += rows;  // the last level is not partitioned (k_predict_walk)
     }
 }
 
@@ -1198,10 +1198,10 @@ static __global__ void __launch_bounds__(1024)
 k_plan_next(int level, const int *__restrict__ next_begin, const int *__restrict__ next_cnt, const int *__restrict__ gcnt,
             const TreeNode *__restrict__ nodes, TreeCtl *__restrict__ ctl, int by_hessian, int *__restrict__ built_right,
             HistWork *__restrict__ work, int *__restrict__ hist_tile_base, int *__restrict__ next_node_tile0, int n_ctas,
-            int *__restrict__ cta_off, int4 *__restrict__ seq) {
+            int *__restrict__ cta_off, int4 *__restrict__ seq, int depth) {
     hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(level + 1, next_cnt, next_node_tile0, ctl);
+    part_plan(level + 1, next_cnt, next_node_tile0, ctl, level + 1 < depth - 1);
 }
 
 // work lists of level 0 (the whole data set in the root)
@@ -1209,10 +1209,10 @@ static __global__ void __launch_bounds__(1024)
 k_plan_root(const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt, const int *__restrict__ gcnt,
             const TreeNode *__restrict__ nodes, int *__restrict__ built_right, HistWork *__restrict__ work,
             int *__restrict__ hist_tile_base, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl, int n_ctas, int *__restrict__ cta_off,
-            int4 *__restrict__ seq) {
+            int4 *__restrict__ seq, int depth) {
     hist_plan(0, seg_begin, seg_cnt, gcnt, nodes, 0, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(0, seg_cnt, node_tile0, ctl);
+    part_plan(0, seg_cnt, node_tile0, ctl, depth > 1);
 }
 
 // Stable scatter of the records into the child segments; records of nodes that stopped splitting are dropped.
