@@ -650,8 +650,9 @@ void BoosterImpl::run_round(int round) {
         for (int k = 0; k < K; ++k) build_tree(round, k);
         round_metric(round);
     };
+    static const bool graph_with_comm = getenv("TGBM_GRAPH_COMM") != nullptr;  // collectives inside the captured round
     const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid && !need_group_file(objective) &&
-                          !(comm && comm->active());
+                          (graph_with_comm || !(comm && comm->active()));
     if (!graph_ok) { direct(); return; }
     if (!round_exec) {
         const long long before = launches;
