@@ -102,13 +102,13 @@ def test_csr_layout_ragged_shapes(gpu, orc, n, f, density, monkeypatch):
 
 
 def test_csr_layout_many_bins_per_feature(gpu, orc, monkeypatch):
-    """Features with 255 bins each: every evaluation chunk holds one feature; 40 features = 10k bins, more than the
-    shared-memory part of the sparse histogram."""
+    """Features with 255 bins each: every evaluation chunk holds one feature; 60 features = 15k bins, more than the
+    shared-memory part of the sparse histogram (12288 bins)."""
     monkeypatch.setenv('TGBM_LAYOUT', 'sparse')
-    d = _rand_csr(20000, 40, 0.6, seed=11)
+    d = _rand_csr(20000, 60, 0.6, seed=11)
     p = dict(objective='reg:linear', depth=6, n_trees=3, max_num_bin=255, learning_rate=0.3)
     o, b = _pair(orc, d, **p)
-    assert b.info.csr_layout == 1 and b.info.n_bins > 6144
+    assert b.info.csr_layout == 1 and b.info.n_bins > 12288
     assert b.trees().tobytes() == o.trees.tobytes() and np.array_equal(b.ypred(), o.ypred)
     b.close()
 

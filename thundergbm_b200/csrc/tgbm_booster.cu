@@ -535,7 +535,7 @@ void BoosterImpl::build_tree(int round, int k) {
             cudaEventRecord(ev.a, stream);
         }
         if (sparse) {
-            const int sp_ctas = num_sms * 2;
+            const int sp_ctas = num_sms;
             const size_t sp_smem = (size_t)std::min(B, SPARSE_SMEM_BINS) * 16;
             if (level == 0)
                 k_hist_sparse<false><<<sp_ctas, SPARSE_THREADS, sp_smem, stream>>>(sp_row_ptr.p, sp_bin.p, nullptr, gh_in, hist_work.p,

@@ -666,11 +666,11 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
 // shared memory; with Zipf-like column frequencies most updates hit the lowest column ids, so the first
 // SPARSE_SMEM_BINS bins are accumulated per CTA in shared memory (int64 atomics) and the long tail goes straight to
 // the node's histogram with global int64 atomics (L2-resident: 16 B per bin).  One warp per row, lanes over its values.
-constexpr int SPARSE_SMEM_BINS = 6144;
-constexpr int SPARSE_THREADS = 256;
+constexpr int SPARSE_SMEM_BINS = 12288;  // 192 KB of int64 (g, h) cells
+constexpr int SPARSE_THREADS = 1024;    // one CTA per SM
 
 template <bool GATHER>
-static __global__ void __launch_bounds__(SPARSE_THREADS)
+static __global__ void __launch_bounds__(SPARSE_THREADS, 1)
 k_hist_sparse(const int *__restrict__ row_ptr, const int *__restrict__ bin, const int *__restrict__ rec_idx,
               const int2 *__restrict__ rec_gh, const HistWork *__restrict__ work, const int *__restrict__ tile_base,
               const TreeCtl *__restrict__ ctl, long long *__restrict__ slab, int B) {
@@ -709,12 +709,32 @@ k_hist_sparse(const int *__restrict__ row_ptr, const int *__restrict__ bin, cons
         long long *dst = slab + (size_t)it.slab * B * 2;
         const int first = (t - tile_base[w]) * HIST_THREADS;
         const int last = min(it.count, first + HIST_THREADS);
-        for (int q = first + warp; q < last; q += SPARSE_THREADS / 32) {
-            const int p = it.begin + q;
-            const int r = GATHER ? rec_idx[p] : p;
-            const int2 v = rec_gh[p];
-            for (int j = row_ptr[r] + lane; j < row_ptr[r + 1]; j += 32) {
-                const int b = bin[j];
+        // A warp takes every 32nd row of the tile.  Three rows are in flight per warp: the row pointers and gradients
+        // of the row after next, the first 32 bin ids of the next row, and the row being accumulated -- a row is a
+        // chain of three dependent loads (record -> row pointers -> bin ids) and would otherwise cost three memory
+        // latencies each.
+        constexpr int W = SPARSE_THREADS / 32;
+        auto meta = [&](int q, int &j0, int &j1, int2 &v) {
+            j0 = j1 = 0; v = make_int2(0, 0);
+            if (q < last) {
+                const int p = it.begin + q;
+                const int r = GATHER ? rec_idx[p] : p;
+                v = rec_gh[p];
+                j0 = row_ptr[r]; j1 = row_ptr[r + 1];
+            }
+        };
+        int q = first + warp;
+        int j0, j1, nj0, nj1, mj0, mj1;
+        int2 v, nv, mv;
+        meta(q, j0, j1, v);
+        meta(q + W, nj0, nj1, nv);
+        int b0 = j0 + lane < j1 ? bin[j0 + lane] : -1;
+        for (; q < last; q += W) {
+            meta(q + 2 * W, mj0, mj1, mv);
+            const int nb0 = nj0 + lane < nj1 ? bin[nj0 + lane] : -1;
+            int b = b0;
+            for (int j = j0 + lane; j < j1; j += 32) {
+                if (j != j0 + lane) b = bin[j];
                 if (b < nsm) {
                     atomicAdd(reinterpret_cast<unsigned long long *>(sh_sparse + 2 * b), (unsigned long long)(long long)v.x);
                     atomicAdd(reinterpret_cast<unsigned long long *>(sh_sparse + 2 * b + 1), (unsigned long long)(long long)v.y);
@@ -723,6 +743,8 @@ k_hist_sparse(const int *__restrict__ row_ptr, const int *__restrict__ bin, cons
                     atomicAdd(reinterpret_cast<unsigned long long *>(dst + 2 * b + 1), (unsigned long long)(long long)v.y);
                 }
             }
+            j0 = nj0; j1 = nj1; v = nv; b0 = nb0;
+            nj0 = mj0; nj1 = mj1; nv = mv;
         }
     }
     flush(work[w_cur].slab);
