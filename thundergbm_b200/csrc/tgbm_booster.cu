@@ -473,7 +473,7 @@ void BoosterImpl::gradient(int round) {
             case MULTI_SOFTMAX: case MULTI_SOFTPROB:
                 k_grad_softmax<<<gb, tb, 0, stream>>>(y.p, ypred.p, N, K, gh.p, maxbits.p); break;
             case RANK_PAIRWISE: case RANK_NDCG:
-                rank.gradient(round, p.rank_seed, ypred.p, gh.p, maxbits.p, stream); break;
+                rank.gradient(rstate.p, p.rank_seed, ypred.p, gh.p, maxbits.p, stream); break;
             }
             ++launches;
         }
@@ -622,8 +622,8 @@ void BoosterImpl::build_tree(int round, int k) {
 void BoosterImpl::round_metric(int round) {
     const int log_len = (int)qinfo_log.n;
     if (need_group_file(objective)) {
-        rank.metric(objective, ypred.p, metric.p + round, comm, N_global, stream);
-        k_round_end<<<1, 32, 0, stream>>>(-1, nullptr, N_global, metric.p, qinfo.p, qinfo_log.p, log_len, rstate.p);
+        rank.metric(objective, ypred.p, nullptr, comm, N_global, stream);
+        k_round_end<<<1, 32, 0, stream>>>(objective, rank.sum.p, rank.n_group_total, metric.p, qinfo.p, qinfo_log.p, log_len, rstate.p);
         ++launches;
         return;
     }
@@ -642,8 +642,8 @@ void BoosterImpl::round_metric(int round) {
 // One boosting round.  From the second round on the launch sequence no longer changes (which kernels run is decided
 // by the objective and by flags that have reached their steady state; everything that depends on the data is decided
 // on the device), so it is captured once into a CUDA graph and replayed: one launch per round instead of ~60, no
-// gaps between the small per-level kernels.  Not with profiling events, a kept row->node table, ranking objectives
-// (their kernels take the round as a launch argument) or a communicator.
+// gaps between the small per-level kernels.  Not with profiling events, a kept row->node table or (unless asked for) a
+// communicator.
 void BoosterImpl::run_round(int round) {
     auto direct = [&]() {
         gradient(round);
@@ -651,7 +651,7 @@ void BoosterImpl::run_round(int round) {
         round_metric(round);
     };
     static const bool graph_with_comm = getenv("TGBM_GRAPH_COMM") != nullptr;  // collectives inside the captured round
-    const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid && !need_group_file(objective) &&
+    const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid &&
                           (graph_with_comm || !(comm && comm->active()));
     if (!graph_ok) { direct(); return; }
     if (!round_exec) {

@@ -1490,13 +1490,14 @@ static __global__ void k_metric_sum(const double *__restrict__ partial, int nb, 
 __device__ __forceinline__ float metric_from_sum(int objective, double s, long long n_total) {
     if (objective == REG_LINEAR || objective == REG_LOGISTIC) return sqrtf((float)s / (float)n_total);
     if (objective == BINARY_LOGISTIC) return 1.0f - (float)(long long)s / (float)n_total;
+    if (objective == RANK_PAIRWISE || objective == RANK_NDCG) return (float)(s / (double)n_total);  // mean over the query groups
     return (float)(long long)s / (float)n_total;
 }
 static __global__ void k_metric_final(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ out) {
     if (threadIdx.x == 0 && blockIdx.x == 0) *out = metric_from_sum(objective, *sum, n_total);
 }
 
-// End of a boosting round: the round's metric (objective < 0: already written by the ranking metric), the round's
+// End of a boosting round: the round's metric (for ranking `sum` and `n_total` are those of the query groups), the round's
 // fixed-point grid for the log, and the device round counter moves on.  One thread.
 static __global__ void k_round_end(int objective, const double *__restrict__ sum, long long n_total, float *__restrict__ metric,
                                    const QuantInfo *__restrict__ qinfo, QuantInfo *__restrict__ qinfo_log, int log_len,

@@ -53,9 +53,10 @@ __device__ inline float disc_gain(int label, int rank, const float *__restrict__
 // LambdaRank::get_gradient for one query group per CTA
 static __global__ void __launch_bounds__(256)
 k_lambdarank(const int *__restrict__ gptr, const float *__restrict__ y, const float *__restrict__ yp, const float *__restrict__ idcg,
-             const float *__restrict__ log2tab, int ndcg, uint32_t seed, uint32_t round, uint32_t group_offset,
+             const float *__restrict__ log2tab, int ndcg, uint32_t seed, const RoundState *__restrict__ rs, uint32_t group_offset,
              float2 *__restrict__ gh, unsigned *__restrict__ maxbits) {
     extern __shared__ __align__(16) unsigned char sm[];
+    const uint32_t round = (uint32_t)rs->round;  // read on the device: the launch is the same every round
     const int k = blockIdx.x;
     const int s0 = gptr[k], len = gptr[k + 1] - s0;
     int P = 1;
@@ -215,19 +216,20 @@ struct RankState {
     }
     int pow2_len() const { int P = 1; while (P < max_len) P <<= 1; return P; }
 
-    void gradient(int round, uint32_t seed, const float *yp, float2 *gh, unsigned *maxbits, cudaStream_t stream) {
+    void gradient(const RoundState *rs, uint32_t seed, const float *yp, float2 *gh, unsigned *maxbits, cudaStream_t stream) {
         if (!n_group) return;
         TGBM_CUDA(cudaMemsetAsync(gh, 0, sizeof(float2) * (size_t)N, stream));
         const int P = pow2_len();
-        k_lambdarank<<<n_group, 256, 40 * (size_t)P, stream>>>(gptr.p, y.p, yp, idcg.p, log2tab.p, idcg_used, seed, (uint32_t)round,
+        k_lambdarank<<<n_group, 256, 40 * (size_t)P, stream>>>(gptr.p, y.p, yp, idcg.p, log2tab.p, idcg_used, seed, rs,
                                                              group_offset, gh, maxbits);
     }
+    // `out` null: the sum of the group scores stays in `sum` (the caller finishes the metric)
     void metric(int objective, const float *yp, float *out, const Comm *comm, long long, cudaStream_t stream) {
         const int P = pow2_len();
         if (n_group) k_rank_metric<<<n_group, 256, 12 * (size_t)P, stream>>>(gptr.p, y.p, yp, idcg.p, log2tab.p, objective == RANK_NDCG, group_score.p);
         k_rank_metric_sum<<<1, 32, 0, stream>>>(group_score.p, n_group, sum.p);
         if (comm && comm->active()) comm->allreduce(sum.p, 1, Comm::F64, Comm::SUM, stream);
-        k_rank_metric_final<<<1, 32, 0, stream>>>(sum.p, n_group_total, out);
+        if (out) k_rank_metric_final<<<1, 32, 0, stream>>>(sum.p, n_group_total, out);
     }
     int idcg_used = 0;
 };
