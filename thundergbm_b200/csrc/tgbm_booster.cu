@@ -642,15 +642,15 @@ void BoosterImpl::round_metric(int round) {
 // One boosting round.  From the second round on the launch sequence no longer changes (which kernels run is decided
 // by the objective and by flags that have reached their steady state; everything that depends on the data is decided
 // on the device), so it is captured once into a CUDA graph and replayed: one launch per round instead of ~60, no
-// gaps between the small per-level kernels.  Not with profiling events, a kept row->node table or (unless asked for) a
-// communicator.
+// gaps between the small per-level kernels.  Not with profiling events or a kept row->node table.  With a communicator
+// the NCCL calls of the round are captured with it (every rank captures and replays the same sequence).
 void BoosterImpl::run_round(int round) {
     auto direct = [&]() {
         gradient(round);
         for (int k = 0; k < K; ++k) build_tree(round, k);
         round_metric(round);
     };
-    static const bool graph_with_comm = getenv("TGBM_GRAPH_COMM") != nullptr;  // collectives inside the captured round
+    static const bool graph_with_comm = getenv("TGBM_NO_GRAPH_COMM") == nullptr;  // the round's collectives are captured with it
     const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid &&
                           (graph_with_comm || !(comm && comm->active()));
     if (!graph_ok) { direct(); return; }
