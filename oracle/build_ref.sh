@@ -13,7 +13,7 @@
 #   2. src/thundergbm/builder/*.cu: bare `cuda::par` is ambiguous with libcu++'s
 #      ::cuda namespace under CUDA 12.x -> `thrust::cuda::par`.
 #
-# Usage: oracle/build_ref.sh [reference_dir]     (default /root/reference)
+# Usage: oracle/build_ref.sh [reference_dir]     (default: where the reference checkout is mounted)
 set -euo pipefail
 REF=${1:-/root/reference}
 HERE=$(cd "$(dirname "$0")" && pwd)

@@ -1,5 +1,5 @@
 """Packs what the reference produced on a B200 (tests/golden/run_reference.sh, outputs under
-gpurun_out/golden/<case>/) into small committed fixtures tests/golden/ref_<case>.npz:
+<out_dir>/<case>/) into small committed fixtures tests/golden/ref_<case>.npz:
 
   cut_val, cut_ptr     cut points of HistCut::get_cut_points_single, complete
   bins_sha256, bins_head   global bin ids of get_bin_ids: digest of the int32 array + its first 4096 entries
@@ -8,7 +8,7 @@ gpurun_out/golden/<case>/) into small committed fixtures tests/golden/ref_<case>
   metric               the per-round training metric the reference logged
   raw_pred_sample      every 37th raw prediction on the training rows + digest of the whole array
 
-    python tests/golden/pack_golden.py [gpurun_out/golden]
+    python tests/golden/pack_golden.py <out_dir>      (the folder run_reference.sh wrote to)
 """
 from __future__ import annotations
 

@@ -1,13 +1,14 @@
 #!/usr/bin/env bash
 # Runs the reference (built by oracle/build_ref.sh) on every golden input on a GPU
-# box and leaves its outputs under gpurun_out/golden/<case>/ : cut points, global
-# bin ids, model file, raw predictions and the log with the per-round metric.
+# box and leaves its outputs under <out_dir>/<case>/ : cut points, global bin ids,
+# model file, raw predictions and the log with the per-round metric.
 # tests/golden/pack_golden.py turns those outputs into the committed fixtures.
+# usage: run_reference.sh [out_dir]
 set -u
 ROOT=$(cd "$(dirname "$0")/../.." && pwd)
 IN=$ROOT/oracle/_ref/inputs
 BIN=$ROOT/oracle/_ref/bin
-OUT=$ROOT/gpurun_out/golden
+OUT=${1:-$ROOT/gpurun_out/golden}
 mkdir -p "$OUT"
 for args in "$IN"/*.args; do
   name=$(basename "$args" .args)
