@@ -136,7 +136,7 @@ int tgbm_predict_raw(int n_rows, const float *val, const int *row_ptr, const int
 int tgbm_predict_raw_timed(int n_rows, const float *val, const int *row_ptr, const int *col, const void *nodes, int n_rounds,
                      int trees_per_round, int n_nodes, float learning_rate, float base_score, float *out, float *kernel_ms);
 
-/* Metric::get_score of the objective's default metric (src/thundergbm/metric/*.cu, rank_metric.cpp) on raw scores
+/* Metric::get_score of the objective's default metric (the .cu files under src/thundergbm/metric, rank_metric.cpp) on raw scores
  * raw[t * n_rows + i]: RMSE, binary error, multi-class accuracy, MAP or NDCG.  `label` holds class indices for the
  * classification objectives.  Host pointers; device buffers and reduction scratch are allocated inside. */
 int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, const float *label, const float *raw,

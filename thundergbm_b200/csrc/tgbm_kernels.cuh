@@ -520,7 +520,7 @@ k_hist(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__res
        long long *__restrict__ slab, int B, int window_rows) {
     extern __shared__ __align__(16) int sh_hist[];  // int32 g,h: [2][256][32]; int64 totals g,h: [2][256][32]
     int *acc = sh_hist;
-    int *hg = acc, *hh = acc + 256 * 32;
+    int *hg = acc;  // g accumulators; the h accumulators follow at +256*32
     long long *tot = reinterpret_cast<long long *>(sh_hist + 2 * 256 * 32);
 
     const int group = blockIdx.y;
