@@ -89,6 +89,8 @@ struct BoosterImpl {
     long long launches = 0;
 
     ~BoosterImpl() {
+        if (stream) cudaStreamSynchronize(stream);    // nothing of this booster is in flight when its buffers go
+        if (stream2) cudaStreamSynchronize(stream2);
         for (auto &e : events) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
         if (round_exec) cudaGraphExecDestroy(round_exec);
         if (round_graph) cudaGraphDestroy(round_graph);

@@ -779,6 +779,9 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
         if (lane == 0 && warp < n_children) recs[(size_t)node_local * F + f] = none;
         return;
     }
+    // asked for now, used after the histogram loads below: one memory latency instead of two
+    const TreeNode nd = nodes[off + (warp < n_children ? node_local : 0)];
+    const double inv_sg = q->inv_sg, inv_sh = q->inv_sh;
     if (level == 0) {
         for (int i = threadIdx.x; i < nb; i += 64) { sg[0][i] = built[2 * (b0 + i)]; sh[0][i] = built[2 * (b0 + i) + 1]; }
     } else {
@@ -795,7 +798,6 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
     }
     __syncthreads();
     if (warp >= n_children) return;
-    const TreeNode nd = nodes[off + node_local];
     if (!nd.is_valid) {
         if (lane == 0) recs[(size_t)node_local * F + f] = none;
         return;
@@ -818,14 +820,14 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
     const long long base_g = ig - tg, base_h = ih - th;
     const long long tot_g = shfl_ll(ig, 31), tot_h = shfl_ll(ih, 31);
     const float pg = nd.sum_g, ph = nd.sum_h;
-    const float mg = __fsub_rn(pg, q2f(tot_g, q->inv_sg)), mh = __fsub_rn(ph, q2f(tot_h, q->inv_sh));
+    const float mg = __fsub_rn(pg, q2f(tot_g, inv_sg)), mh = __fsub_rn(ph, q2f(tot_h, inv_sh));
     float best = 0.f, best_lg = 0.f, best_lh = 0.f;
     int best_bin = -1;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int b = lane * 8 + i;
         if (b < nb) {
-            const float lg = q2f(base_g + lg8[i], q->inv_sg), lh = q2f(base_h + lh8[i], q->inv_sh);
+            const float lg = q2f(base_g + lg8[i], inv_sg), lh = q2f(base_h + lh8[i], inv_sh);
             const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
             const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
             const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
