@@ -76,7 +76,7 @@ struct BoosterImpl {
     DevBuf<int> hist_cta_off;  // dense histogram kernel: tile sequence of every CTA
     DevBuf<int4> hist_seq;
     DevBuf<SplitRec> recs;
-    DevBuf<int> node_tile0[2], tile_left;
+    DevBuf<int> node_tile0[2], tile_left, tile_node[2];
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
     DevBuf<double> metric_partial, metric_sum;
@@ -430,6 +430,7 @@ void Booster::init(const DataSet &ds) {
     m.recs.alloc(((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
     m.tile_left.alloc(m.max_tiles);
+    m.tile_node[0].alloc(m.max_tiles); m.tile_node[1].alloc(m.max_tiles);
     m.node_tile0[0].alloc(((size_t)1 << depth) + 1); m.node_tile0[1].alloc(((size_t)1 << depth) + 1);
     m.bits.alloc((size_t)m.max_tiles * (PART_TILE / 32));
     m.ctl.alloc(1);
@@ -518,7 +519,7 @@ void BoosterImpl::build_tree(int round, int k) {
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
-                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth);
+                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[0].p);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * 2));
@@ -572,10 +573,10 @@ void BoosterImpl::build_tree(int round, int k) {
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
         if (sparse)
             k_part_count<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                                       idx_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, bits.p, tile_left.p);
+                                                                       idx_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p);
         else
             k_part_count<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                                        idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p);
+                                                                        idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p);
         k_part_scan<<<1, 1024, 0, stream>>>(level, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
                                             seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p);
         // the next level's plan runs beside the scatter: launched first so that it gets its SM slot, while the
@@ -583,11 +584,11 @@ void BoosterImpl::build_tree(int round, int k) {
         TGBM_CUDA(cudaEventRecord(ev_scan, stream));
         TGBM_CUDA(cudaStreamWaitEvent(stream2, ev_scan, 0));
         k_plan_next<<<1, 1024, 0, stream2>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, nodes.p, ctl.p, by_hessian, built_right.p,
-                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth);
+                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p);
         TGBM_CUDA(cudaEventRecord(ev_plan, stream2));
         k_part_scatter<<<std::max(1, part_ctas - 1), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
                                                                                 node_tile0[cur].p, ctl.p, idx_in, gh_in, bits.p, tile_left.p,
-                                                                                seg_begin[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p);
+                                                                                seg_begin[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, tile_node[cur].p);
         TGBM_CUDA(cudaStreamWaitEvent(stream, ev_plan, 0));
         if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
         launches += 4;

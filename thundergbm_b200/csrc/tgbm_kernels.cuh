@@ -1091,9 +1091,11 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
 // ------------------------------------------------------------------ instance partition
 // (replaces update_ins2node_id + the per-level radix sort, hist_tree_builder_single.cu:908-1020, :397-415)
 // Every node of the level that holds records gets ceil(count / PART_TILE) tiles of 4096 records;
-// node_tile0[n] is the first tile of node n.  Called by every thread of a 1024-thread block.
+// node_tile0[n] is the first tile of node n, tile_node[t] the node of tile t (looked up here, off the critical path,
+// so that the partition kernels do not search for it tile after tile).  Called by every thread of a 1024-thread block.
+__device__ inline int tile_owner(const int *__restrict__ node_tile0, int nl, int t);
 __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0,
-                                 TreeCtl *__restrict__ ctl, bool count_rows = true) {
+                                 int *__restrict__ tile_node, TreeCtl *__restrict__ ctl, bool count_rows = true) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     const int nl = 1 << level;
@@ -1109,6 +1111,8 @@ __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int
         ctl->n_part_tiles[level & 1] = total;
         if (count_rows) ctl->stat_part_rows += rows;  // the last level is not partitioned (k_predict_walk)
     }
+    __syncthreads();
+    for (int t = threadIdx.x; t < total; t += 1024) tile_node[t] = tile_owner(node_tile0, nl, t);
 }
 
 // node that owns tile t: the n with node_tile0[n] <= t < node_tile0[n + 1]
@@ -1132,16 +1136,13 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
              const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
              const unsigned char *__restrict__ binsT, size_t Npad, const int *__restrict__ sp_row_ptr,
              const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr, unsigned *__restrict__ bits,
-             int *__restrict__ tile_left) {
+             int *__restrict__ tile_left, const int *__restrict__ tile_node) {
     __shared__ int wsum[32];
-    __shared__ int sh_n;
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = blockIdx.x; t < nt; t += gridDim.x) {
-        __syncthreads();
-        if (threadIdx.x == 0) sh_n = tile_owner(node_tile0, nl, t);
-        __syncthreads();
-        const int n = sh_n;
+        __syncthreads();  // wsum of the previous tile has been read
+        const int n = tile_node[t];
         const TreeNode nd = nodes[nl - 1 + n];
         if (!(nd.is_valid && !nd.is_leaf)) { if (threadIdx.x == 0) tile_left[t] = 0; continue; }
         const int p0 = seg_begin[n] + (t - node_tile0[n]) * PART_TILE, end = seg_begin[n] + seg_cnt[n];
@@ -1222,10 +1223,10 @@ static __global__ void __launch_bounds__(1024)
 k_plan_next(int level, const int *__restrict__ next_begin, const int *__restrict__ next_cnt, const int *__restrict__ gcnt,
             const TreeNode *__restrict__ nodes, TreeCtl *__restrict__ ctl, int by_hessian, int *__restrict__ built_right,
             HistWork *__restrict__ work, int *__restrict__ hist_tile_base, int *__restrict__ next_node_tile0, int n_ctas,
-            int *__restrict__ cta_off, int4 *__restrict__ seq, int depth) {
+            int *__restrict__ cta_off, int4 *__restrict__ seq, int depth, int *__restrict__ next_tile_node) {
     hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(level + 1, next_cnt, next_node_tile0, ctl, level + 1 < depth - 1);
+    part_plan(level + 1, next_cnt, next_node_tile0, next_tile_node, ctl, level + 1 < depth - 1);
 }
 
 // work lists of level 0 (the whole data set in the root)
@@ -1233,10 +1234,10 @@ static __global__ void __launch_bounds__(1024)
 k_plan_root(const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt, const int *__restrict__ gcnt,
             const TreeNode *__restrict__ nodes, int *__restrict__ built_right, HistWork *__restrict__ work,
             int *__restrict__ hist_tile_base, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl, int n_ctas, int *__restrict__ cta_off,
-            int4 *__restrict__ seq, int depth) {
+            int4 *__restrict__ seq, int depth, int *__restrict__ tile_node) {
     hist_plan(0, seg_begin, seg_cnt, gcnt, nodes, 0, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(0, seg_cnt, node_tile0, ctl, depth > 1);
+    part_plan(0, seg_cnt, node_tile0, tile_node, ctl, depth > 1);
 }
 
 // Stable scatter of the records into the child segments; records of nodes that stopped splitting are dropped.
@@ -1245,18 +1246,15 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
                const int *__restrict__ seg_cnt, const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl,
                const int *__restrict__ rec_idx, const int2 *__restrict__ rec_gh, const unsigned *__restrict__ bits,
                const int *__restrict__ tile_left, const int *__restrict__ next_begin,
-               int *__restrict__ out_idx, int2 *__restrict__ out_gh) {
+               int *__restrict__ out_idx, int2 *__restrict__ out_gh, const int *__restrict__ tile_node) {
     constexpr int WORDS = PART_TILE / 32;  // 128
     __shared__ int wpre[WORDS];
     __shared__ int wtot[4];
-    __shared__ int sh_n;
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = blockIdx.x; t < nt; t += gridDim.x) {
-        __syncthreads();
-        if (threadIdx.x == 0) sh_n = tile_owner(node_tile0, nl, t);
-        __syncthreads();
-        const int n = sh_n;
+        __syncthreads();  // wpre / wtot of the previous tile have been read
+        const int n = tile_node[t];
         const TreeNode nd = nodes[nl - 1 + n];
         const int b = seg_begin[n], end = b + seg_cnt[n];
         const int t0 = node_tile0[n];
