@@ -522,7 +522,7 @@ void BoosterImpl::build_tree(int round, int k) {
                                         node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[0].p);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
-    const int part_ctas = std::max(1, std::min(max_tiles, num_sms * 2));
+    const int part_ctas = std::max(1, std::min(max_tiles, num_sms * (2048 / PART_THREADS)));
     for (int level = 0; level < depth; ++level) {
         const int cur = level & 1, nxt = cur ^ 1;
         const int nl = 1 << level, pairs = std::max(1, nl / 2);
@@ -580,13 +580,13 @@ void BoosterImpl::build_tree(int round, int k) {
         k_part_scan<<<1, 1024, 0, stream>>>(level, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
                                             seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p);
         // the next level's plan runs beside the scatter: launched first so that it gets its SM slot, while the
-        // scatter leaves one of its 2 x SMs block slots free
+        // scatter leaves 1024 threads' worth of its block slots free
         TGBM_CUDA(cudaEventRecord(ev_scan, stream));
         TGBM_CUDA(cudaStreamWaitEvent(stream2, ev_scan, 0));
         k_plan_next<<<1, 1024, 0, stream2>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, nodes.p, ctl.p, by_hessian, built_right.p,
                                              hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p);
         TGBM_CUDA(cudaEventRecord(ev_plan, stream2));
-        k_part_scatter<<<std::max(1, part_ctas - 1), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
+        k_part_scatter<<<std::max(1, part_ctas - 1024 / PART_THREADS), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
                                                                                 node_tile0[cur].p, ctl.p, idx_in, gh_in, bits.p, tile_left.p,
                                                                                 seg_begin[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, tile_node[cur].p);
         TGBM_CUDA(cudaStreamWaitEvent(stream, ev_plan, 0));

@@ -19,7 +19,7 @@
 namespace tgbm {
 
 constexpr int HIST_THREADS = 1024;  // one CTA per SM: 64 KB of int32 accumulators + up to 128 KB of int64 totals
-constexpr int PART_THREADS = 1024;
+constexpr int PART_THREADS = 512;  // 512 x 4 records per tile measured best (1024: fewer tiles in flight per SM, 256: longer tile scan)
 constexpr int PART_RPT = 4;         // records per thread
 constexpr int PART_TILE = PART_THREADS * PART_RPT;
 constexpr int MISSING_BIN = 255;
@@ -1090,7 +1090,7 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
 
 // ------------------------------------------------------------------ instance partition
 // (replaces update_ins2node_id + the per-level radix sort, hist_tree_builder_single.cu:908-1020, :397-415)
-// Every node of the level that holds records gets ceil(count / PART_TILE) tiles of 4096 records;
+// Every node of the level that holds records gets ceil(count / PART_TILE) tiles of PART_TILE records;
 // node_tile0[n] is the first tile of node n, tile_node[t] the node of tile t (looked up here, off the critical path,
 // so that the partition kernels do not search for it tile after tile).  Called by every thread of a 1024-thread block.
 __device__ inline int tile_owner(const int *__restrict__ node_tile0, int nl, int t);
@@ -1177,12 +1177,12 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
         for (int j = 0; j < PART_RPT; ++j) {
             const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (b[j] < nd.split_bid));
             const unsigned m = __ballot_sync(0xffffffffu, left);
-            if (lane == 0) { bits[(size_t)t * (PART_TILE / 32) + j * 32 + warp] = m; cnt += __popc(m); }
+            if (lane == 0) { bits[(size_t)t * (PART_TILE / 32) + j * (PART_THREADS / 32) + warp] = m; cnt += __popc(m); }
         }
         if (lane == 0) wsum[warp] = cnt;
         __syncthreads();
         if (warp == 0) {
-            int v = wsum[lane];
+            int v = lane < PART_THREADS / 32 ? wsum[lane] : 0;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == 0) tile_left[t] = v;
@@ -1247,9 +1247,9 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
                const int *__restrict__ rec_idx, const int2 *__restrict__ rec_gh, const unsigned *__restrict__ bits,
                const int *__restrict__ tile_left, const int *__restrict__ next_begin,
                int *__restrict__ out_idx, int2 *__restrict__ out_gh, const int *__restrict__ tile_node) {
-    constexpr int WORDS = PART_TILE / 32;  // 128
+    constexpr int WORDS = PART_TILE / 32;
     __shared__ int wpre[WORDS];
-    __shared__ int wtot[4];
+    __shared__ int wtot[(WORDS + 31) / 32];
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int t = blockIdx.x; t < nt; t += gridDim.x) {
@@ -1269,9 +1269,9 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
             const int p = p0 + j * PART_THREADS + threadIdx.x;
             r[j] = p < end ? (rec_idx ? rec_idx[p] : p) : -1;
             if (p < end) g[j] = rec_gh[p];
-            m[j] = bits[(size_t)t * WORDS + j * 32 + warp];
+            m[j] = bits[(size_t)t * WORDS + j * (PART_THREADS / 32) + warp];
         }
-        // exclusive prefix of the left counts over the tile's 128 ballot words (record order = word order)
+        // exclusive prefix of the left counts over the tile's ballot words (record order = word order)
         if (threadIdx.x < WORDS) {
             const int c = __popc(bits[(size_t)t * WORDS + threadIdx.x]);
             int v = c;
@@ -1287,7 +1287,7 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
         for (int j = 0; j < PART_RPT; ++j) {
             if (r[j] < 0) continue;
             const int p = p0 + j * PART_THREADS + threadIdx.x;
-            const int w = j * 32 + warp;
+            const int w = j * (PART_THREADS / 32) + warp;
             int pre = wpre[w];
             for (int q = 0; q < (w >> 5); ++q) pre += wtot[q];
             const bool left = (m[j] >> lane) & 1u;
