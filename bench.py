@@ -292,8 +292,13 @@ def main():
             if not model.value:
                 raise SystemExit('sparse_train_scikit failed: ' + lib.tgbm_last_error().decode())
             lib.model_free(C.byref(model))
+        # untimed warm-up of the same entry point (allocator state after the first booster's frees)
         if world == 1:
-            scikit_call(3)  # untimed warm-up of the same entry point (allocator state after the first booster's frees)
+            scikit_call(3)
+        else:
+            bw = Booster(synth.CsrData(data.n_rows, data.n_cols, rp, col, val, y), comm=comm, n_trees=3, **PARAMS)
+            bw.boost(3)
+            bw.close()
         barrier()
         t0 = time.perf_counter()
         if world == 1:
