@@ -156,6 +156,24 @@ def test_boost_in_pieces_equals_one_call(gpu, cases):
     a.close(); b.close()
 
 
+def test_graph_replay_and_plain_launches_mix(gpu, cases, monkeypatch):
+    """Rounds replayed as a CUDA graph, rounds launched kernel by kernel (profiling on, or TGBM_NO_GRAPH) and any mix of
+    the two give the same trees and the same per-round metrics."""
+    d, params = cases('c2_higgs_small')
+    p = {**params, 'n_trees': 9}
+    a = _booster(d, p); a.boost(9)
+    b = _booster(d, p)
+    b.boost(3); b.set_profile(True); b.boost(2); b.set_profile(False); b.boost(3); b.set_profile(True); b.boost(1)
+    prof = b.profile()
+    assert prof.hist_launches == 3 * p['depth'] and prof.hist_ms > 0
+    monkeypatch.setenv('TGBM_NO_GRAPH', '1')
+    c = _booster(d, p); c.boost(9)
+    assert a.trees().tobytes() == b.trees().tobytes() == c.trees().tobytes()
+    assert np.array_equal(a.metrics(), b.metrics()) and np.array_equal(a.metrics(), c.metrics())
+    assert np.array_equal(a.quant_scale(), b.quant_scale())
+    a.close(); b.close(); c.close()
+
+
 def test_predict_raw_against_oracle(gpu, orc, cases):
     for name in ('c1_dense_reg', 'c3_covtype_small', 'c5_mslr_small', 'c4_sparse_small'):
         from thundergbm_b200.booster import predict_raw

@@ -56,8 +56,19 @@ std::vector<std::vector<tgbm::Tree>> wrap_model(::Tree *model, int n_trees, int 
 std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSet &ds, const tgbm::Comm *comm) {
     TGBM_CHECK(p.tree_method == "hist" || p.tree_method == "auto", "tree_method=" + p.tree_method +
                " is outside this library: only the histogram builder (tree_method=hist) is implemented");
+    const bool timing = getenv("TGBM_TIMING") != nullptr;  // phase times on stderr
+    auto t_mark = std::chrono::steady_clock::now();
+    auto lap = [&](const char *what) {
+        if (!timing) return;
+        const auto t = std::chrono::steady_clock::now();
+        fprintf(stderr, "[tgbm train] %-26s %8.1f ms\n", what, std::chrono::duration<double, std::milli>(t - t_mark).count());
+        t_mark = t;
+    };
+    std::vector<std::vector<tgbm::Tree>> result;
+    {
     tgbm::Booster booster(p, comm);
     booster.init(ds);  // counts the features when the data set has not
+    lap("init");
     if (p.tree_method == "auto") p.tree_method = booster.n_features() > 20000 ? "exact" : "hist";  // trainer.cu:19-23
     TGBM_CHECK(p.tree_method == "hist", "tree_method=auto resolves to exact above 20000 features"
                " (src/thundergbm/trainer.cu:19-23), which is outside this library: ask for tree_method=hist");
@@ -65,6 +76,7 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
     booster.boost(p.n_trees);
     booster.sync();
     const auto t1 = std::chrono::high_resolution_clock::now();
+    lap("boost");
     const auto metrics = booster.get_metrics();
     for (size_t i = 0; i < metrics.size(); ++i)  // include/thundergbm/booster.h:91-92
         tgbm::log_info("[%zu/%d] %s = %g", i + 1, p.n_trees, tgbm::metric_name(tgbm::objective_from_name(p.objective)), metrics[i]);
@@ -72,7 +84,11 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
     p.base_score = booster.base_score();
     p.num_class = booster.num_class();
     p.tree_per_rounds = booster.trees_per_round();
-    return booster.get_model();
+    result = booster.get_model();
+    lap("metrics + model read-back");
+    }
+    lap("booster teardown");
+    return result;
 }
 
 // distinct integer labels over all ranks (DataSet::group_label applied to the union); the rows keep the caller's
