@@ -46,8 +46,8 @@ PARAMS = dict(objective='binary:logistic', depth=8, max_num_bin=255, learning_ra
 WORKLOAD = 'higgs-shape 10.5M x 28 f32, binary:logistic, depth 8, 255 bins, lr 0.1, lambda 1'
 SAMPLE_ROWS = 1_000_000
 # dram__bytes_read.sum + dram__bytes_write.sum per k_hist launch, mean of the eight launches of one tree captured with
-# ncu (root 424.3 MB, levels 1-7 332 to 401 MB; profiles/k_hist_higgs_10p5M_x28.md)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 363.4e6
+# ncu (root 425.0 MB, levels 1-7 331 to 397 MB; profiles/k_hist_higgs_10p5M_x28.md)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 363.1e6
 
 
 def measured_peaks():
