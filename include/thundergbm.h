@@ -78,6 +78,9 @@ typedef struct {
     int verbose;
     int profile;        /* time the histogram and partition kernels with CUDA events */
     unsigned rank_seed; /* LambdaRank partner sampling */
+    int hist_mode;      /* histogram arithmetic: 0 fp32 -- float (g,h) added value by value into one accumulator per bin,
+                           what the reference does (hist_tree_builder_single.cu:203-216, :485-505); 1 exact -- integer sums
+                           on a fixed-point grid, bit-identical from run to run and for any number of GPUs */
 } TgbmParam;
 
 typedef struct {
@@ -121,7 +124,8 @@ int tgbm_booster_get_cuts(TgbmBooster *b, float *cut_val, int *cut_ptr); /* n_bi
 int tgbm_booster_get_bins(TgbmBooster *b, unsigned char *out);       /* dense layout: n_rows * fpad, 255 = missing */
 int tgbm_booster_get_bins_csr(TgbmBooster *b, int *out);             /* CSR layout: global bin id per stored value */
 int tgbm_booster_get_nid(TgbmBooster *b, int *out);                  /* rounds_done*trees_per_round*n_rows (keep_nid) */
-int tgbm_booster_get_root_hist(TgbmBooster *b, long long *out);      /* n_bins*2 of the last tree */
+int tgbm_booster_get_root_hist(TgbmBooster *b, long long *out);      /* exact mode: n_bins*2 of the last tree */
+int tgbm_booster_get_root_hist_f32(TgbmBooster *b, float *out);      /* fp32 mode: n_bins*2 of the last tree */
 int tgbm_booster_get_quant_scale(TgbmBooster *b, double *out);       /* rounds_done*2 */
 int tgbm_booster_get_labels(TgbmBooster *b, float *out);             /* n_labels */
 /* hands the trained trees over as the opaque model of part 1 */

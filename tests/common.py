@@ -46,3 +46,32 @@ def compare_tree_decisive(ref, mine, gain2, rel_margin=1e-4):
             if a['lch_index'] < len(ref):
                 stack.extend([int(a['lch_index']), int(a['rch_index'])])
     return same, bad
+
+
+def walk_same_path(a, b):
+    """Walks two trees from the root for as long as both split on the same (feature, bin).  Returns the relative gain
+    differences of the identically split nodes, the weight differences of every node reached that way (relative to
+    max(|weight|, 1 % of the tree's largest weight): a weight -G/(H+lambda) near zero is a cancellation and has no
+    meaningful relative error) and the nodes where the two trees part."""
+    gains, weights, parted = [], [], []
+    wfloor = 0.01 * float(np.max(np.abs(a['base_weight'][a['is_valid'] != 0]))) if (a['is_valid'] != 0).any() else 0.0
+    stack = [0]
+    while stack:
+        i = stack.pop()
+        x, y = a[i], b[i]
+        if not x['is_valid'] or not y['is_valid']:
+            if bool(x['is_valid']) != bool(y['is_valid']):
+                parted.append(i)
+            continue
+        weights.append(abs(float(x['base_weight']) - float(y['base_weight'])) / max(abs(float(x['base_weight'])), wfloor, 1e-30))
+        xs = x['split_feature_id'] >= 0 and x['gain'] > 0 and x['lch_index'] > 0
+        ys = y['split_feature_id'] >= 0 and y['gain'] > 0 and y['lch_index'] > 0
+        if xs != ys or (xs and (x['split_feature_id'] != y['split_feature_id'] or x['split_bid'] != y['split_bid'])):
+            parted.append(i)
+            continue
+        if xs:
+            gains.append(abs(float(x['gain']) - float(y['gain'])) / abs(float(x['gain'])))
+            # a split whose children were pruned back keeps its fields; children beyond the table do not exist
+            if x['lch_index'] < len(a):
+                stack.extend([int(x['lch_index']), int(x['rch_index'])])
+    return dict(gains=np.asarray(gains), weights=np.asarray(weights), parted=parted)

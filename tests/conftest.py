@@ -9,6 +9,11 @@ for p in (ROOT, os.path.join(ROOT, 'oracle'), os.path.join(ROOT, 'tests', 'golde
         sys.path.insert(0, p)
 
 
+# The parity tests written against the oracle's exact mode (bit-for-bit comparisons) run the library in its
+# deterministic mode; the tests of the fp32 mode (the library's default, tests/test_gpu_fp32.py) ask for it by name.
+os.environ.setdefault('TGBM_HIST_MODE', 'exact')
+
+
 def pytest_configure(config):
     config.addinivalue_line('markers', 'gpu: needs a CUDA device (run with -m gpu on a B200)')
 

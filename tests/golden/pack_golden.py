@@ -1,5 +1,5 @@
 """Packs what the reference produced on a B200 (tests/golden/run_reference.sh, outputs under
-<out_dir>/<case>/) into small committed fixtures tests/golden/ref_<case>.npz:
+<run_dir>/<case>/) into small committed fixtures tests/golden/ref_<case>.npz:
 
   cut_val, cut_ptr     cut points of HistCut::get_cut_points_single, complete
   bins_sha256, bins_head   global bin ids of get_bin_ids: digest of the int32 array + its first 4096 entries
@@ -7,8 +7,16 @@
   base_score, label, num_class
   metric               the per-round training metric the reference logged
   raw_pred_sample      every 37th raw prediction on the training rows + digest of the whole array
+  logloss              mean negative log-likelihood of the training labels under the reference's raw scores
+                       (classification objectives; the reference itself logs only error / accuracy)
+  spread_*             how far further runs of the reference on the same input sit from the packed one
+                       (its histograms are unordered float atomics): per-round metric, raw predictions,
+                       logloss, gains and node weights of the first tree along identically split paths
 
-    python tests/golden/pack_golden.py <out_dir>      (the folder run_reference.sh wrote to)
+    python tests/golden/pack_golden.py <run_dir> [--rerun <run_dir2> ...] [--out <dir>] [--shrink]
+
+--shrink replaces <case>/csr_bin_id.i32 by its digest (bins_digest.npz) so that a large case can be
+carried off the GPU box; packing accepts either form.
 """
 from __future__ import annotations
 
@@ -21,6 +29,13 @@ import sys
 import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+sys.path.insert(0, os.path.join(HERE, '..'))
+
+NODE_DTYPE = np.dtype([('final_id', '<i4'), ('lch_index', '<i4'), ('rch_index', '<i4'), ('parent_index', '<i4'),
+                       ('gain', '<f4'), ('base_weight', '<f4'), ('split_feature_id', '<i4'), ('split_value', '<f4'),
+                       ('split_bid', 'u1'), ('default_right', 'u1'), ('is_leaf', 'u1'), ('is_valid', 'u1'),
+                       ('is_pruned', 'u1'), ('pad', 'u1', (3,)), ('sum_g', '<f4'), ('sum_h', '<f4')])
 
 
 def read_model(path):
@@ -44,27 +59,120 @@ def read_model(path):
                 trees=np.stack(rounds))
 
 
-def main(src):
+def logloss(objective, raw, y, label):
+    """Mean negative log-likelihood from raw scores, evaluated in float64.  `y` holds the caller's label values,
+    `label` the sorted distinct ones (class index = position).  None for objectives without class probabilities."""
+    if objective == 'binary:logistic':
+        cls = np.searchsorted(label, y).astype(np.float64)
+        z = raw.astype(np.float64).reshape(-1)
+        # -[c log s(z) + (1-c) log(1-s(z))] = softplus(z) - c z
+        return float(np.mean(np.logaddexp(0.0, z) - cls * z))
+    if objective in ('multi:softmax', 'multi:softprob'):
+        k = label.size
+        z = raw.astype(np.float64).reshape(k, -1)
+        cls = np.searchsorted(label, y)
+        lse = np.logaddexp.reduce(z, axis=0)
+        return float(np.mean(lse - z[cls, np.arange(z.shape[1])]))
+    return None
+
+
+def metrics_of(log):
+    return [float(x) for x in re.findall(r'\[\d+/\d+\] [^=]+ = ([-+0-9.eEnNaA]+)', log)]
+
+
+def tree_view(trees_u8):
+    r, k, nb = trees_u8.shape
+    return trees_u8.reshape(r, k, nb // 48, 48).copy().view(NODE_DTYPE).reshape(r, k, nb // 48)
+
+
+def spread(primary, others):
+    """Largest distance of the further runs from the packed one.  Gains and node weights of the first tree are compared
+    along the paths on which both runs split identically (common.walk_same_path); spread_parted_tree0 counts the nodes
+    of the first tree at which some run chose another split (a near-tie decided by the order of the float atomics)."""
+    from common import walk_same_path
+    out = dict(spread_runs=len(others), spread_metric=0.0, spread_raw_max=0.0, spread_logloss=0.0,
+               spread_gain_tree0=0.0, spread_root_gain=0.0, spread_weight_tree0=0.0, spread_parted_tree0=0,
+               spread_first_diff_tree=-1)
+    T = tree_view(primary['trees'])
+    for o in others:
+        n = min(len(primary['metric']), len(o['metric']))
+        if n:
+            out['spread_metric'] = max(out['spread_metric'], float(np.max(np.abs(np.asarray(primary['metric'][:n]) - np.asarray(o['metric'][:n])))))
+        out['spread_raw_max'] = max(out['spread_raw_max'], float(np.max(np.abs(primary['raw'] - o['raw']))))
+        if primary['logloss'] is not None:
+            out['spread_logloss'] = max(out['spread_logloss'], abs(primary['logloss'] - o['logloss']))
+        t = tree_view(o['trees'])
+        w = walk_same_path(T[0, 0], t[0, 0])
+        if w['gains'].size:
+            out['spread_gain_tree0'] = max(out['spread_gain_tree0'], float(w['gains'].max()))
+            out['spread_root_gain'] = max(out['spread_root_gain'], float(w['gains'][0]))
+        if w['weights'].size:
+            out['spread_weight_tree0'] = max(out['spread_weight_tree0'], float(w['weights'].max()))
+        out['spread_parted_tree0'] = max(out['spread_parted_tree0'], len(w['parted']))
+        for r in range(T.shape[0]):
+            keys = ('is_valid', 'is_leaf', 'split_feature_id', 'split_bid', 'is_pruned')
+            if any(not np.array_equal(T[r][f], t[r][f]) for f in keys):
+                if out['spread_first_diff_tree'] < 0 or r < out['spread_first_diff_tree']:
+                    out['spread_first_diff_tree'] = r
+                break
+    return out
+
+
+def load_run(g, y):
+    m = read_model(os.path.join(g, 'tgbm.model'))
+    raw = np.fromfile(os.path.join(g, 'raw_pred.f32'), np.float32)
+    log = open(os.path.join(g, 'log.txt')).read()
+    return dict(model=m, trees=m['trees'], raw=raw, metric=metrics_of(log), logloss=logloss(m['objective'], raw, y, m['label']))
+
+
+def bins_digest(g):
+    d = os.path.join(g, 'bins_digest.npz')
+    if os.path.exists(d):
+        z = np.load(d)
+        return z['sha256'], z['head'], int(z['n'])
+    bins = np.fromfile(os.path.join(g, 'csr_bin_id.i32'), np.int32)
+    return np.frombuffer(hashlib.sha256(bins.tobytes()).digest(), np.uint8), bins[:4096].copy(), bins.size
+
+
+def main(argv):
+    src, reruns, out, shrink = None, [], HERE, False
+    i = 0
+    while i < len(argv):
+        if argv[i] == '--rerun': reruns.append(argv[i + 1]); i += 2
+        elif argv[i] == '--out': out = argv[i + 1]; i += 2
+        elif argv[i] == '--shrink': shrink = True; i += 1
+        else: src = argv[i]; i += 1
+    if src is None:
+        raise SystemExit(__doc__)
+    from make_inputs import CASES
+    os.makedirs(out, exist_ok=True)
     for name in sorted(os.listdir(src)):
         g = os.path.join(src, name)
-        if not os.path.exists(os.path.join(g, 'tgbm.model')) or not os.path.exists(os.path.join(g, 'cut_val.f32')):
+        if name not in CASES or not os.path.exists(os.path.join(g, 'tgbm.model')) or not os.path.exists(os.path.join(g, 'cut_val.f32')):
             continue
-        m = read_model(os.path.join(g, 'tgbm.model'))
-        bins = np.fromfile(os.path.join(g, 'csr_bin_id.i32'), np.int32)
-        raw = np.fromfile(os.path.join(g, 'raw_pred.f32'), np.float32)
-        log = open(os.path.join(g, 'log.txt')).read()
-        metric = [float(x) for x in re.findall(r'\[\d+/\d+\] [^=]+ = ([-+0-9.eEnNaA]+)', log)]
+        if shrink and os.path.exists(os.path.join(g, 'csr_bin_id.i32')):
+            sha, head, n = bins_digest(g)
+            np.savez(os.path.join(g, 'bins_digest.npz'), sha256=sha, head=head, n=n)
+            os.remove(os.path.join(g, 'csr_bin_id.i32'))
+        y = CASES[name][0]().y
+        run = load_run(g, y)
+        m = run['model']
+        others = [load_run(os.path.join(r, name), y) for r in reruns if os.path.exists(os.path.join(r, name, 'tgbm.model'))]
+        sha, head, n_bins = bins_digest(g)
+        raw = run['raw']
+        extra = spread(run, others) if others else dict(spread_runs=0)
         np.savez_compressed(
-            os.path.join(HERE, f'ref_{name}.npz'),
+            os.path.join(out, f'ref_{name}.npz'),
             cut_val=np.fromfile(os.path.join(g, 'cut_val.f32'), np.float32),
             cut_ptr=np.fromfile(os.path.join(g, 'cut_row_ptr.i32'), np.int32),
-            bins_sha256=np.frombuffer(hashlib.sha256(bins.tobytes()).digest(), np.uint8), bins_head=bins[:4096],
-            n_bin_ids=bins.size, trees=m['trees'], base_score=np.float32(m['base_score']), label=m['label'],
-            num_class=m['num_class'], learning_rate=np.float32(m['learning_rate']), metric=np.asarray(metric, np.float32),
+            bins_sha256=sha, bins_head=head, n_bin_ids=n_bins, trees=m['trees'], base_score=np.float32(m['base_score']),
+            label=m['label'], num_class=m['num_class'], learning_rate=np.float32(m['learning_rate']),
+            metric=np.asarray(run['metric'], np.float32),
             raw_pred_sample=raw[::37], raw_pred_sha256=np.frombuffer(hashlib.sha256(raw.tobytes()).digest(), np.uint8),
-            n_raw=raw.size)
-        print(name, 'bins', bins.size, 'trees', m['trees'].shape, 'metric', metric[-1] if metric else None)
+            n_raw=raw.size, logloss=np.float64(run['logloss'] if run['logloss'] is not None else np.nan), **extra)
+        print(name, 'bins', n_bins, 'trees', m['trees'].shape, 'metric', run['metric'][-1] if run['metric'] else None,
+              'logloss', run['logloss'], {k: (float('%.3g' % v) if isinstance(v, float) else v) for k, v in extra.items()})
 
 
 if __name__ == '__main__':
-    main(sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, '..', '..', 'gpurun_out', 'golden'))
+    main(sys.argv[1:])

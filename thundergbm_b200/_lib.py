@@ -15,7 +15,8 @@ class TgbmParam(C.Structure):
     _fields_ = [('depth', C.c_int), ('n_trees', C.c_int), ('max_num_bin', C.c_int), ('num_class', C.c_int),
                 ('min_child_weight', C.c_float), ('lambda_', C.c_float), ('gamma', C.c_float),
                 ('learning_rate', C.c_float), ('objective', C.c_char_p), ('quant_bits', C.c_int),
-                ('keep_nid', C.c_int), ('verbose', C.c_int), ('profile', C.c_int), ('rank_seed', C.c_uint)]
+                ('keep_nid', C.c_int), ('verbose', C.c_int), ('profile', C.c_int), ('rank_seed', C.c_uint),
+                ('hist_mode', C.c_int)]
 
 
 class TgbmInfo(C.Structure):
@@ -50,7 +51,7 @@ def load() -> C.CDLL:
     lib.tgbm_booster_boost_timed.argtypes = [vp, C.c_int, fp]
     lib.tgbm_booster_info.argtypes = [vp, P(TgbmInfo)]
     lib.tgbm_booster_profile.argtypes = [vp, P(TgbmProfile)]
-    for name in ('get_trees', 'get_metrics', 'get_ypred', 'get_bins', 'get_bins_csr', 'get_nid', 'get_root_hist', 'get_quant_scale',
+    for name in ('get_trees', 'get_metrics', 'get_ypred', 'get_bins', 'get_bins_csr', 'get_nid', 'get_root_hist', 'get_root_hist_f32', 'get_quant_scale',
                  'get_labels', 'to_model'):
         getattr(lib, 'tgbm_booster_' + name).argtypes = [vp, vp]
     lib.tgbm_booster_get_cuts.argtypes = [vp, vp, vp]

@@ -54,6 +54,8 @@ def make_param(**kw) -> TgbmParam:
             v = v.encode()
         if k == 'tree_method':
             continue
+        if k == 'hist_mode' and isinstance(v, str):
+            v = {'fp32': 0, 'exact': 1}[v]
         if not hasattr(p, k):
             raise KeyError(k)
         setattr(p, k, v)
@@ -136,6 +138,9 @@ class Booster:
         return self._get('get_nid', (i.rounds_done * i.trees_per_round, i.n_rows), np.int32)
 
     def root_hist(self) -> np.ndarray:
+        """Level-0 histogram of the last tree: int64 sums on the round's grid (exact mode) or float sums (fp32 mode)."""
+        if self.param.hist_mode == 0:
+            return self._get('get_root_hist_f32', (self.info.n_bins, 2), np.float32)
         return self._get('get_root_hist', (self.info.n_bins, 2), np.int64)
 
     def quant_scale(self) -> np.ndarray:

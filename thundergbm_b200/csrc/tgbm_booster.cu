@@ -12,6 +12,7 @@
 #include <cstring>
 
 #include "tgbm_kernels.cuh"
+#include "tgbm_hist_f32.cuh"
 #include "tgbm_rank.cuh"
 
 namespace tgbm {
@@ -59,6 +60,15 @@ struct BoosterImpl {
     DevBuf<int> seg_begin[2], seg_cnt[2], gcnt;
     DevBuf<int> nid_keep;
     DevBuf<long long> hist_full, hist_built;
+    // fp32 mode: the same two buffers hold float pairs; `hist_spread` receives the built histograms of the levels with
+    // few nodes, their cells `f32_stride(pairs)` float2 apart (see tgbm_hist_f32.cuh)
+    bool f32 = false;
+    DevBuf<float2> hist_spread;
+    DevBuf<double> sum_partial;
+    int f32_stride(int pairs) const {
+        if (comm && comm->active()) return 1;  // the built histograms are all-reduced: keep them compact
+        return pairs <= 2 ? 8 : pairs <= 8 ? 4 : pairs <= 16 ? 2 : 1;
+    }
     DevBuf<int> built_right, hist_tile_base;
     DevBuf<HistWork> hist_work;
     bool prune_in_smem = true;
@@ -323,6 +333,8 @@ void Booster::init(const DataSet &ds) {
     TGBM_CHECK(p.depth >= 1 && p.depth <= 14, "depth must be in [1, 14]");
     TGBM_CHECK(p.max_num_bin >= 1 && p.max_num_bin <= 255, "max_num_bin must be in [1, 255] (bin ids are bytes, 255 marks a missing value)");
     TGBM_CHECK(p.quant_bits >= 8 && p.quant_bits <= 20, "quant_bits must be in [8, 20]");
+    TGBM_CHECK(p.hist_mode == 0 || p.hist_mode == 1, "hist_mode must be 0 (fp32) or 1 (exact)");
+    m.f32 = p.hist_mode == 0;
     TGBM_CHECK(!p.bagging, "bagging is not part of the histogram path implemented here");
     TGBM_CHECK(p.column_sampling_rate >= 1.0f, "column sampling is not part of the histogram path implemented here");
     int dev = 0;
@@ -419,6 +431,13 @@ void Booster::init(const DataSet &ds) {
     m.hist_full.alloc((((size_t)1 << depth) - 1) * B1 * 2);
     m.hist_built.alloc(std::max<size_t>(1, (size_t)1 << std::max(0, depth - 2)) * B1 * 2);
     const int max_pairs = std::max(1, 1 << std::max(0, depth - 2));
+    if (m.f32) {
+        m.hist_spread.alloc((size_t)32 * B1);
+        m.sum_partial.alloc((size_t)SUM_BLOCKS * K * 2);
+        const QuantInfo one{1.0, 1.0, 1.0, 1.0};
+        TGBM_CUDA(cudaMemcpyAsync(m.qinfo.p, &one, sizeof(one), cudaMemcpyHostToDevice, m.stream));
+        TGBM_CUDA(cudaStreamSynchronize(m.stream));
+    }
     m.built_right.alloc(max_pairs); m.hist_work.alloc(max_pairs); m.hist_tile_base.alloc(max_pairs + 1);
     m.hist_cta_off.alloc((size_t)m.num_sms + 1);
     m.eval_ticket.alloc(max_pairs);
@@ -463,7 +482,7 @@ void BoosterImpl::gradient(int round) {
     const bool pointwise = objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC;
     const int logistic = objective == REG_LINEAR ? 0 : 1;
     // the pass that applied the previous tree has already found this round's gradient maxima
-    const bool have_max = pointwise && grad_max_ready && round >= 0;
+    const bool have_max = pointwise && grad_max_ready && round >= 0 && !f32;
     grad_max_ready = false;
     root_sum.zero(stream);
     if (!have_max) {
@@ -480,6 +499,13 @@ void BoosterImpl::gradient(int round) {
             }
             ++launches;
         }
+    }
+    if (f32) {  // float gradients as they are; root sums in fp64, block partials combined in a fixed order
+        k_sum_gh<<<dim3(SUM_BLOCKS, K), 256, 0, stream>>>(gh.p, N, sum_partial.p);
+        k_sum_gh_final<<<K, 32, 0, stream>>>(sum_partial.p, SUM_BLOCKS, reinterpret_cast<double *>(root_sum.p));
+        launches += 2;
+        if (comm && comm->active()) comm->allreduce(root_sum.p, 2 * (size_t)K, Comm::F64, Comm::SUM, stream);
+        return;
     }
     if (comm && comm->active()) comm->allreduce(maxbits.p, 2, Comm::U32, Comm::MAX, stream);
     const int blocks = std::max(1, std::min(ceil_div(N, tb), num_sms * 8));
@@ -501,7 +527,14 @@ void BoosterImpl::init_base_score() {
     TGBM_CUDA(cudaMemcpyAsync(hs, root_sum.p, sizeof(hs), cudaMemcpyDeviceToHost, stream));
     TGBM_CUDA(cudaMemcpyAsync(&q, qinfo.p, sizeof(q), cudaMemcpyDeviceToHost, stream));
     TGBM_CUDA(cudaStreamSynchronize(stream));
-    const float fg = (float)((double)(long long)hs[0] * q.inv_sg), fh = (float)((double)(long long)hs[1] * q.inv_sh);
+    float fg, fh;
+    if (f32) {
+        double d[2];
+        memcpy(d, hs, sizeof(d));
+        fg = (float)d[0]; fh = (float)d[1];
+    } else {
+        fg = (float)((double)(long long)hs[0] * q.inv_sg); fh = (float)((double)(long long)hs[1] * q.inv_sh);
+    }
     float w = (float)(-(double)fg / std::fmax((double)fh, 1e-6));
     if (objective == BINARY_LOGISTIC) {
         w = 1 / (1 + expf(-w));
@@ -514,10 +547,11 @@ void BoosterImpl::init_base_score() {
 
 void BoosterImpl::build_tree(int round, int k) {
     const int tree_index = round * K + k;
-    const int2 *gq = ghq.p + (size_t)k * N;
+    // fp32 mode: the records carry the float gradient pairs themselves (same 8 bytes)
+    const int2 *gq = f32 ? reinterpret_cast<const int2 *>(gh.p + (size_t)k * N) : ghq.p + (size_t)k * N;
     const int hist_ctas = std::min(num_sms, HIST_MAX_CTAS);
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
-                                                            seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p);
+                                                            seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p, f32 ? 1 : 0);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
                                         node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[0].p);
     launches += 2;
@@ -530,14 +564,31 @@ void BoosterImpl::build_tree(int round, int k) {
         const int2 *gh_in = level == 0 ? gq : rec_gh[cur].p;
         // -- histogram of the root / of the smaller child of every pair
         long long *built = level == 0 ? hist_full.p : hist_built.p;
-        TGBM_CUDA(cudaMemsetAsync(built, 0, sizeof(long long) * 2 * (size_t)B * pairs, stream));
+        const int bs = f32 ? f32_stride(pairs) : 1;  // fp32 mode: distance of two cells of the built histograms
+        float2 *built_f = bs != 1 ? hist_spread.p : reinterpret_cast<float2 *>(built);
+        if (f32) TGBM_CUDA(cudaMemsetAsync(built_f, 0, sizeof(float2) * (size_t)B * pairs * bs, stream));
+        else TGBM_CUDA(cudaMemsetAsync(built, 0, sizeof(long long) * 2 * (size_t)B * pairs, stream));
         TimedEvent ev{};
         if (profile_on) {
             cudaEventCreate(&ev.a); cudaEventCreate(&ev.b);
             ev.kind = level == 0 ? 0 : 1;
             cudaEventRecord(ev.a, stream);
         }
-        if (sparse) {
+        if (f32) {
+            const float2 *ghf = reinterpret_cast<const float2 *>(gh_in);
+            const int f32_ctas = num_sms * (2048 / F32_THREADS);
+            if (sparse) {
+                if (level == 0)
+                    k_hist_sparse_f32<false><<<f32_ctas, F32_THREADS, 0, stream>>>(sp_row_ptr.p, sp_bin.p, nullptr, ghf, hist_work.p, hist_tile_base.p,
+                                                                                   ctl.p, built_f, B, bs);
+                else
+                    k_hist_sparse_f32<true><<<f32_ctas, F32_THREADS, 0, stream>>>(sp_row_ptr.p, sp_bin.p, idx_in, ghf, hist_work.p, hist_tile_base.p,
+                                                                                  ctl.p, built_f, B, bs);
+            } else if (level == 0)
+                k_hist_f32<false><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, nullptr, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs);
+            else
+                k_hist_f32<true><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, idx_in, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs);
+        } else if (sparse) {
             const int sp_ctas = num_sms;
             const size_t sp_smem = (size_t)std::min(B, SPARSE_SMEM_BINS) * 16;
             if (level == 0)
@@ -553,18 +604,35 @@ void BoosterImpl::build_tree(int round, int k) {
             k_hist<true><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, idx_in, gh_in, hist_cta_off.p, hist_seq.p,
                                                                                   cut_ptr.p, cut_fid.p, built, B, window_rows);
         if (profile_on) { cudaEventRecord(ev.b, stream); events.push_back(ev); }
-        if (comm && comm->active()) comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
+        if (comm && comm->active()) {
+            if (f32) comm->allreduce(built_f, 2 * (size_t)B * pairs, Comm::F32, Comm::SUM, stream);
+            else comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
+        }
         // -- split selection and tree update
+        if (f32) {
+            const float *parent_f = level == 0 ? nullptr : reinterpret_cast<const float *>(hist_full.p) + full_offset(level - 1);
+            float *full_f = reinterpret_cast<float *>(hist_full.p) + full_offset(level);
+            const float *bf = reinterpret_cast<const float *>(built_f);
+            if (sparse) {
+                k_eval_chunk<float><<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
+                                                                              bf, parent_f, full_f, qinfo.p, p.min_child_weight, p.lambda, recs.p, bs);
+                k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
+            } else {
+                k_eval<float><<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, bf, parent_f, full_f, qinfo.p,
+                                                                 p.min_child_weight, p.lambda, recs.p, cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, bs);
+            }
+        } else {
         const long long *parent_hist = level == 0 ? nullptr : hist_full.p + full_offset(level - 1);
         if (sparse) {
-            k_eval_chunk<<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
+            k_eval_chunk<long long><<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
                                                                    built, parent_hist, hist_full.p + full_offset(level), qinfo.p,
-                                                                   p.min_child_weight, p.lambda, recs.p);
+                                                                   p.min_child_weight, p.lambda, recs.p, 1);
             k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
         } else {
-            k_eval<<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built, parent_hist,
+            k_eval<long long><<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built, parent_hist,
                                                       hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p,
-                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p);
+                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, 1);
+        }
         }
         // -- move the rows (not after the last level: the finished tree is applied by walking it, see k_predict_walk)
         launches += sparse ? 3 : 2;
@@ -735,7 +803,7 @@ HistProfile Booster::profile() {
     const TreeCtl &c0 = m.stat_base;
     r.hist_root_bytes = (double)(c.stat_rows_root - c0.stat_rows_root) * (row_bytes + 8);
     r.hist_bytes = r.hist_root_bytes + (double)(c.stat_rows_gather - c0.stat_rows_gather) * (row_bytes + 8 + 4) +
-                   (double)(c.stat_hists - c0.stat_hists) * m.B * 16.0;
+                   (double)(c.stat_hists - c0.stat_hists) * m.B * (m.f32 ? 8.0 : 16.0);
     r.partition_bytes = (double)(c.stat_part_rows - c0.stat_part_rows) * (4 + 1 + 4);
     r.kernel_launches = m.launches;
     return r;
@@ -784,7 +852,16 @@ std::vector<int> Booster::get_nid() {
     if (!impl_->p.keep_nid) return {};
     return to_host(impl_->nid_keep.p, (size_t)impl_->N * impl_->K * impl_->rounds);
 }
-std::vector<long long> Booster::get_root_hist() { sync(); return to_host(impl_->hist_full.p, (size_t)impl_->B * 2); }
+std::vector<long long> Booster::get_root_hist() {
+    sync();
+    TGBM_CHECK(!impl_->f32, "fp32 mode keeps float histograms: use get_root_hist_f32");
+    return to_host(impl_->hist_full.p, (size_t)impl_->B * 2);
+}
+std::vector<float> Booster::get_root_hist_f32() {
+    sync();
+    TGBM_CHECK(impl_->f32, "exact mode keeps integer histograms: use get_root_hist");
+    return to_host(reinterpret_cast<const float *>(impl_->hist_full.p), (size_t)impl_->B * 2);
+}
 std::vector<double> Booster::get_quant_scale() {
     sync();
     auto q = to_host(impl_->qinfo_log.p, impl_->rounds);

@@ -62,7 +62,8 @@ public:
     std::vector<int> get_bins_csr();                      // CSR layout: global bin id per stored value
     bool is_sparse() const;
     std::vector<int> get_nid();                           // [tree][N] when param.keep_nid
-    std::vector<long long> get_root_hist();               // [B][2] level-0 histogram of the last tree built
+    std::vector<long long> get_root_hist();               // exact mode: [B][2] level-0 histogram of the last tree built
+    std::vector<float> get_root_hist_f32();               // fp32 mode: the same as float pairs
     std::vector<double> get_quant_scale();                // per round: scale_g, scale_h
 
 private:

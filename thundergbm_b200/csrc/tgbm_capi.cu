@@ -121,6 +121,7 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
     p.min_child_weight = cp->min_child_weight; p.lambda = cp->lambda; p.gamma = cp->gamma; p.learning_rate = cp->learning_rate;
     p.objective = cp->objective ? cp->objective : "reg:linear";
     p.quant_bits = cp->quant_bits; p.keep_nid = cp->keep_nid; p.verbose = cp->verbose; p.rank_seed = cp->rank_seed;
+    p.hist_mode = cp->hist_mode;
     p.tree_method = "hist";
     return p;
 }
@@ -128,6 +129,13 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
 
 namespace tgbm {
 void set_last_error(const std::string &msg) { g_err = msg; }
+int default_hist_mode() {
+    const char *e = getenv("TGBM_HIST_MODE");
+    if (!e || !*e) return 0;
+    const int m = hist_mode_from_name(e);
+    TGBM_CHECK(m >= 0, std::string("TGBM_HIST_MODE must be fp32 or exact, not ") + e);
+    return m;
+}
 }  // namespace tgbm
 
 extern "C" {
@@ -149,6 +157,7 @@ void sparse_train_scikit(int row_size, float *val, int *row_ptr, int *col_ptr, f
         p.column_sampling_rate = column_sampling_rate; p.bagging = bagging != 0; p.n_parallel_trees = n_parallel_trees;
         p.learning_rate = learning_rate; p.objective = obj_type; p.num_class = *num_class; p.tree_method = tree_method;
         p.rt_eps = 1e-6f; p.tree_per_rounds = 1;
+        p.hist_mode = tgbm::default_hist_mode();
         set_logger(verbose);
         TGBM_CHECK(n_device == 1, "one process drives one GPU here; multi-GPU training goes through tgbm_comm_create / "
                                   "tgbm_booster_create with one process per GPU");
@@ -264,6 +273,7 @@ void train_R(int *depth, int *n_trees, int *n_gpus, int *verbose, int *profiling
         p.bagging = *bagging != 0; p.n_parallel_trees = *n_parallel_trees; p.learning_rate = (float)*learning_rate;
         p.objective = objective[0]; p.num_class = *num_class; p.min_child_weight = (float)*min_child_weight;
         p.lambda = (float)*lambda_tgbm; p.gamma = (float)*gamma; p.tree_method = tree_method[0];
+        p.hist_mode = tgbm::default_hist_mode();
         set_logger(*verbose);
         tgbm::DataSet ds;
         ds.load_from_file(p.path, p);
@@ -294,6 +304,7 @@ void tgbm_default_param(TgbmParam *p) {
     p->depth = d.depth; p->n_trees = d.n_trees; p->max_num_bin = d.max_num_bin; p->num_class = d.num_class;
     p->min_child_weight = d.min_child_weight; p->lambda = d.lambda; p->gamma = d.gamma; p->learning_rate = d.learning_rate;
     p->objective = "reg:linear"; p->quant_bits = d.quant_bits; p->keep_nid = 0; p->verbose = 0; p->profile = 0; p->rank_seed = 0;
+    p->hist_mode = tgbm::default_hist_mode();
 }
 
 int tgbm_comm_unique_id(unsigned char id[128]) { return guard([&] { tgbm::comm_get_unique_id(id); }); }
@@ -400,6 +411,7 @@ int tgbm_booster_get_bins(TgbmBooster *b, unsigned char *out) { return guard([&]
 int tgbm_booster_get_bins_csr(TgbmBooster *b, int *out) { return guard([&] { auto v = b->b->get_bins_csr(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_nid(TgbmBooster *b, int *out) { return guard([&] { auto v = b->b->get_nid(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_root_hist(TgbmBooster *b, long long *out) { return guard([&] { auto v = b->b->get_root_hist(); std::copy(v.begin(), v.end(), out); }); }
+int tgbm_booster_get_root_hist_f32(TgbmBooster *b, float *out) { return guard([&] { auto v = b->b->get_root_hist_f32(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_quant_scale(TgbmBooster *b, double *out) { return guard([&] { auto v = b->b->get_quant_scale(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_labels(TgbmBooster *b, float *out) { return guard([&] { std::copy(b->label.begin(), b->label.end(), out); }); }
 int tgbm_booster_to_model(TgbmBooster *b, ::Tree **model) { return guard([&] { *model = unwrap_model(b->b->get_model()); }); }

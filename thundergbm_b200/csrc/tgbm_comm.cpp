@@ -15,7 +15,7 @@ namespace {
 typedef struct ncclComm *ncclComm_t;
 typedef struct { char internal[128]; } ncclUniqueId;
 typedef int ncclResult_t;
-enum { ncclInt8 = 0, ncclUint8 = 1, ncclInt32 = 2, ncclUint32 = 3, ncclInt64 = 4, ncclUint64 = 5, ncclFloat64 = 8 };
+enum { ncclInt8 = 0, ncclUint8 = 1, ncclInt32 = 2, ncclUint32 = 3, ncclInt64 = 4, ncclUint64 = 5, ncclFloat32 = 7, ncclFloat64 = 8 };
 enum { ncclSum = 0, ncclProd = 1, ncclMax = 2, ncclMin = 3 };
 
 struct Api {
@@ -63,6 +63,7 @@ int nccl_type(Comm::DType t) {
     case Comm::U32: return ncclUint32;
     case Comm::F64: return ncclFloat64;
     case Comm::U8: return ncclUint8;
+    case Comm::F32: return ncclFloat32;
     }
     return ncclInt32;
 }

@@ -17,7 +17,7 @@ struct Comm {
     int world = 1;
     void *nccl_comm = nullptr;
 
-    enum DType { I32, I64, U32, F64, U8 };
+    enum DType { I32, I64, U32, F64, U8, F32 };
     enum Op { SUM, MAX };
 
     bool active() const { return world > 1; }

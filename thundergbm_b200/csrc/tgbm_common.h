@@ -77,10 +77,25 @@ struct GBMParam {
     int n_device = 1;
     std::string tree_method = "auto";
     // additions of this implementation
-    int quant_bits = 18;        // value bits of the fixed-point gradient grid
+    // Histogram arithmetic.  0 "fp32": float (g,h) added per stored value into one accumulator per bin, float prefix
+    // sums -- the reference's own arithmetic (hist_tree_builder_single.cu:203-216), results depend on the order of
+    // the additions in the last bits.  1 "exact": gradients on a power-of-two grid, integer sums -- the deterministic
+    // mode: bit-identical from run to run and for any number of GPUs.
+    int hist_mode = 0;
+    int quant_bits = 18;        // exact mode: value bits of the fixed-point gradient grid
     unsigned rank_seed = 0;     // LambdaRank partner sampling
     int keep_nid = 0;           // tests: keep ins2node_id of every tree
 };
+
+// "fp32" / "0" and "exact" / "deterministic" / "1"; anything else is -1 (rejected by Booster::init)
+inline int hist_mode_from_name(const std::string &s) {
+    if (s == "fp32" || s == "0") return 0;
+    if (s == "exact" || s == "deterministic" || s == "1") return 1;
+    return -1;
+}
+// Default histogram arithmetic of the entry points whose signature has no room for it (the reference's own C
+// surface): the environment variable TGBM_HIST_MODE, else fp32.
+int default_hist_mode();
 
 struct Error : std::runtime_error {
     using std::runtime_error::runtime_error;

@@ -289,9 +289,10 @@ static __global__ void k_quantize(const float2 *__restrict__ gh, int n, const un
 
 // ------------------------------------------------------------------ tree set-up
 // Tree::init2 (src/thundergbm/tree.cu:8-39)
+// root_is_f64: fp32 mode, the root sums are doubles (k_sum_gh_final) instead of integers on the fixed-point grid
 static __global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, const unsigned long long *__restrict__ root_sum,
                             const QuantInfo *__restrict__ q, float lambda, int n_rows, int *__restrict__ seg_begin,
-                            int *__restrict__ seg_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl) {
+                            int *__restrict__ seg_cnt, int *__restrict__ gcnt, TreeCtl *__restrict__ ctl, int root_is_f64) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_nodes) return;
     TreeNode t;
@@ -302,8 +303,13 @@ static __global__ void k_tree_init(TreeNode *__restrict__ nodes, int n_nodes, co
     if (i < n_nodes / 2) { t.is_leaf = 0; t.lch_index = 2 * i + 1; t.rch_index = 2 * i + 2; }
     else { t.is_leaf = 1; t.lch_index = -1; t.rch_index = -1; }
     if (i == 0) {
-        t.sum_g = q2f((long long)root_sum[0], q->inv_sg);
-        t.sum_h = q2f((long long)root_sum[1], q->inv_sh);
+        if (root_is_f64) {
+            t.sum_g = __double2float_rn(__longlong_as_double((long long)root_sum[0]));
+            t.sum_h = __double2float_rn(__longlong_as_double((long long)root_sum[1]));
+        } else {
+            t.sum_g = q2f((long long)root_sum[0], q->inv_sg);
+            t.sum_h = q2f((long long)root_sum[1], q->inv_sh);
+        }
         t.is_valid = 1;
         t.base_weight = __fdiv_rn(-t.sum_g, __fadd_rn(t.sum_h, lambda));
         seg_begin[0] = 0; seg_cnt[0] = n_rows; gcnt[0] = n_rows;
@@ -751,6 +757,19 @@ k_hist_sparse(const int *__restrict__ row_ptr, const int *__restrict__ bin, cons
 }
 
 // ------------------------------------------------------------------ split evaluation
+// Histogram cells are `long long` sums on the round's fixed-point grid (exact mode) or `float` sums (fp32 mode, the
+// reference's own arithmetic: GHPair of floats, include/thundergbm/common.h:43-59).  The evaluation kernels are
+// written once over the cell type.
+template <typename T> __device__ __forceinline__ double cell_inv(const QuantInfo *q, int h);
+template <> __device__ __forceinline__ double cell_inv<long long>(const QuantInfo *q, int h) { return h ? q->inv_sh : q->inv_sg; }
+template <> __device__ __forceinline__ double cell_inv<float>(const QuantInfo *, int) { return 1.0; }
+__device__ __forceinline__ float cell_f(long long v, double inv_scale) { return q2f(v, inv_scale); }
+__device__ __forceinline__ float cell_f(float v, double) { return v; }
+__device__ __forceinline__ long long shfl_up_t(long long v, int d) { return shfl_up_ll(v, d); }
+__device__ __forceinline__ float shfl_up_t(float v, int d) { return __shfl_up_sync(0xffffffffu, v, d); }
+__device__ __forceinline__ long long shfl_t(long long v, int src) { return shfl_ll(v, src); }
+__device__ __forceinline__ float shfl_t(float v, int src) { return __shfl_sync(0xffffffffu, v, src); }
+
 __device__ __forceinline__ float split_gain(float pg, float ph, float lg, float lh, float rg, float rh, float mcw, float lam) {
     // compute_gain, hist_tree_builder_single.cu:279-286 (no fused multiply-add: products feed divisions)
     if (lh >= mcw && rh >= mcw)
@@ -762,11 +781,13 @@ __device__ __forceinline__ float split_gain(float pg, float ph, float lg, float 
 // Sibling subtraction, per-feature prefix scan, missing sums, gains and per-feature argmax
 // (hist_tree_builder_single.cu:257-347 for the root, :538-540 and :614-704 for sibling pairs).
 // grid = (F, pairs); block = 64: warp 0 evaluates the left child, warp 1 the right child.
+template <typename T>
 __device__ __forceinline__ void eval_feature(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode *nodes,
-                                             const int *__restrict__ built_right, const long long *__restrict__ built,
-                                             const long long *__restrict__ parent, long long *__restrict__ full,
-                                             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs) {
-    __shared__ long long sg[2][256], sh[2][256];
+                                             const int *__restrict__ built_right, const T *__restrict__ built,
+                                             const T *__restrict__ parent, T *__restrict__ full,
+                                             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, int bs) {
+    // bs: distance of two cells of `built` in cells (1 unless the fp32 histogram kernel spread them out)
+    __shared__ T sg[2][256], sh[2][256];
     const int f = blockIdx.x, j = blockIdx.y;
     const int b0 = cut_ptr[f], nb = cut_ptr[f + 1] - b0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -781,15 +802,19 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
     }
     // asked for now, used after the histogram loads below: one memory latency instead of two
     const TreeNode nd = nodes[off + (warp < n_children ? node_local : 0)];
-    const double inv_sg = q->inv_sg, inv_sh = q->inv_sh;
+    const double inv_sg = cell_inv<T>(q, 0), inv_sh = cell_inv<T>(q, 1);
     if (level == 0) {
-        for (int i = threadIdx.x; i < nb; i += 64) { sg[0][i] = built[2 * (b0 + i)]; sh[0][i] = built[2 * (b0 + i) + 1]; }
-    } else {
-        const long long *bp = built + (size_t)j * B * 2, *pp = parent + (size_t)j * B * 2;
-        long long *fb = full + (size_t)(2 * j + br) * B * 2, *fo = full + (size_t)(2 * j + 1 - br) * B * 2;
         for (int i = threadIdx.x; i < nb; i += 64) {
-            const long long cg = bp[2 * (b0 + i)], ch = bp[2 * (b0 + i) + 1];
-            const long long og = pp[2 * (b0 + i)] - cg, oh = pp[2 * (b0 + i) + 1] - ch;
+            const T cg = built[(size_t)2 * bs * (b0 + i)], ch = built[(size_t)2 * bs * (b0 + i) + 1];
+            sg[0][i] = cg; sh[0][i] = ch;
+            if (bs != 1) { full[2 * (b0 + i)] = cg; full[2 * (b0 + i) + 1] = ch; }  // the compact copy the next level subtracts from
+        }
+    } else {
+        const T *bp = built + (size_t)j * B * 2 * bs, *pp = parent + (size_t)j * B * 2;
+        T *fb = full + (size_t)(2 * j + br) * B * 2, *fo = full + (size_t)(2 * j + 1 - br) * B * 2;
+        for (int i = threadIdx.x; i < nb; i += 64) {
+            const T cg = bp[(size_t)2 * bs * (b0 + i)], ch = bp[(size_t)2 * bs * (b0 + i) + 1];
+            const T og = pp[2 * (b0 + i)] - cg, oh = pp[2 * (b0 + i) + 1] - ch;
             sg[br][i] = cg; sh[br][i] = ch;
             sg[1 - br][i] = og; sh[1 - br][i] = oh;
             fb[2 * (b0 + i)] = cg; fb[2 * (b0 + i) + 1] = ch;
@@ -803,31 +828,34 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
         return;
     }
     // each lane owns 8 consecutive bins
-    long long lg8[8], lh8[8];
-    long long tg = 0, th = 0;
+    T lg8[8], lh8[8];
+    T tg = 0, th = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int b = lane * 8 + i;
         lg8[i] = tg; lh8[i] = th;  // exclusive prefix inside the lane
         if (b < nb) { tg += sg[warp][b]; th += sh[warp][b]; }
     }
-    long long ig = tg, ih = th;  // inclusive scan of the lane totals
+    T ig = tg, ih = th;  // inclusive scan of the lane totals
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const long long ug = shfl_up_ll(ig, o), uh = shfl_up_ll(ih, o);
+        const T ug = shfl_up_t(ig, o), uh = shfl_up_t(ih, o);
         if (lane >= o) { ig += ug; ih += uh; }
     }
-    const long long base_g = ig - tg, base_h = ih - th;
-    const long long tot_g = shfl_ll(ig, 31), tot_h = shfl_ll(ih, 31);
+    // prefix before the lane's first bin = inclusive value of the lane before (float cells: no subtraction of the
+    // lane's own total, which would round)
+    T base_g = shfl_up_t(ig, 1), base_h = shfl_up_t(ih, 1);
+    if (lane == 0) { base_g = 0; base_h = 0; }
+    const T tot_g = shfl_t(ig, 31), tot_h = shfl_t(ih, 31);
     const float pg = nd.sum_g, ph = nd.sum_h;
-    const float mg = __fsub_rn(pg, q2f(tot_g, inv_sg)), mh = __fsub_rn(ph, q2f(tot_h, inv_sh));
+    const float mg = __fsub_rn(pg, cell_f(tot_g, inv_sg)), mh = __fsub_rn(ph, cell_f(tot_h, inv_sh));
     float best = 0.f, best_lg = 0.f, best_lh = 0.f;
     int best_bin = -1;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int b = lane * 8 + i;
         if (b < nb) {
-            const float lg = q2f(base_g + lg8[i], inv_sg), lh = q2f(base_h + lh8[i], inv_sh);
+            const float lg = cell_f(base_g + lg8[i], inv_sg), lh = cell_f(base_h + lh8[i], inv_sh);
             const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
             const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
             const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
@@ -857,12 +885,13 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
 // add up to at most 256 (a 100k-column one-hot-like data set has one or two bins per feature; a block per feature
 // would launch millions of near-empty blocks).  The scan is segmented by feature; the record of a (node, chunk) keeps
 // the GLOBAL bin index of its best candidate.  grid = (chunks, pairs); block = 64.
+template <typename T>
 static __global__ void __launch_bounds__(64)
 k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0, const int *__restrict__ cut_ptr,
              const int *__restrict__ cut_fid, const TreeNode *__restrict__ nodes, const int *__restrict__ built_right,
-             const long long *__restrict__ built, const long long *__restrict__ parent, long long *__restrict__ full,
-             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs) {
-    __shared__ long long sg[2][256], sh[2][256];
+             const T *__restrict__ built, const T *__restrict__ parent, T *__restrict__ full,
+             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs, int bs) {
+    __shared__ T sg[2][256], sh[2][256];
     const int c = blockIdx.x, j = blockIdx.y;
     const int b0 = chunk_bin0[c], nb = chunk_bin0[c + 1] - b0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -876,13 +905,17 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
         return;
     }
     if (level == 0) {
-        for (int i = threadIdx.x; i < nb; i += 64) { sg[0][i] = built[2 * (b0 + i)]; sh[0][i] = built[2 * (b0 + i) + 1]; }
-    } else {
-        const long long *bp = built + (size_t)j * B * 2, *pp = parent + (size_t)j * B * 2;
-        long long *fb = full + (size_t)(2 * j + br) * B * 2, *fo = full + (size_t)(2 * j + 1 - br) * B * 2;
         for (int i = threadIdx.x; i < nb; i += 64) {
-            const long long cg = bp[2 * (b0 + i)], ch = bp[2 * (b0 + i) + 1];
-            const long long og = pp[2 * (b0 + i)] - cg, oh = pp[2 * (b0 + i) + 1] - ch;
+            const T cg = built[(size_t)2 * bs * (b0 + i)], ch = built[(size_t)2 * bs * (b0 + i) + 1];
+            sg[0][i] = cg; sh[0][i] = ch;
+            if (bs != 1) { full[2 * (b0 + i)] = cg; full[2 * (b0 + i) + 1] = ch; }
+        }
+    } else {
+        const T *bp = built + (size_t)j * B * 2 * bs, *pp = parent + (size_t)j * B * 2;
+        T *fb = full + (size_t)(2 * j + br) * B * 2, *fo = full + (size_t)(2 * j + 1 - br) * B * 2;
+        for (int i = threadIdx.x; i < nb; i += 64) {
+            const T cg = bp[(size_t)2 * bs * (b0 + i)], ch = bp[(size_t)2 * bs * (b0 + i) + 1];
+            const T og = pp[2 * (b0 + i)] - cg, oh = pp[2 * (b0 + i) + 1] - ch;
             sg[br][i] = cg; sh[br][i] = ch;
             sg[1 - br][i] = og; sh[1 - br][i] = oh;
             fb[2 * (b0 + i)] = cg; fb[2 * (b0 + i) + 1] = ch;
@@ -897,9 +930,9 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
         return;
     }
     // lane-local pass over 8 consecutive bins; sums restart where a feature starts
-    long long eg[8], eh[8];       // exclusive prefix inside the feature, as far as the lane can see
+    T eg[8], eh[8];       // exclusive prefix inside the feature, as far as the lane can see
     bool before_start[8];         // no feature start in this lane up to and including this bin -> add the carry
-    long long rg = 0, rh = 0;
+    T rg = 0, rh = 0;
     bool seen = false;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -912,18 +945,18 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
         } else { eg[i] = 0; eh[i] = 0; before_start[i] = false; }
     }
     // segmented inclusive scan of the lanes' open tails (rg, rh); flag = the lane contains a feature start
-    long long vg = rg, vh = rh;
+    T vg = rg, vh = rh;
     bool fl = seen;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        const long long ug = shfl_up_ll(vg, o), uh = shfl_up_ll(vh, o);
+        const T ug = shfl_up_t(vg, o), uh = shfl_up_t(vh, o);
         const int uf = __shfl_up_sync(0xffffffffu, (int)fl, o);
         if (lane >= o) {
             if (!fl) { vg += ug; vh += uh; }
             fl = fl || uf;
         }
     }
-    long long cg = shfl_up_ll(vg, 1), ch = shfl_up_ll(vh, 1);  // carry into this lane = inclusive value of lane-1
+    T cg = shfl_up_t(vg, 1), ch = shfl_up_t(vh, 1);  // carry into this lane = inclusive value of lane-1
     if (lane == 0) { cg = 0; ch = 0; }
     // inclusive prefix per bin back into shared memory: the last bin of a feature then holds the feature total
     __syncwarp();
@@ -932,12 +965,13 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
         const int b = lane * 8 + i;
         if (b < nb) {
             if (before_start[i]) { eg[i] += cg; eh[i] += ch; }
-            const long long ig = eg[i] + sg[warp][b], ih = eh[i] + sh[warp][b];
+            const T ig = eg[i] + sg[warp][b], ih = eh[i] + sh[warp][b];
             sg[warp][b] = ig; sh[warp][b] = ih;
         }
     }
     __syncwarp();
     const float pg = nd.sum_g, ph = nd.sum_h;
+    const double inv_sg = cell_inv<T>(q, 0), inv_sh = cell_inv<T>(q, 1);
     float best = 0.f, best_lg = 0.f, best_lh = 0.f, best_mg = 0.f, best_mh = 0.f;
     int best_bin = -1;
 #pragma unroll
@@ -946,8 +980,8 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
         if (b < nb) {
             const int f = cut_fid[b0 + b];
             const int lastb = cut_ptr[f + 1] - 1 - b0;
-            const float mg = __fsub_rn(pg, q2f(sg[warp][lastb], q->inv_sg)), mh = __fsub_rn(ph, q2f(sh[warp][lastb], q->inv_sh));
-            const float lg = q2f(eg[i], q->inv_sg), lh = q2f(eh[i], q->inv_sh);
+            const float mg = __fsub_rn(pg, cell_f(sg[warp][lastb], inv_sg)), mh = __fsub_rn(ph, cell_f(sh[warp][lastb], inv_sh));
+            const float lg = cell_f(eg[i], inv_sg), lh = cell_f(eh[i], inv_sh);
             const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
             const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
             const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
@@ -1067,12 +1101,13 @@ k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__r
 // Dense layout: evaluation of every (pair, feature) and, by the block that finishes a pair last, the choice among the
 // features and the tree update of the pair's two nodes -- one launch per level instead of two.
 // `ticket[pair]` counts the finished blocks of a pair and is left at zero.
+template <typename T>
 static __global__ void __launch_bounds__(64)
 k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes, const int *__restrict__ built_right,
-       const long long *__restrict__ built, const long long *__restrict__ parent, long long *__restrict__ full,
+       const T *__restrict__ built, const T *__restrict__ parent, T *__restrict__ full,
        const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, const float *__restrict__ cut_val,
-       float rt_eps, const int *__restrict__ cut_fid, int *__restrict__ ticket) {
-    eval_feature(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs);
+       float rt_eps, const int *__restrict__ cut_fid, int *__restrict__ ticket, int built_stride) {
+    eval_feature<T>(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs, built_stride);
     __shared__ int last;
     __threadfence();  // the block's records are visible before its ticket is
     __syncthreads();
