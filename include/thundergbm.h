@@ -92,6 +92,7 @@ typedef struct {
 typedef struct {
     double hist_ms, hist_bytes, hist_root_ms, hist_root_bytes, partition_ms, partition_bytes;
     long long hist_launches, hist_root_launches, partition_launches, kernel_launches;
+    long long hist_rows; /* rows the timed histogram launches processed */
 } TgbmProfile;
 
 /* message of the last failure on this thread ("" if none) */

@@ -53,7 +53,7 @@ def _worker(rank, world, port, case, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('case', ['c2_higgs_small', 'c3_covtype_small', 'fixture_bin'])
+@pytest.mark.parametrize('case', ['c2_higgs_small', 'c3_covtype_small', 'fixture_bin', 'fixture_rank', 'c5_mslr_small'])
 def test_two_gpus_equal_one_gpu(gpu, cases, case):
     import torch
     import torch.multiprocessing as mp
@@ -79,3 +79,67 @@ def test_two_gpus_equal_one_gpu(gpu, cases, case):
     for rank, lo, hi, trees, metrics in res:
         assert trees == want, f'rank {rank} rows [{lo},{hi}) trees differ from the single-GPU run'
         assert np.allclose(metrics, want_m, rtol=0, atol=1e-6)
+        if d.group.size:  # NDCG is a mean over ALL query groups, whichever rank holds them
+            assert all(0.0 < v <= 1.0 for v in metrics)
+
+
+def _scikit_train(d, n_device, depth, n_trees, objective, lr):
+    import ctypes as C
+    from thundergbm_b200 import _lib
+    from thundergbm_b200.booster import NODE_DTYPE
+    lib = _lib.lib()
+    val = np.ascontiguousarray(d.val, np.float32); rp = np.ascontiguousarray(d.row_ptr, np.int32)
+    col = np.ascontiguousarray(d.col, np.int32); y = np.ascontiguousarray(d.y, np.float32)
+    grp = np.ascontiguousarray(d.group, np.int32)
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    model = C.c_void_p(None)
+    num_class = C.c_int(1); per_iter = C.c_int(0)
+    group_label = (C.c_float * 64)()
+    lib.sparse_train_scikit(d.n_rows, vp(val), vp(rp), vp(col), vp(y), depth, n_trees, n_device, 1.0, 1.0, 1.0, 255, 0, 1.0, 0, 1, lr,
+                            objective.encode(), C.byref(num_class), b'hist', C.byref(model), C.byref(per_iter), group_label,
+                            vp(grp) if grp.size else None, int(grp.size))
+    if not model.value:
+        return None, lib.tgbm_last_error().decode()
+    n_nodes = (1 << (depth + 1)) - 1
+    out = []
+    for t in range(n_trees * per_iter.value):
+        arrs = [np.zeros(n_nodes, np.int32) for _ in range(4)] + [np.zeros(n_nodes, np.float32) for _ in range(3)]
+        lib.get_a_tree(C.byref(model), t, n_nodes, *[vp(a) for a in arrs])
+        out.append(np.concatenate([a.view(np.uint8) for a in arrs]).tobytes())
+    lib.model_free(C.byref(model))
+    return out, ''
+
+
+@pytest.mark.parametrize('case', ['c2_higgs_small', 'fixture_rank'])
+def test_n_device_two_through_the_reference_entry_point(gpu, cases, case):
+    """sparse_train_scikit(n_device=2): one process, one host thread per GPU, rows sharded inside the call
+    (include/thundergbm/booster.h:39-64 does the same with OpenMP threads).  In the deterministic mode the trees equal
+    those of n_device=1 bit for bit."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    d, params = cases(case)
+    one, err1 = _scikit_train(d, 1, params['depth'], 3, params['objective'], params['learning_rate'])
+    two, err2 = _scikit_train(d, 2, params['depth'], 3, params['objective'], params['learning_rate'])
+    assert one is not None and two is not None, (err1, err2)
+    assert one == two
+
+
+def test_n_device_beyond_the_visible_gpus_is_refused(gpu, cases):
+    d, params = cases('fixture_reg')
+    out, err = _scikit_train(d, 64, 3, 1, 'reg:linear', 1.0)
+    assert out is None and 'GPU(s) are visible' in err
+
+
+def test_bad_query_groups_on_one_rank_stop_every_rank(gpu, cases):
+    """A rank-local validation failure (group sizes that do not add up) is agreed on before the first collective: the
+    call returns an error instead of leaving the other GPU inside a collective.  The failure is made on the host."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    d, params = cases('fixture_rank')
+    bad = d.rows(0, d.n_rows)
+    bad.group = d.group.copy()
+    bad.group[-1] += 5   # the last rank's groups no longer add up to its rows
+    out, err = _scikit_train(bad, 2, 4, 2, 'rank:ndcg', 0.3)
+    assert out is None and 'group sizes' in err

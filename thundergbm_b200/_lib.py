@@ -28,7 +28,7 @@ class TgbmProfile(C.Structure):
     _fields_ = [(n, C.c_double) for n in ('hist_ms', 'hist_bytes', 'hist_root_ms', 'hist_root_bytes', 'partition_ms',
                                           'partition_bytes')] + \
                [(n, C.c_longlong) for n in ('hist_launches', 'hist_root_launches', 'partition_launches',
-                                            'kernel_launches')]
+                                            'kernel_launches', 'hist_rows')]
 
 
 def load() -> C.CDLL:

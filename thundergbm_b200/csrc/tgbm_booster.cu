@@ -87,6 +87,9 @@ struct BoosterImpl {
     DevBuf<int4> hist_seq;
     DevBuf<SplitRec> recs;
     DevBuf<int> node_tile0[2], tile_left, tile_node[2];
+    DevBuf<int> part_base;                    // single-pass partition: records of the nodes before a node
+    DevBuf<unsigned long long> part_status;   // single-pass partition: look-back word of every tile
+    bool part_one = true;
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
     DevBuf<double> metric_partial, metric_sum;
@@ -96,6 +99,7 @@ struct BoosterImpl {
 
     struct TimedEvent { cudaEvent_t a, b; int kind; };
     std::vector<TimedEvent> events;
+    HistProfile profile_acc;  // kernel times of the events already read and destroyed
     long long launches = 0;
 
     ~BoosterImpl() {
@@ -130,22 +134,26 @@ void BoosterImpl::upload_csr(const DataSet &ds) {
     TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
     TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
     TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
-    if (F < 0) {
-        F = 1;  // dataset.cpp:54-57: largest column index + 1
-        if (nnz) {
-            DevBuf<int> d_max;
-            d_max.alloc(1);
-            size_t tb = 0;
-            TGBM_CUDA(cub::DeviceReduce::Max(nullptr, tb, d_col.p, d_max.p, (int)nnz, stream));
-            DevBuf<unsigned char> tmp;
-            tmp.alloc(std::max<size_t>(tb, 1));
-            TGBM_CUDA(cub::DeviceReduce::Max(tmp.p, tb, d_col.p, d_max.p, (int)nnz, stream));
-            int h_max = 0;
-            TGBM_CUDA(cudaMemcpyAsync(&h_max, d_max.p, sizeof(int), cudaMemcpyDeviceToHost, stream));
-            TGBM_CUDA(cudaStreamSynchronize(stream));
-            TGBM_CHECK(h_max >= 0, "negative column index in the CSR input");
-            F = h_max + 1;
-        }
+    // Largest and smallest column index, found here at HBM speed: the largest gives the feature count when the caller
+    // did not count (dataset.cpp:54-57), a negative one would send the binning kernels out of bounds.
+    const bool count_features = F < 0;
+    if (count_features) F = 1;
+    if (nnz) {
+        DevBuf<int> d_mm;
+        d_mm.alloc(2);
+        size_t tb = 0, tb2 = 0;
+        TGBM_CUDA(cub::DeviceReduce::Max(nullptr, tb, d_col.p, d_mm.p, (long long)nnz, stream));
+        TGBM_CUDA(cub::DeviceReduce::Min(nullptr, tb2, d_col.p, d_mm.p + 1, (long long)nnz, stream));
+        DevBuf<unsigned char> tmp;
+        tmp.alloc(std::max<size_t>(std::max(tb, tb2), 1));
+        TGBM_CUDA(cub::DeviceReduce::Max(tmp.p, tb, d_col.p, d_mm.p, (long long)nnz, stream));
+        TGBM_CUDA(cub::DeviceReduce::Min(tmp.p, tb2, d_col.p, d_mm.p + 1, (long long)nnz, stream));
+        int h_mm[2] = {0, 0};
+        TGBM_CUDA(cudaMemcpyAsync(h_mm, d_mm.p, sizeof(h_mm), cudaMemcpyDeviceToHost, stream));
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+        TGBM_CHECK(h_mm[1] >= 0, "negative column index in the CSR input");
+        if (count_features) F = h_mm[0] + 1;
+        else TGBM_CHECK(h_mm[0] < F, "column index beyond the feature count");
     }
 }
 
@@ -168,10 +176,17 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     lap("H2D of the CSR");
     long long nu = 0;
     DevBuf<unsigned long long> ukeys;
+    const bool multi = comm && comm->active();
+    std::string local_err;  // see Booster::init: local phases are followed by an agreement of all ranks
+    auto agree = [&](const char *what) {
+        if (multi) comm->agree(local_err, what, stream);
+        else if (!local_err.empty()) throw Error(local_err);
+    };
     {
         DevBuf<unsigned long long> keys, keys2;
         DevBuf<long long> d_nu;
-        keys.alloc(std::max<size_t>(nnz, 1)); keys2.alloc(std::max<size_t>(nnz, 1)); d_nu.alloc(1);
+        try { keys.alloc(std::max<size_t>(nnz, 1)); keys2.alloc(std::max<size_t>(nnz, 1)); d_nu.alloc(1); }
+        catch (const std::exception &e) { local_err = e.what(); }
         auto sort_unique = [&](size_t n) -> long long {  // keys -> keys (sorted distinct), returns the count
             if (n == 0) return 0;
             size_t tb = 0;
@@ -191,9 +206,14 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             TGBM_CUDA(cudaStreamSynchronize(stream));
             return r;
         };
-        if (nnz) k_make_keys<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_val.p, d_col.p, nnz, keys.p);
-        nu = sort_unique(nnz);
-        if (comm && comm->active()) {
+        if (local_err.empty()) {
+            try {
+                if (nnz) k_make_keys<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_val.p, d_col.p, nnz, keys.p);
+                nu = sort_unique(nnz);
+            } catch (const std::exception &e) { local_err = e.what(); }
+        }
+        agree("sorting its feature values");
+        if (multi) {
             // union of the ranks' distinct keys: all-gather (padded to the largest rank), then sort + unique again
             DevBuf<long long> counts;
             counts.alloc(comm->world);
@@ -203,10 +223,11 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             comm->allgather(mine.p, counts.p, 1, Comm::I64, stream);
             std::vector<long long> hc(comm->world);
             TGBM_CUDA(cudaMemcpyAsync(hc.data(), counts.p, sizeof(long long) * comm->world, cudaMemcpyDeviceToHost, stream));
-            TGBM_CUDA(cudaStreamSynchronize(stream));
+            comm->wait(stream);
             const long long mx = std::max<long long>(1, *std::max_element(hc.begin(), hc.end()));
             DevBuf<unsigned long long> padded, all;
-            padded.alloc(mx); all.alloc((size_t)mx * comm->world);
+            try { padded.alloc(mx); all.alloc((size_t)mx * comm->world); } catch (const std::exception &e) { local_err = e.what(); }
+            agree("making room for the ranks' feature values");
             TGBM_CUDA(cudaMemsetAsync(padded.p, 0xff, sizeof(unsigned long long) * mx, stream));
             if (nu) TGBM_CUDA(cudaMemcpyAsync(padded.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
             comm->allgather(padded.p, all.p, mx, Comm::I64, stream);
@@ -346,28 +367,46 @@ void Booster::init(const DataSet &ds) {
     TGBM_CUDA(cudaEventCreateWithFlags(&m.ev_plan, cudaEventDisableTiming));
     m.N = ds.n_rows;
     m.F = ds.n_features;
-    m.upload_csr(ds);
     m.depth = p.depth;
     m.n_nodes = (1 << (p.depth + 1)) - 1;
     m.label = ds.label;
+    const bool multi = m.comm && m.comm->active();
+    // Every phase that can fail on one rank alone (a check of this rank's input, an allocation) runs under `locally`
+    // and is followed by an agreement of all ranks, so that no rank enters a collective its peers will never join.
+    std::string local_err;
+    auto locally = [&](auto &&phase) {
+        try { phase(); } catch (const std::exception &e) { local_err = e.what(); }
+    };
+    auto agree = [&](const char *what) {
+        if (multi) m.comm->agree(local_err, what, m.stream);
+        else if (!local_err.empty()) throw Error(local_err);
+    };
+    locally([&] {
+        if (need_group_file(m.objective)) RankState::validate(ds, m.N);
+        m.upload_csr(ds);
+    });
+    agree("loading its rows");
 
-    // global row count, this rank's row offset, global feature count
+    // global row count, this rank's row offset, global feature count, query groups before this rank's
     m.N_global = m.N;
     m.row_offset = 0;
-    if (m.comm && m.comm->active()) {
+    long long first_group = 0, total_groups = (long long)ds.group.size();
+    if (multi) {
         DevBuf<long long> mine, all;
-        mine.alloc(2); all.alloc(2 * (size_t)m.comm->world);
-        long long h[2] = {m.N, m.F};
+        mine.alloc(3); all.alloc(3 * (size_t)m.comm->world);
+        long long h[3] = {m.N, m.F, (long long)ds.group.size()};
         TGBM_CUDA(cudaMemcpyAsync(mine.p, h, sizeof(h), cudaMemcpyHostToDevice, m.stream));
-        m.comm->allgather(mine.p, all.p, 2, Comm::I64, m.stream);
-        std::vector<long long> ha(2 * (size_t)m.comm->world);
+        m.comm->allgather(mine.p, all.p, 3, Comm::I64, m.stream);
+        std::vector<long long> ha(3 * (size_t)m.comm->world);
         TGBM_CUDA(cudaMemcpyAsync(ha.data(), all.p, sizeof(long long) * ha.size(), cudaMemcpyDeviceToHost, m.stream));
-        TGBM_CUDA(cudaStreamSynchronize(m.stream));
+        m.comm->wait(m.stream);
         m.N_global = 0;
+        total_groups = 0;
         for (int r = 0; r < m.comm->world; ++r) {
-            if (r < m.comm->rank) m.row_offset += ha[2 * r];
-            m.N_global += ha[2 * r];
-            m.F = std::max<int>(m.F, (int)ha[2 * r + 1]);
+            if (r < m.comm->rank) { m.row_offset += ha[3 * r]; first_group += ha[3 * r + 2]; }
+            m.N_global += ha[3 * r];
+            m.F = std::max<int>(m.F, (int)ha[3 * r + 1]);
+            total_groups += ha[3 * r + 2];
         }
     }
     TGBM_CHECK(m.N_global < (1ll << 31), "row count must fit 32 bits");
@@ -402,6 +441,7 @@ void Booster::init(const DataSet &ds) {
     m.find_cuts_and_bins(ds);
     lap("= cuts and bins, with frees");
 
+    locally([&] {
     const int N = m.N, K = m.K, depth = m.depth;
     const size_t n1 = std::max<size_t>(N, 1);
     m.y.alloc(n1); m.ypred.alloc(n1 * K); m.gh.alloc(n1 * K); m.ghq.alloc(n1 * K);
@@ -420,7 +460,7 @@ void Booster::init(const DataSet &ds) {
     m.model.alloc((size_t)std::max(p.n_trees, 1) * K * m.n_nodes);
     m.metric.alloc(std::max(p.n_trees, 1));
     for (int i = 0; i < 2; ++i) {
-        m.rec_idx[i].alloc(n1); m.rec_gh[i].alloc(n1);
+        m.rec_idx[i].alloc(2 * n1); m.rec_gh[i].alloc(2 * n1);  // left children in the first half, right children in the second
         m.seg_begin[i].alloc((size_t)1 << depth); m.seg_cnt[i].alloc((size_t)1 << depth);
         m.seg_begin[i].zero(m.stream); m.seg_cnt[i].zero(m.stream);
     }
@@ -452,6 +492,10 @@ void Booster::init(const DataSet &ds) {
     m.tile_node[0].alloc(m.max_tiles); m.tile_node[1].alloc(m.max_tiles);
     m.node_tile0[0].alloc(((size_t)1 << depth) + 1); m.node_tile0[1].alloc(((size_t)1 << depth) + 1);
     m.bits.alloc((size_t)m.max_tiles * (PART_TILE / 32));
+    m.part_base.alloc((size_t)1 << depth);
+    m.part_status.alloc(m.max_tiles);
+    m.part_status.zero(m.stream);
+    m.part_one = getenv("TGBM_PART_3PASS") == nullptr;
     m.ctl.alloc(1);
     m.ctl.zero(m.stream);
     m.metric_partial.alloc(1024); m.metric_sum.alloc(1);
@@ -468,7 +512,9 @@ void Booster::init(const DataSet &ds) {
     m.prune_in_smem = sizeof(TreeNode) * (size_t)m.n_nodes <= 200 * 1024;  // up to depth 11
     if (m.prune_in_smem && sizeof(TreeNode) * (size_t)m.n_nodes > 48 * 1024)
         TGBM_CUDA(cudaFuncSetAttribute(k_prune, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(sizeof(TreeNode) * (size_t)m.n_nodes)));
-    if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream);
+    if (need_group_file(m.objective)) m.rank.init(ds, m.objective, m.N, m.stream, first_group, total_groups);
+    });
+    agree("allocating its training buffers");
     lap("training buffers");
     m.init_base_score();
     TGBM_CUDA(cudaStreamSynchronize(m.stream));
@@ -553,7 +599,8 @@ void BoosterImpl::build_tree(int round, int k) {
     k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p, f32 ? 1 : 0);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
-                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[0].p);
+                                        node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[0].p, part_base.p,
+                                        seg_begin[1].p, seg_cnt[1].p);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * (2048 / PART_THREADS)));
@@ -639,6 +686,24 @@ void BoosterImpl::build_tree(int round, int k) {
         if (level == depth - 1) break;
         TimedEvent pv{};
         if (profile_on) { cudaEventCreate(&pv.a); cudaEventCreate(&pv.b); pv.kind = 2; cudaEventRecord(pv.a, stream); }
+        if (part_one) {
+            // one pass: count, look-back prefix inside every node and scatter; then the plan of the next level
+            const int n1 = std::max(N, 1);
+            if (sparse)
+                k_part_one<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, tile_node[cur].p,
+                                                                         part_base.p, ctl.p, idx_in, gh_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p,
+                                                                         part_status.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
+            else
+                k_part_one<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, tile_node[cur].p,
+                                                                          part_base.p, ctl.p, idx_in, gh_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p,
+                                                                          part_status.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
+            k_plan_next<<<1, 1024, 0, stream>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, seg_cnt[nxt].p, nodes.p, ctl.p, by_hessian, built_right.p,
+                                                hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p,
+                                                part_base.p, seg_begin[cur].p, seg_cnt[cur].p);
+            if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
+            launches += 2;
+            continue;
+        }
         if (sparse)
             k_part_count<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
                                                                        idx_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p);
@@ -652,7 +717,8 @@ void BoosterImpl::build_tree(int round, int k) {
         TGBM_CUDA(cudaEventRecord(ev_scan, stream));
         TGBM_CUDA(cudaStreamWaitEvent(stream2, ev_scan, 0));
         k_plan_next<<<1, 1024, 0, stream2>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, nodes.p, ctl.p, by_hessian, built_right.p,
-                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p);
+                                             hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p,
+                                             part_base.p, nullptr, nullptr);
         TGBM_CUDA(cudaEventRecord(ev_plan, stream2));
         k_part_scatter<<<std::max(1, part_ctas - 1024 / PART_THREADS), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
                                                                                 node_tile0[cur].p, ctl.p, idx_in, gh_in, bits.p, tile_left.p,
@@ -760,7 +826,8 @@ void Booster::boost(int n_rounds) {
 }
 
 void Booster::sync() {
-    TGBM_CUDA(cudaStreamSynchronize(impl_->stream));
+    if (impl_->comm && impl_->comm->active()) impl_->comm->wait(impl_->stream);  // bounded: a rank may have left
+    else TGBM_CUDA(cudaStreamSynchronize(impl_->stream));
     TGBM_CUDA(cudaGetLastError());
 }
 
@@ -795,6 +862,14 @@ HistProfile Booster::profile() {
             if (e.kind == 0) { r.hist_root_ms += ms; r.hist_root_launches += 1; }
         }
     }
+    // the timed events have been read: their times move into running totals and the events are destroyed, so that a
+    // long profiled run does not pile them up
+    for (auto &e : m.events) { cudaEventDestroy(e.a); cudaEventDestroy(e.b); }
+    m.events.clear();
+    m.profile_acc.hist_ms += r.hist_ms; m.profile_acc.hist_launches += r.hist_launches;
+    m.profile_acc.hist_root_ms += r.hist_root_ms; m.profile_acc.hist_root_launches += r.hist_root_launches;
+    m.profile_acc.partition_ms += r.partition_ms; m.profile_acc.partition_launches += r.partition_launches;
+    r = m.profile_acc;
     TreeCtl c;
     TGBM_CUDA(cudaMemcpy(&c, m.ctl.p, sizeof(c), cudaMemcpyDeviceToHost));
     // algorithmic bytes: rows * (F bin bytes + 8 gradient bytes [+ 4 row index]) + histograms * B * 16 written
@@ -805,6 +880,7 @@ HistProfile Booster::profile() {
     r.hist_bytes = r.hist_root_bytes + (double)(c.stat_rows_gather - c0.stat_rows_gather) * (row_bytes + 8 + 4) +
                    (double)(c.stat_hists - c0.stat_hists) * m.B * (m.f32 ? 8.0 : 16.0);
     r.partition_bytes = (double)(c.stat_part_rows - c0.stat_part_rows) * (4 + 1 + 4);
+    r.hist_rows = (long long)((c.stat_rows_root - c0.stat_rows_root) + (c.stat_rows_gather - c0.stat_rows_gather));
     r.kernel_launches = m.launches;
     return r;
 }

@@ -26,6 +26,7 @@ struct HistProfile {
     double hist_root_ms = 0;
     double hist_root_bytes = 0;
     long long hist_root_launches = 0;
+    long long hist_rows = 0;       // rows those histogram launches processed (root + gathered)
 };
 
 class Booster {
@@ -69,6 +70,11 @@ public:
 private:
     std::unique_ptr<BoosterImpl> impl_;
 };
+
+// TreeTrainer::train (src/thundergbm/trainer.cu:18-57) for the histogram path: one booster on the current device, or --
+// param.n_device > 1 -- one host thread per GPU on devices 0 .. n_device-1 with the rows sharded between them.
+// Logs the per-round metric and the training time like the reference; updates base_score, num_class, tree_per_rounds.
+std::vector<std::vector<Tree>> train_model(GBMParam &param, const DataSet &ds);
 
 // batch inference, Predictor::predict_raw (src/thundergbm/predictor.cu:32-189): out[t*N+i]
 // kernel_ms (optional): device time of the traversal kernel alone

@@ -5,6 +5,7 @@
 #include <cstring>
 #include <map>
 #include <string>
+#include <thread>
 
 #include "../../include/thundergbm.h"
 #include "tgbm_booster.h"
@@ -18,6 +19,7 @@ struct TgbmBooster {
     tgbm::GBMParam param;
     std::vector<float> label;
     int n_rows = 0;
+    ~TgbmBooster() { delete b; }  // also when init() throws half way through tgbm_booster_create
 };
 
 namespace {
@@ -78,9 +80,11 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
     const auto t1 = std::chrono::high_resolution_clock::now();
     lap("boost");
     const auto metrics = booster.get_metrics();
-    for (size_t i = 0; i < metrics.size(); ++i)  // include/thundergbm/booster.h:91-92
-        tgbm::log_info("[%zu/%d] %s = %g", i + 1, p.n_trees, tgbm::metric_name(tgbm::objective_from_name(p.objective)), metrics[i]);
-    tgbm::log_info("training time = %g", std::chrono::duration<float>(t1 - t0).count());  // trainer.cu:50
+    if (!comm || comm->rank == 0) {
+        for (size_t i = 0; i < metrics.size(); ++i)  // include/thundergbm/booster.h:91-92
+            tgbm::log_info("[%zu/%d] %s = %g", i + 1, p.n_trees, tgbm::metric_name(tgbm::objective_from_name(p.objective)), metrics[i]);
+        tgbm::log_info("training time = %g", std::chrono::duration<float>(t1 - t0).count());  // trainer.cu:50
+    }
     p.base_score = booster.base_score();
     p.num_class = booster.num_class();
     p.tree_per_rounds = booster.trees_per_round();
@@ -91,20 +95,105 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
     return result;
 }
 
+// n_device > 1 through the reference's own entry points (include/thundergbm/booster.h:39-64 runs one OpenMP thread per
+// GPU inside the process).  Here too: one host thread per GPU, devices 0 .. n_device-1, each with a contiguous block
+// of the rows (query groups stay whole), an NCCL communicator between them and a host-side meeting point
+// (tgbm::HostGroup) so that a rank that fails takes the others with it instead of leaving them in a collective.
+// The rows are sharded, not the columns, and every rank builds the same trees; rank 0's copy is returned.
+std::vector<std::vector<tgbm::Tree>> train_in_process(tgbm::GBMParam &p, const tgbm::DataSet &ds, int n_dev) {
+    int avail = 0;
+    TGBM_CUDA(cudaGetDeviceCount(&avail));
+    TGBM_CHECK(n_dev <= avail, "n_device = " + std::to_string(n_dev) + " but only " + std::to_string(avail) + " GPU(s) are visible");
+    int caller_dev = 0;
+    TGBM_CUDA(cudaGetDevice(&caller_dev));
+    unsigned char id[128];
+    tgbm::comm_get_unique_id(id);
+    auto group = std::make_shared<tgbm::HostGroup>(n_dev, 600.0);
+    // row blocks: rows n*r/W, moved to the next query-group boundary when there are groups
+    std::vector<int> row_lo(n_dev + 1, 0), grp_lo(n_dev + 1, 0);
+    {
+        std::vector<long long> gend;
+        long long acc = 0;
+        for (int g : ds.group) { acc += g; gend.push_back(acc); }
+        for (int r = 1; r < n_dev; ++r) {
+            long long want = (long long)ds.n_rows * r / n_dev;
+            if (!gend.empty()) {
+                const size_t gi = std::lower_bound(gend.begin(), gend.end(), want) - gend.begin();
+                grp_lo[r] = (int)std::min(gi + 1, gend.size());
+                want = grp_lo[r] ? gend[grp_lo[r] - 1] : 0;
+            }
+            row_lo[r] = (int)want;
+        }
+        row_lo[n_dev] = ds.n_rows;
+        grp_lo[n_dev] = (int)ds.group.size();
+    }
+    std::vector<std::string> errors(n_dev);
+    std::vector<std::vector<tgbm::Tree>> result;
+    tgbm::GBMParam p0 = p;
+    std::vector<std::thread> threads;
+    for (int r = 0; r < n_dev; ++r)
+        threads.emplace_back([&, r] {
+            tgbm::Comm *c = nullptr;
+            try {
+                TGBM_CUDA(cudaSetDevice(r));
+                c = tgbm::comm_create(id, r, n_dev);
+                c->host = group;
+                const int lo = row_lo[r], hi = row_lo[r + 1];
+                tgbm::DataSet shard;
+                shard.n_rows = hi - lo;
+                shard.n_features = ds.n_features;
+                shard.row_ptr.resize(hi - lo + 1);
+                for (int i = lo; i <= hi; ++i) shard.row_ptr[i - lo] = ds.rp[i] - ds.rp[lo];
+                shard.rp = shard.row_ptr.data();
+                shard.ci = ds.ci + ds.rp[lo];
+                shard.vv = ds.vv + ds.rp[lo];
+                const float *labels = ds.yv ? ds.yv : ds.y.data();
+                shard.yv = labels ? labels + lo : nullptr;
+                shard.labels_raw = ds.labels_raw;
+                shard.label = ds.label;
+                shard.group.assign(ds.group.begin() + grp_lo[r], ds.group.begin() + grp_lo[r + 1]);
+                tgbm::GBMParam pr = p0;
+                auto m = train(pr, shard, c);
+                if (r == 0) { result = std::move(m); p = pr; }
+            } catch (const std::exception &e) {
+                errors[r] = e.what();
+                group->abandon();
+            }
+            if (c) tgbm::comm_destroy(c);
+        });
+    for (auto &t : threads) t.join();
+    cudaSetDevice(caller_dev);
+    // a rank's own failure explains more than the "another rank failed" of its peers
+    std::string first, own;
+    for (int r = 0; r < n_dev; ++r) {
+        if (errors[r].empty()) continue;
+        if (first.empty()) first = errors[r];
+        if (own.empty() && errors[r].find("another rank") == std::string::npos) own = "rank " + std::to_string(r) + ": " + errors[r];
+    }
+    if (!first.empty()) throw tgbm::Error(own.empty() ? first : own);
+    return result;
+}
+
 // distinct integer labels over all ranks (DataSet::group_label applied to the union); the rows keep the caller's
 // label values, the booster maps them to class indices on the device
 void group_label_global(tgbm::DataSet &ds, const float *label, tgbm::GBMParam &p, const tgbm::Comm *comm) {
     constexpr int CAP = 4096;
-    ds.distinct_labels(label, (size_t)ds.n_rows);
-    TGBM_CHECK((int)ds.label.size() <= CAP, "more than 4096 distinct labels");
+    // Failures of this rank alone (too many labels, no device memory) travel WITH the all-gather as a marker in slot 0,
+    // so that every rank leaves together instead of this one alone before the collective.
+    std::string local_err;
     std::vector<int> padded(CAP, INT_MAX);
-    for (size_t i = 0; i < ds.label.size(); ++i) padded[i] = (int)ds.label[i];
     tgbm::DevBuf<int> d_in, d_out;
-    d_in.alloc(CAP); d_out.alloc((size_t)CAP * comm->world);
+    try {
+        ds.distinct_labels(label, (size_t)ds.n_rows);
+        TGBM_CHECK((int)ds.label.size() <= CAP, "more than 4096 distinct labels");
+        for (size_t i = 0; i < ds.label.size(); ++i) padded[i] = (int)ds.label[i];
+        d_in.alloc(CAP); d_out.alloc((size_t)CAP * comm->world);
+    } catch (const std::exception &e) { local_err = e.what(); }
+    comm->agree(local_err, "grouping its labels", nullptr);
     TGBM_CUDA(cudaMemcpy(d_in.p, padded.data(), sizeof(int) * CAP, cudaMemcpyHostToDevice));
     comm->allgather(d_in.p, d_out.p, CAP, tgbm::Comm::I32, nullptr);
     std::vector<int> all((size_t)CAP * comm->world);
-    TGBM_CUDA(cudaDeviceSynchronize());
+    comm->wait(nullptr);
     TGBM_CUDA(cudaMemcpy(all.data(), d_out.p, sizeof(int) * all.size(), cudaMemcpyDeviceToHost));
     std::sort(all.begin(), all.end());
     all.erase(std::unique(all.begin(), all.end()), all.end());
@@ -128,6 +217,10 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
 }  // namespace
 
 namespace tgbm {
+std::vector<std::vector<Tree>> train_model(GBMParam &p, const DataSet &ds) {
+    TGBM_CHECK(p.n_device >= 1, "n_device must be at least 1");
+    return p.n_device > 1 ? train_in_process(p, ds, p.n_device) : train(p, ds, nullptr);
+}
 void set_last_error(const std::string &msg) { g_err = msg; }
 int default_hist_mode() {
     const char *e = getenv("TGBM_HIST_MODE");
@@ -159,13 +252,12 @@ void sparse_train_scikit(int row_size, float *val, int *row_ptr, int *col_ptr, f
         p.rt_eps = 1e-6f; p.tree_per_rounds = 1;
         p.hist_mode = tgbm::default_hist_mode();
         set_logger(verbose);
-        TGBM_CHECK(n_device == 1, "one process drives one GPU here; multi-GPU training goes through tgbm_comm_create / "
-                                  "tgbm_booster_create with one process per GPU");
+        TGBM_CHECK(n_device >= 1, "n_device must be at least 1");
         tgbm::DataSet ds;
         ds.load_from_sparse(row_size, val, row_ptr, col_ptr, label, group, num_group, p, /*lazy=*/true);
         tgbm::log_info("#instances = %d", ds.n_rows);
         *num_class = p.num_class;
-        auto m = train(p, ds, nullptr);
+        auto m = tgbm::train_model(p, ds);
         *num_class = p.num_class;
         *tree_per_iter = m.empty() ? 1 : (int)m[0].size();
         TGBM_CHECK((int)m.size() == n_trees, "trained fewer rounds than requested");
@@ -277,7 +369,7 @@ void train_R(int *depth, int *n_trees, int *n_gpus, int *verbose, int *profiling
         set_logger(*verbose);
         tgbm::DataSet ds;
         ds.load_from_file(p.path, p);
-        auto m = train(p, ds, nullptr);
+        auto m = tgbm::train_model(p, ds);
         tgbm::save_model(model_out[0], p, m, ds.label);
     });
 }
@@ -390,6 +482,7 @@ int tgbm_booster_profile(TgbmBooster *b, TgbmProfile *o) {
         o->hist_ms = p.hist_ms; o->hist_bytes = p.hist_bytes; o->hist_root_ms = p.hist_root_ms; o->hist_root_bytes = p.hist_root_bytes;
         o->partition_ms = p.partition_ms; o->partition_bytes = p.partition_bytes; o->hist_launches = p.hist_launches;
         o->hist_root_launches = p.hist_root_launches; o->partition_launches = p.partition_launches; o->kernel_launches = p.kernel_launches;
+        o->hist_rows = p.hist_rows;
     });
 }
 int tgbm_booster_get_trees(TgbmBooster *b, void *out) {
@@ -415,11 +508,7 @@ int tgbm_booster_get_root_hist_f32(TgbmBooster *b, float *out) { return guard([&
 int tgbm_booster_get_quant_scale(TgbmBooster *b, double *out) { return guard([&] { auto v = b->b->get_quant_scale(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_labels(TgbmBooster *b, float *out) { return guard([&] { std::copy(b->label.begin(), b->label.end(), out); }); }
 int tgbm_booster_to_model(TgbmBooster *b, ::Tree **model) { return guard([&] { *model = unwrap_model(b->b->get_model()); }); }
-void tgbm_booster_free(TgbmBooster *b) {
-    if (!b) return;
-    delete b->b;
-    delete b;
-}
+void tgbm_booster_free(TgbmBooster *b) { delete b; }
 
 int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, const float *label, const float *raw,
                       const int *group, int num_group, float *out) {

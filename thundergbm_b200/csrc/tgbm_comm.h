@@ -9,6 +9,10 @@
 #include <cuda_runtime.h>
 #include <cstddef>
 #include <cstdint>
+#include <memory>
+#include <string>
+
+#include "tgbm_hostgroup.h"
 
 namespace tgbm {
 
@@ -16,6 +20,10 @@ struct Comm {
     int rank = 0;
     int world = 1;
     void *nccl_comm = nullptr;
+    // ranks that are threads of one process (n_device > 1 through the reference's entry points) also meet on the host
+    std::shared_ptr<HostGroup> host;
+    int *d_flag = nullptr;  // one device word for agree() between processes
+    double timeout_s = 600;  // wait(): how long a stream with collectives in flight may stay busy (TGBM_COMM_TIMEOUT_S)
 
     enum DType { I32, I64, U32, F64, U8, F32 };
     enum Op { SUM, MAX };
@@ -25,6 +33,15 @@ struct Comm {
     void allreduce(void *buf, size_t count, DType t, Op op, cudaStream_t stream) const;
     // out must hold world*count elements
     void allgather(const void *in, void *out, size_t count, DType t, cudaStream_t stream) const;
+
+    // Every rank reports whether its last local phase succeeded (`local_error` empty) before anyone enqueues the next
+    // collective; throws on EVERY rank when some rank failed: the failing rank its own message, the others a note
+    // naming the phase.  In-process groups meet on the host (HostGroup); process groups all-reduce one word.
+    void agree(const std::string &local_error, const char *phase, cudaStream_t stream) const;
+    // cudaStreamSynchronize for a stream that carries collectives: polls the stream and the communicator's asynchronous
+    // error state, and gives up (aborting the communicator, then throwing) after `timeout_s` or on a reported error --
+    // a rank that left between steps must not keep this host thread waiting for ever.
+    void wait(cudaStream_t stream) const;
 };
 
 // 128-byte NCCL unique id, created by rank 0 and handed to every rank by the caller

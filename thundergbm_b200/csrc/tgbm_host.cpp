@@ -206,9 +206,11 @@ void parse_svm_piece(const char *p, const char *end, SvmPiece &o) {
                     while (q < stop && !is_num(*q)) ++q;
                     const float fv = (float)fast_atof(q, stop);
                     while (q < stop && is_num(*q)) ++q;
-                    o.col.push_back(fid - 1);
-                    o.val.push_back(fv);
-                    o.maxf = std::max(o.maxf, fid);
+                    if (fid >= 1) {  // LibSVM indices are 1-based; 0 or a negative index names no column and is dropped
+                        o.col.push_back(fid - 1);
+                        o.val.push_back(fv);
+                        o.maxf = std::max(o.maxf, fid);
+                    }
                 }
             }
             o.row_nnz.push_back((int)(o.col.size() - before));
@@ -267,6 +269,7 @@ void DataSet::load_from_file(const std::string &file, GBMParam &param) {
 // src/thundergbm/parser.cpp:9-100: defaults, then `key=value` lines of the conf file, then argv.
 void parse_param(GBMParam &mp, int argc, char **argv) {
     mp = GBMParam();
+    mp.hist_mode = default_hist_mode();  // TGBM_HIST_MODE, else fp32; the conf key hist_mode overrides it
     auto parse_value = [&](const char *name_val) {
         char name[256], val[256];
         if (sscanf(name_val, "%255[^=]=%255s", name, val) != 2) return;

@@ -45,6 +45,11 @@ struct TreeCtl {  // device-side scalars of the tree being built
     int n_part_tiles[2];  // by level parity: level l+1 is planned while level l is still being scattered
     int n_records;  // records alive at the current level
     unsigned long long stat_rows_root, stat_rows_gather, stat_hists, stat_part_rows;
+    // single-pass partition: next tile to hand out, tag of the running pass in the tile status words, and a word the
+    // host reads after a sync: non-zero when a bounded wait gave up (1 + the tile that waited)
+    int part_ticket;
+    unsigned part_epoch;
+    int error;
 };
 
 struct SplitRec {  // best candidate of one (node, feature)
@@ -1130,10 +1135,19 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
 // so that the partition kernels do not search for it tile after tile).  Called by every thread of a 1024-thread block.
 __device__ inline int tile_owner(const int *__restrict__ node_tile0, int nl, int t);
 __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0,
-                                 int *__restrict__ tile_node, TreeCtl *__restrict__ ctl, bool count_rows = true) {
+                                 int *__restrict__ tile_node, TreeCtl *__restrict__ ctl, bool count_rows, int *__restrict__ part_base,
+                                 int *__restrict__ child_begin, int *__restrict__ child_cnt) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     const int nl = 1 << level;
+    // single-pass partition: where the children of node n go in the two output halves = records of the nodes before it;
+    // a node without records has no tile that could write its children's (empty) segments
+    block_scan_excl(nl, [&](int n) { return seg_cnt[n]; },
+                    [&](int n, int b) {
+                        part_base[n] = b;
+                        if (seg_cnt[n] == 0 && child_cnt) { child_cnt[2 * n] = 0; child_cnt[2 * n + 1] = 0; child_begin[2 * n] = b; child_begin[2 * n + 1] = b; }
+                    }, scratch);
+    if (threadIdx.x == 0) { ctl->part_ticket = 0; ctl->part_epoch = (ctl->part_epoch + 1) & 0x3fffffffu; }
     if (threadIdx.x == 0) rows = 0;
     __syncthreads();
     const int total = block_scan_excl(nl, [&](int n) { return (seg_cnt[n] + PART_TILE - 1) / PART_TILE; },
@@ -1258,10 +1272,12 @@ static __global__ void __launch_bounds__(1024)
 k_plan_next(int level, const int *__restrict__ next_begin, const int *__restrict__ next_cnt, const int *__restrict__ gcnt,
             const TreeNode *__restrict__ nodes, TreeCtl *__restrict__ ctl, int by_hessian, int *__restrict__ built_right,
             HistWork *__restrict__ work, int *__restrict__ hist_tile_base, int *__restrict__ next_node_tile0, int n_ctas,
-            int *__restrict__ cta_off, int4 *__restrict__ seq, int depth, int *__restrict__ next_tile_node) {
+            int *__restrict__ cta_off, int4 *__restrict__ seq, int depth, int *__restrict__ next_tile_node, int *__restrict__ part_base,
+            int *__restrict__ child_begin, int *__restrict__ child_cnt) {
+    // child_begin / child_cnt: segment table of level + 2, the one the partition of level + 1 will fill
     hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(level + 1, next_cnt, next_node_tile0, next_tile_node, ctl, level + 1 < depth - 1);
+    part_plan(level + 1, next_cnt, next_node_tile0, next_tile_node, ctl, level + 1 < depth - 1, part_base, child_begin, child_cnt);
 }
 
 // work lists of level 0 (the whole data set in the root)
@@ -1269,10 +1285,11 @@ static __global__ void __launch_bounds__(1024)
 k_plan_root(const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt, const int *__restrict__ gcnt,
             const TreeNode *__restrict__ nodes, int *__restrict__ built_right, HistWork *__restrict__ work,
             int *__restrict__ hist_tile_base, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl, int n_ctas, int *__restrict__ cta_off,
-            int4 *__restrict__ seq, int depth, int *__restrict__ tile_node) {
+            int4 *__restrict__ seq, int depth, int *__restrict__ tile_node, int *__restrict__ part_base,
+            int *__restrict__ child_begin, int *__restrict__ child_cnt) {
     hist_plan(0, seg_begin, seg_cnt, gcnt, nodes, 0, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(0, seg_cnt, node_tile0, tile_node, ctl, depth > 1);
+    part_plan(0, seg_cnt, node_tile0, tile_node, ctl, depth > 1, part_base, child_begin, child_cnt);
 }
 
 // Stable scatter of the records into the child segments; records of nodes that stopped splitting are dropped.
@@ -1329,6 +1346,148 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
             const int lefts_before = lefts_before_tile + pre + __popc(m[j] & ((1u << lane) - 1u));
             const int rank = left ? lefts_before : (p - b) - lefts_before;
             const int d = (left ? next_begin[2 * n] : next_begin[2 * n + 1]) + rank;
+            out_idx[d] = r[j];
+            out_gh[d] = g[j];
+        }
+    }
+}
+
+
+// ---- the same in one pass ----------------------------------------------------------------------------------------
+// Count, prefix and scatter of a level in ONE kernel.  The output list has two halves: the left children of all nodes
+// go to the first half, the right children to the second, both at offset part_base[n] = records of the nodes before
+// node n.  A record's place then depends only on how many records BEFORE it in its own node go left -- a prefix
+// inside the node, which the tiles of a node pass along by decoupled look-back: every tile publishes its own left
+// count at once ("aggregate") and, as soon as it has summed up its predecessors, its inclusive prefix.  Tiles are
+// handed out in ascending order by a ticket, so a tile only ever waits for tiles that are already running.
+// The waits are bounded: a tile that gives up records itself in ctl->error and goes on (the host checks the word
+// after its next sync), so no GPU is ever left spinning.
+// Stable: the rows of either child ascend like those of the node.  Records of nodes that stopped splitting drop out.
+constexpr unsigned long long PART_AGG = 1ull << 32, PART_PREFIX = 2ull << 32;
+constexpr int PART_WAIT_LIMIT = 1 << 22;  // polls of ~50 ns each
+
+__device__ __forceinline__ unsigned long long part_status_wait(const unsigned long long *p, unsigned epoch, TreeCtl *ctl, int tile) {
+    for (int it = 0; it < PART_WAIT_LIMIT; ++it) {
+        const unsigned long long s = *reinterpret_cast<const volatile unsigned long long *>(p);
+        if ((unsigned)(s >> 34) == epoch) return s;
+        __nanosleep(40);
+    }
+    atomicCAS(&ctl->error, 0, 1 + tile);
+    return ((unsigned long long)epoch << 34) | PART_PREFIX;  // acts as "nothing before": the result is wrong, the error word says so
+}
+
+template <bool SPARSE>
+static __global__ void __launch_bounds__(PART_THREADS)
+k_part_one(int level, const TreeNode *__restrict__ nodes, const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt,
+           const int *__restrict__ node_tile0, const int *__restrict__ tile_node, const int *__restrict__ part_base,
+           TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx, const int2 *__restrict__ rec_gh,
+           const unsigned char *__restrict__ binsT, size_t Npad, const int *__restrict__ sp_row_ptr,
+           const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr, unsigned long long *__restrict__ status,
+           int *__restrict__ next_begin, int *__restrict__ next_cnt, int *__restrict__ out_idx, int2 *__restrict__ out_gh,
+           int half) {
+    constexpr int WORDS = PART_TILE / 32;        // ballot words of a tile, in record order
+    constexpr int WARPS = PART_THREADS / 32;
+    __shared__ int s_tile, s_before;
+    __shared__ int wpre[WORDS];
+    const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
+    const unsigned epoch = ctl->part_epoch;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (;;) {
+        __syncthreads();  // s_tile, s_before, wpre of the previous tile have been read
+        if (threadIdx.x == 0) s_tile = atomicAdd(&ctl->part_ticket, 1);
+        __syncthreads();
+        const int t = s_tile;
+        if (t >= nt) break;
+        const int n = tile_node[t];
+        const TreeNode nd = nodes[nl - 1 + n];
+        const int t0 = node_tile0[n], k = t - t0, cnt = seg_cnt[n];
+        const int base = part_base[n];
+        if (!(nd.is_valid && !nd.is_leaf)) {  // finished node: its rows leave the lists
+            if (k == 0 && threadIdx.x == 0) { next_cnt[2 * n] = 0; next_cnt[2 * n + 1] = 0; next_begin[2 * n] = base; next_begin[2 * n + 1] = half + base; }
+            continue;
+        }
+        const int p0 = seg_begin[n] + k * PART_TILE, end = seg_begin[n] + cnt;
+        int r[PART_RPT];
+        int2 g[PART_RPT];
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) {
+            const int p = p0 + j * PART_THREADS + threadIdx.x;
+            r[j] = p < end ? (rec_idx ? rec_idx[p] : p) : -1;
+            if (p < end) g[j] = rec_gh[p];
+        }
+        unsigned char b[PART_RPT];
+        if (SPARSE) {
+            const int c0 = cut_ptr[nd.split_feature_id], c1 = cut_ptr[nd.split_feature_id + 1];
+#pragma unroll
+            for (int j = 0; j < PART_RPT; ++j) {
+                b[j] = MISSING_BIN;
+                if (r[j] >= 0) {
+                    int lo = sp_row_ptr[r[j]], hi = sp_row_ptr[r[j] + 1];  // bin ids ascend inside a row
+                    while (lo < hi) {
+                        const int mid = lo + (hi - lo) / 2, v = sp_bin[mid];
+                        if (v >= c0 && v < c1) { b[j] = (unsigned char)(v - c0); break; }
+                        if (v < c0) lo = mid + 1; else hi = mid;
+                    }
+                }
+            }
+        } else {
+            const unsigned char *colp = binsT + (size_t)nd.split_feature_id * Npad;
+#pragma unroll
+            for (int j = 0; j < PART_RPT; ++j) b[j] = r[j] >= 0 ? colp[r[j]] : 0;
+        }
+        unsigned m[PART_RPT];
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) {
+            const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (b[j] < nd.split_bid));
+            m[j] = __ballot_sync(0xffffffffu, left);
+            if (lane == 0) wpre[j * WARPS + warp] = __popc(m[j]);
+        }
+        __syncthreads();
+        // exclusive prefix over the tile's ballot words (WORDS = 64: two per lane of warp 0), look-back for the
+        // left count of the node's earlier tiles
+        if (warp == 0) {
+            const int c0 = wpre[2 * lane], c1 = wpre[2 * lane + 1];
+            int v = c0 + c1;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, v, o); if (lane >= o) v += u; }
+            const int total = __shfl_sync(0xffffffffu, v, 31);
+            wpre[2 * lane] = v - c0 - c1;
+            wpre[2 * lane + 1] = v - c1;
+            int before = 0;
+            const unsigned long long tag = (unsigned long long)epoch << 34;
+            if (k > 0) {
+                if (lane == 0) *reinterpret_cast<volatile unsigned long long *>(status + t) = tag | PART_AGG | (unsigned)total;
+                for (int look = t - 1;; look -= 32) {
+                    const int idx = look - lane;
+                    unsigned long long st = tag | PART_PREFIX;  // before the node's first tile: nothing
+                    if (idx >= t0) st = part_status_wait(status + idx, epoch, ctl, t);
+                    const unsigned stop = __ballot_sync(0xffffffffu, (st & PART_PREFIX) != 0);
+                    const int first = stop ? __ffs(stop) - 1 : 32;
+                    int add = lane <= first ? (int)(unsigned)(st & 0xffffffffull) : 0;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) add += __shfl_xor_sync(0xffffffffu, add, o);
+                    before += add;
+                    if (stop) break;
+                }
+            }
+            if (lane == 0) {
+                *reinterpret_cast<volatile unsigned long long *>(status + t) = tag | PART_PREFIX | (unsigned)(before + total);
+                s_before = before;
+                if (t == node_tile0[n + 1] - 1) {  // the node's last tile knows the node's left count
+                    next_cnt[2 * n] = before + total; next_cnt[2 * n + 1] = cnt - (before + total);
+                    next_begin[2 * n] = base; next_begin[2 * n + 1] = half + base;
+                }
+            }
+        }
+        __syncthreads();
+        const int before = s_before;
+#pragma unroll
+        for (int j = 0; j < PART_RPT; ++j) {
+            if (r[j] < 0) continue;
+            const int q = k * PART_TILE + j * PART_THREADS + threadIdx.x;  // position in the node
+            const bool left = (m[j] >> lane) & 1u;
+            const int lefts_before = before + wpre[j * WARPS + warp] + __popc(m[j] & ((1u << lane) - 1u));
+            const int d = left ? base + lefts_before : half + base + (q - lefts_before);
             out_idx[d] = r[j];
             out_gh[d] = g[j];
         }

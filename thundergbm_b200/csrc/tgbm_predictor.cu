@@ -126,6 +126,114 @@ k_predict_csr_staged(const int *__restrict__ row_ptr, const int *__restrict__ co
     }
 }
 
+
+// ---- tiled traversal ---------------------------------------------------------------------------------------------
+// The same two arithmetics (dense path: double accumulator, missing = +inf; CSR path: float accumulator with one fused
+// multiply-add per tree, missing = a slot never stored) with everything a step touches in shared memory:
+//   * the trees of a chunk as 8-byte records in heap order (the node table IS a heap: children of i are 2i+1, 2i+2,
+//     checked on the host), so a step is one 8-byte read of the node and one 4-byte read of the row's feature;
+//   * the rows of a tile spread out as [feature][row] (bank = row: no conflicts whatever features the lanes ask for);
+//   * RPT rows per thread walk a tree level by level side by side -- a walk is a chain of dependent shared-memory
+//     reads, several independent chains per thread keep the pipeline busy.
+// Trees are visited in ascending round order for every row, so the sums are those of the one-thread-per-row kernels
+// bit for bit.  CTAs are persistent and loop over the row tiles.
+struct HNode { float v; int fid; };  // split value or leaf weight; feature id, bit 31 = leaf, bit 30 = default right
+constexpr int PT_THREADS = 256;
+
+template <bool DENSE_PATH, int RPT>
+__global__ void __launch_bounds__(PT_THREADS)
+k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F,
+                const HNode *__restrict__ model, int n_rounds, int K, int n_nodes, int depth, int chunk_trees, float lr,
+                float base_score, float *__restrict__ out) {
+    extern __shared__ __align__(16) unsigned char pt_sm[];
+    constexpr int ROWS = PT_THREADS * RPT;
+    float *dense = reinterpret_cast<float *>(pt_sm);                                   // [F][ROWS]
+    HNode *trees = reinterpret_cast<HNode *>(pt_sm + sizeof(float) * (size_t)F * ROWS);  // [chunk_trees][n_nodes]
+    const float absent = DENSE_PATH ? INFINITY : __uint_as_float(PRED_ABSENT);
+    const int n_tiles = (n_rows + ROWS - 1) / ROWS;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        __syncthreads();  // the previous tile's walks are over
+        for (int i = threadIdx.x; i < F * ROWS; i += PT_THREADS) dense[i] = absent;
+        __syncthreads();
+        const int row0 = tile * ROWS;
+#pragma unroll
+        for (int j = 0; j < RPT; ++j) {
+            const int q = j * PT_THREADS + threadIdx.x, i = row0 + q;
+            if (i < n_rows)
+                for (int e = row_ptr[i]; e < row_ptr[i + 1]; ++e) {
+                    const int c = col[e];
+                    if (c >= 0 && c < F) dense[c * ROWS + q] = val[e];
+                }
+        }
+        for (int t = 0; t < K; ++t) {
+            double dsum[RPT];
+            float fsum[RPT];
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) { dsum[j] = base_score; fsum[j] = base_score; }
+            for (int r0 = 0; r0 < n_rounds; r0 += chunk_trees) {
+                const int nc = min(chunk_trees, n_rounds - r0);
+                __syncthreads();  // the previous chunk is no longer read (and the rows are in place)
+                for (int i = threadIdx.x; i < nc * n_nodes; i += PT_THREADS)
+                    trees[i] = model[((size_t)(r0 + i / n_nodes) * K + t) * n_nodes + i % n_nodes];
+                __syncthreads();
+                for (int c = 0; c < nc; ++c) {
+                    const HNode *nd = trees + (size_t)c * n_nodes;
+                    int cur[RPT];
+#pragma unroll
+                    for (int j = 0; j < RPT; ++j) cur[j] = 0;
+                    for (int lvl = 0; lvl < depth; ++lvl) {
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) {
+                            const HNode h = nd[cur[j]];
+                            if (h.fid >= 0) {  // not a leaf
+                                const int f = h.fid & 0x3fffffff;
+                                const float fv = f < F ? dense[f * ROWS + j * PT_THREADS + threadIdx.x] : absent;
+                                const bool present = DENSE_PATH ? (fv < INFINITY) : (__float_as_uint(fv) != PRED_ABSENT);
+                                const bool right = present ? !(fv < h.v) : (h.fid & 0x40000000) != 0;
+                                cur[j] = 2 * cur[j] + 1 + (right ? 1 : 0);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < RPT; ++j) {
+                        const float w = nd[cur[j]].v;
+                        if (DENSE_PATH) dsum[j] += (double)__fmul_rn(lr, w);
+                        else fsum[j] = __fmaf_rn(lr, w, fsum[j]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < RPT; ++j) {
+                const int i = row0 + j * PT_THREADS + threadIdx.x;
+                if (i < n_rows) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
+            }
+        }
+    }
+}
+
+template <bool DENSE_PATH>
+static bool launch_predict_tiles(const int *rp, const int *col, const float *val, int N, int F, const HNode *model, int n_rounds, int K,
+                                 int n_nodes, int depth, float lr, float base_score, float *out, int num_sms, cudaStream_t st) {
+    const size_t budget = 200 * 1024, tree_bytes = sizeof(HNode) * (size_t)n_nodes;
+    for (int rpt : {4, 2, 1}) {
+        const size_t rows_bytes = sizeof(float) * (size_t)F * PT_THREADS * rpt;
+        if (rows_bytes + std::min<size_t>(8, n_rounds) * tree_bytes > budget) continue;  // at least 8 trees (or all) per chunk
+        const int chunk = (int)std::min<size_t>(std::min<size_t>(64, n_rounds), (budget - rows_bytes) / tree_bytes);
+        const size_t smem = rows_bytes + chunk * tree_bytes;
+        const int tiles = (N + PT_THREADS * rpt - 1) / (PT_THREADS * rpt);
+        const int grid = std::max(1, std::min(tiles, num_sms));
+        auto go = [&](auto kern) {
+            TGBM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            kern<<<grid, PT_THREADS, smem, st>>>(rp, col, val, N, F, model, n_rounds, K, n_nodes, depth, chunk, lr, base_score, out);
+        };
+        if (rpt == 4) go(k_predict_tiles<DENSE_PATH, 4>);
+        else if (rpt == 2) go(k_predict_tiles<DENSE_PATH, 2>);
+        else go(k_predict_tiles<DENSE_PATH, 1>);
+        return true;
+    }
+    return false;
+}
+
 void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model, float learning_rate, float base_score,
                  std::vector<float> &out, float *kernel_ms) {
     const int N = ds.n_rows;
@@ -148,23 +256,65 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
                 else { d.v = s.split_value; d.fid = (s.split_feature_id & 0x3fffffff) | (s.default_right ? 0x40000000 : 0); }
             }
         }
-    cudaStream_t st;
-    TGBM_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+    // is every tree a heap (children of i at 2i+1, 2i+2)?  The trainers here and the reference's Tree::init2 build them so.
+    bool heap = ((n_nodes + 1) & n_nodes) == 0;
+    int depth = 0;
+    while ((2 << depth) - 1 < n_nodes) ++depth;
+    std::vector<HNode> hflat;
+    if (heap) {
+        hflat.resize(flat.size());
+        for (size_t i = 0; i < flat.size() && heap; ++i) {
+            const int n = (int)(i % n_nodes);
+            const PNode &s = flat[i];
+            if (!(s.fid & 0x80000000) && (s.lch != 2 * n + 1 || s.rch != 2 * n + 2 || s.rch >= n_nodes)) heap = false;
+            hflat[i].v = s.v;
+            hflat[i].fid = s.fid;
+        }
+    }
+    // streams and events are released on every way out, also when a CUDA call throws
+    struct Guard {
+        cudaStream_t st = nullptr;
+        cudaEvent_t e0 = nullptr, e1 = nullptr;
+        ~Guard() {
+            if (e0) cudaEventDestroy(e0);
+            if (e1) cudaEventDestroy(e1);
+            if (st) cudaStreamDestroy(st);
+        }
+    } gd;
+    TGBM_CUDA(cudaStreamCreateWithFlags(&gd.st, cudaStreamNonBlocking));
+    cudaStream_t st = gd.st;
     const size_t nnz = (size_t)ds.rp[N];
     DevBuf<int> d_rp, d_col;
     DevBuf<float> d_val, d_out;
     DevBuf<PNode> d_model;
+    DevBuf<HNode> d_hmodel;
     d_rp.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1)); d_out.alloc((size_t)N * K);
-    d_model.alloc(flat.size());
     TGBM_CUDA(cudaMemcpyAsync(d_rp.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, st));
     TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, st));
     TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, st));
+    if (heap) {
+        d_hmodel.alloc(hflat.size());
+        TGBM_CUDA(cudaMemcpyAsync(d_hmodel.p, hflat.data(), sizeof(HNode) * hflat.size(), cudaMemcpyHostToDevice, st));
+    }
+    d_model.alloc(flat.size());
     TGBM_CUDA(cudaMemcpyAsync(d_model.p, flat.data(), sizeof(PNode) * flat.size(), cudaMemcpyHostToDevice, st));
     const int F = ds.n_features;
     const size_t smem = (size_t)F * PRED_ROWS * sizeof(float);
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&e0)); TGBM_CUDA(cudaEventCreate(&e1)); TGBM_CUDA(cudaEventRecord(e0, st)); }
-    if (smem <= 48 * 1024) {
+    int dev = 0, num_sms = 148;
+    TGBM_CUDA(cudaGetDevice(&dev));
+    TGBM_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
+    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
+    // The reference chooses its arithmetic by F * 128 * 4 <= 48 KB (predictor.cu:88); that choice is kept, the tiled
+    // kernel serves either whenever a tile of rows and a chunk of trees fit the shared memory of an SM.
+    const bool dense_path = smem <= 48 * 1024;
+    bool done = false;
+    if (heap && getenv("TGBM_PREDICT_SIMPLE") == nullptr)
+        done = dense_path ? launch_predict_tiles<true>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
+                                                       base_score, d_out.p, num_sms, st)
+                          : launch_predict_tiles<false>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
+                                                        base_score, d_out.p, num_sms, st);
+    if (done) {
+    } else if (dense_path) {
         k_predict_dense<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds, K,
                                                                                 n_nodes, learning_rate, base_score, d_out.p);
     } else if (smem <= 200 * 1024) {
@@ -176,11 +326,10 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
                                                        base_score, d_out.p);
     }
     TGBM_CUDA(cudaGetLastError());
-    if (kernel_ms) TGBM_CUDA(cudaEventRecord(e1, st));
+    if (kernel_ms) TGBM_CUDA(cudaEventRecord(gd.e1, st));
     TGBM_CUDA(cudaMemcpyAsync(out.data(), d_out.p, sizeof(float) * out.size(), cudaMemcpyDeviceToHost, st));
     TGBM_CUDA(cudaStreamSynchronize(st));
-    if (kernel_ms) { TGBM_CUDA(cudaEventElapsedTime(kernel_ms, e0, e1)); cudaEventDestroy(e0); cudaEventDestroy(e1); }
-    cudaStreamDestroy(st);
+    if (kernel_ms) TGBM_CUDA(cudaEventElapsedTime(kernel_ms, gd.e0, gd.e1));
 }
 
 // ---- predict_transform -------------------------------------------------------------------------
@@ -239,7 +388,7 @@ float metric_score(int objective, const DataSet &ds, int num_class, const std::v
     TGBM_CUDA(cudaMemcpy(d_raw.p, raw.data(), sizeof(float) * raw.size(), cudaMemcpyHostToDevice));
     if (need_group_file(objective)) {
         RankState rs;
-        rs.init(ds, objective, N, nullptr);
+        rs.init(ds, objective, N, nullptr, 0, (long long)ds.group.size());
         rs.metric(objective, d_raw.p, d_out.p, nullptr, N, nullptr);
     } else {
         DevBuf<double> partial, sum;

@@ -178,14 +178,25 @@ struct RankState {
     DevBuf<float> idcg, log2tab, y, group_score;
     DevBuf<double> sum;
 
-    void init(const DataSet &ds, int objective, int n_rows, cudaStream_t stream) {
+    // Rank-local checks of the query groups.  Called before the first collective of Booster::init, so that a rank with
+    // bad groups stops together with its peers instead of leaving them inside a collective.
+    static void validate(const DataSet &ds, int n_rows) {
+        long long total = 0;
+        int longest = 0;
+        for (int g : ds.group) { TGBM_CHECK(g >= 0, "negative query group size"); total += g; longest = std::max(longest, g); }
+        TGBM_CHECK(total == n_rows, "group sizes must add up to the number of rows");
+        TGBM_CHECK(longest <= RANK_MAX_GROUP, "query groups of more than 4096 rows are not supported");
+    }
+
+    // first_group / total_groups: global index of this rank's first query group and the number of groups over all ranks
+    // (the partner sampling is keyed by the global group index, the metric is the mean over all groups)
+    void init(const DataSet &ds, int objective, int n_rows, cudaStream_t stream, long long first_group, long long total_groups) {
         N = n_rows;
         const float *labels = ds.yv ? ds.yv : ds.y.data();
         n_group = (int)ds.group.size();
         std::vector<int> h(n_group + 1, 0);
         for (int i = 0; i < n_group; ++i) { h[i + 1] = h[i] + ds.group[i]; max_len = std::max(max_len, ds.group[i]); }
-        TGBM_CHECK(h[n_group] == n_rows, "group sizes must add up to the number of rows");
-        TGBM_CHECK(max_len <= RANK_MAX_GROUP, "query groups of more than 4096 rows are not supported");
+        validate(ds, n_rows);
         // NDCG::get_IDCG (rank_metric.cpp:102-123), host code in the reference as well
         std::vector<float> hid(std::max(n_group, 1), 0.f);
         std::vector<float> ltab(std::max(max_len, 1));
@@ -205,7 +216,8 @@ struct RankState {
         TGBM_CUDA(cudaMemcpyAsync(log2tab.p, ltab.data(), sizeof(float) * ltab.size(), cudaMemcpyHostToDevice, stream));
         TGBM_CUDA(cudaMemcpyAsync(y.p, labels, sizeof(float) * n_rows, cudaMemcpyHostToDevice, stream));
         TGBM_CUDA(cudaStreamSynchronize(stream));
-        n_group_total = n_group;
+        n_group_total = total_groups;
+        group_offset = (uint32_t)first_group;
         idcg_used = objective == RANK_NDCG;
         int P = 1;
         while (P < max_len) P <<= 1;
