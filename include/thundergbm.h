@@ -81,6 +81,9 @@ typedef struct {
     int hist_mode;      /* histogram arithmetic: 0 fp32 -- float (g,h) added value by value into one accumulator per bin,
                            what the reference does (hist_tree_builder_single.cu:203-216, :485-505); 1 exact -- integer sums
                            on a fixed-point grid, bit-identical from run to run and for any number of GPUs */
+    int bagging;        /* RowSampler::do_bagging (src/thundergbm/row_sampler.cu:9-35): bootstrap multiplicities on (g,h) */
+    float column_sampling_rate; /* Shard::column_sampling (src/thundergbm/builder/shard.cu:8-23); 1 = off */
+    unsigned sample_seed;       /* seed of both samplers (the reference draws from std::rand()) */
 } TgbmParam;
 
 typedef struct {

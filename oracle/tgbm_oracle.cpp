@@ -74,6 +74,9 @@ struct TgoParam {
     int keep_nid;     // keep ins2node_id of every tree (tests only)
     int portable_exp; // 1: use the portable expf shared with the CUDA path, 0: libm expf
     unsigned rank_seed;
+    int bagging;                // RowSampler::do_bagging
+    float column_sampling_rate; // Shard::column_sampling, 1 = off
+    unsigned sample_seed;
 };
 }
 
@@ -131,6 +134,7 @@ struct Ctx {
     std::vector<double> quant_scale;  // per round: 2^s_g, 2^s_h
     std::vector<double> round_seconds;
     std::vector<float> gain2;  // [tree][n_nodes]: runner-up |gain| at every evaluated node (how decisive the split was)
+    std::vector<unsigned char> ignored;  // column-sampling mask of the running round (empty = no sampling)
     double train_seconds = 0, init_seconds = 0;
     float expf_(float x) const { return p.portable_exp ? portable_expf(x) : expf(x); }
 };
@@ -458,6 +462,7 @@ struct Builder {
         for (int f = 0; f < c.F; ++f) {
             const int b0 = c.cut_ptr[f], b1 = c.cut_ptr[f + 1];
             if (b0 == b1) continue;
+            if (!c.ignored.empty() && c.ignored[f]) continue;  // hist_tree_builder_single.cu:304,663
             if (c.p.hist_mode == 1) {
                 double ag = 0, ah = 0;
                 for (int i = b0; i < b1; ++i) { ag += H.g[i]; ah += H.h[i]; Pg[i] = to_f(ag, q.sg); Ph[i] = to_f(ah, q.sh); }
@@ -627,6 +632,34 @@ struct Builder {
     }
 };
 
+// src/thundergbm/row_sampler.cu:9-35 do_bagging: M = size of the gradient array (num_class x rows) draws of a uniform
+// entry of that array; every entry's (g,h) is multiplied by the number of times it was drawn.  The reference seeds
+// thrust's generator from std::rand(); draw j of round r is a counter-based hash here (shared with the CUDA path).
+void do_bagging(const Ctx &c, int round, GH *gh) {
+    const uint64_t M = (uint64_t)std::max(c.p.num_class, 1) * (uint64_t)c.N;
+    std::vector<int> count((size_t)c.K * c.N, 0);
+    for (uint64_t j = 0; j < M; ++j) {
+        const uint32_t r = mix32(c.p.sample_seed ^ 0xBA661D6Eu, (uint32_t)round, (uint32_t)(j >> 32), (uint32_t)j);
+        const uint64_t e = ((uint64_t)r * M) >> 32;
+        if (e < (uint64_t)c.K * c.N) count[e]++;
+    }
+    for (size_t i = 0; i < count.size(); ++i) { gh[i].g = gh[i].g * (float)count[i]; gh[i].h = gh[i].h * (float)count[i]; }
+}
+
+// src/thundergbm/builder/shard.cu:8-23 column_sampling, once per round (tree_builder.cu:150-152): max(1, int(F * rate))
+// randomly chosen features are put into the ignored set -- the rate is the share that is LEFT OUT.  The reference
+// shuffles with std::random_shuffle / rand(); here the features with the smallest hash of (seed, round, feature).
+void column_sampling(Ctx &c, int round) {
+    c.ignored.clear();
+    if (!(c.p.column_sampling_rate < 1.f)) return;
+    const int F = c.F, n_ignored = std::min(F, std::max(1, (int)(F * c.p.column_sampling_rate)));
+    std::vector<std::pair<uint32_t, int>> key(F);
+    for (int f = 0; f < F; ++f) key[f] = {mix32(c.p.sample_seed ^ 0xC01A5EEDu, (uint32_t)round, 0u, (uint32_t)f), f};
+    std::sort(key.begin(), key.end());
+    c.ignored.assign(F, 0);
+    for (int i = 0; i < n_ignored; ++i) c.ignored[key[i].second] = 1;
+}
+
 // include/thundergbm/objective/regression_obj.h:35-53 (reg) and :95-114 (binary:logistic)
 void init_base_score(Ctx &c, std::vector<GH> &gh) {
     c.base_score = 0;
@@ -737,6 +770,8 @@ void train(Ctx &c) {
     for (int r = 0; r < c.p.n_trees; ++r) {  // src/thundergbm/trainer.cu:44-47, include/thundergbm/booster.h:76-93
         const double tr0 = now_s();
         get_gradient(c, r, c.ypred.data(), gh.data());
+        if (c.p.bagging) do_bagging(c, r, gh.data());  // include/thundergbm/booster.h:83
+        column_sampling(c, r);                         // tree_builder.cu:150-152
         Quant q;
         if (c.p.hist_mode == 1) q = choose_quant(c, gh.data(), (size_t)K * N);
         c.quant_scale.push_back(q.sg); c.quant_scale.push_back(q.sh);

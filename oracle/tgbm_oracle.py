@@ -27,7 +27,8 @@ class TgoParam(C.Structure):
     _fields_ = [('depth', C.c_int), ('n_trees', C.c_int), ('max_num_bin', C.c_int), ('objective', C.c_int),
                 ('num_class', C.c_int), ('lambda_', C.c_float), ('gamma', C.c_float), ('min_child_weight', C.c_float),
                 ('rt_eps', C.c_float), ('learning_rate', C.c_float), ('hist_mode', C.c_int), ('quant_bits', C.c_int),
-                ('n_threads', C.c_int), ('keep_nid', C.c_int), ('portable_exp', C.c_int), ('rank_seed', C.c_uint)]
+                ('n_threads', C.c_int), ('keep_nid', C.c_int), ('portable_exp', C.c_int), ('rank_seed', C.c_uint),
+                ('bagging', C.c_int), ('column_sampling_rate', C.c_float), ('sample_seed', C.c_uint)]
 
 
 def build() -> str:
@@ -85,12 +86,13 @@ class Result:
 
 def train(data, objective='reg:linear', depth=6, n_trees=40, max_num_bin=255, learning_rate=1.0, gamma=1.0,
           min_child_weight=1.0, hist_mode=1, quant_bits=18, n_threads=0, keep_nid=0, portable_exp=1, rank_seed=0,
-          num_class=1, rt_eps=1e-6, tree_method='hist', **kw):
+          num_class=1, rt_eps=1e-6, tree_method='hist', bagging=0, column_sampling_rate=1.0, sample_seed=0, **kw):
     lam = kw.pop('lambda', kw.pop('lambda_', 1.0))
     assert not kw, kw
     l = lib()
     p = TgoParam(depth, n_trees, max_num_bin, OBJECTIVES[objective], num_class, lam, gamma, min_child_weight, rt_eps,
-                 learning_rate, hist_mode, quant_bits, n_threads, keep_nid, portable_exp, rank_seed)
+                 learning_rate, hist_mode, quant_bits, n_threads, keep_nid, portable_exp, rank_seed, int(bagging),
+                 column_sampling_rate, sample_seed)
     rp = np.ascontiguousarray(data.row_ptr, np.int32); col = np.ascontiguousarray(data.col, np.int32)
     val = np.ascontiguousarray(data.val, np.float32); y = np.ascontiguousarray(data.y, np.float32)
     grp = np.ascontiguousarray(data.group, np.int32)

@@ -132,7 +132,8 @@ def compare_with_noise(ref, mine, dG, dH, rel=1e-5, lam=1.0, runner_up=None):
     Where the trees part, the node must be a near-tie: with `runner_up` (the second-best |gain| of every node in `ref`'s
     run) the best and the second-best gain are within the gain noise of each other.  Returns a dict with the number of
     nodes compared, the worst ratios difference / tolerance and the nodes that broke a rule."""
-    out = dict(compared=0, worst_gain=0.0, worst_weight=0.0, bad_gain=[], bad_weight=[], bad_split=[], parted=[])
+    out = dict(compared=0, worst_gain=0.0, worst_weight=0.0, bad_gain=[], bad_weight=[], bad_split=[], parted=[],
+               ratios_gain=[], ratios_weight=[])
     stack = [0]
     while stack:
         i = stack.pop()
@@ -145,6 +146,7 @@ def compare_with_noise(ref, mine, dG, dH, rel=1e-5, lam=1.0, runner_up=None):
         tw = rel * abs(float(x['base_weight'])) + weight_noise(ref, i, dG, dH, lam)
         rw = abs(float(x['base_weight']) - float(y['base_weight'])) / max(tw, 1e-30)
         out['worst_weight'] = max(out['worst_weight'], rw)
+        out['ratios_weight'].append(rw)
         if rw > 1.0:
             out['bad_weight'].append(i)
         xs = x['split_feature_id'] >= 0 and x['gain'] > 0 and x['lch_index'] > 0
@@ -163,6 +165,7 @@ def compare_with_noise(ref, mine, dG, dH, rel=1e-5, lam=1.0, runner_up=None):
             tg = rel * abs(float(x['gain'])) + noise
             rg = abs(float(x['gain']) - float(y['gain'])) / tg
             out['worst_gain'] = max(out['worst_gain'], rg)
+            out['ratios_gain'].append(rg)
             if rg > 1.0:
                 out['bad_gain'].append(i)
             if bool(x['default_right']) != bool(y['default_right']) and x['lch_index'] < len(ref):
@@ -174,3 +177,14 @@ def compare_with_noise(ref, mine, dG, dH, rel=1e-5, lam=1.0, runner_up=None):
             if x['lch_index'] < len(ref):
                 stack.extend([int(x['lch_index']), int(x['rch_index'])])
     return out
+
+
+def within_noise(r, hard=4.0, share=0.9):
+    """The noise is random: of the nodes compared by compare_with_noise, at least `share` must sit inside their tolerance
+    and none further out than `hard` times it."""
+    ok = True
+    for key in ('ratios_gain', 'ratios_weight'):
+        v = np.asarray(r[key])
+        if v.size:
+            ok = ok and float(v.max()) <= hard and float(np.mean(v <= 1.0)) >= share
+    return ok

@@ -131,3 +131,23 @@ def test_exact_mode_is_thread_count_invariant(orc, cases):
     a = orc.train(d, hist_mode=1, n_threads=1, **p)
     b = orc.train(d, hist_mode=1, n_threads=4, **p)
     assert a.trees.tobytes() == b.trees.tobytes() and np.array_equal(a.ypred, b.ypred)
+
+
+def test_oracle_sampling_restatement(orc, cases):
+    """Bagging multiplies every gradient by its multiplicity in a bootstrap sample of the gradient array
+    (src/thundergbm/row_sampler.cu:9-35); column sampling leaves max(1, int(F * rate)) features out of the split search
+    for a round (src/thundergbm/builder/shard.cu:8-23).  Same seed, same trees; another seed, other trees."""
+    d, params = cases('c1_dense_reg')
+    p = {**params, 'n_trees': 3}
+    plain = orc.train(d, **p)
+    a = orc.train(d, bagging=1, column_sampling_rate=0.5, sample_seed=5, **p)
+    b = orc.train(d, bagging=1, column_sampling_rate=0.5, sample_seed=5, **p)
+    c = orc.train(d, bagging=1, column_sampling_rate=0.5, sample_seed=6, **p)
+    assert a.trees.tobytes() == b.trees.tobytes() != c.trees.tobytes()
+    assert a.trees.tobytes() != plain.trees.tobytes()
+    for r in range(3):
+        t = a.trees[r, 0]
+        used = set(t['split_feature_id'][(t['is_valid'] != 0) & (t['split_feature_id'] >= 0)].tolist())
+        assert 1 <= len(used) <= 16          # 32 features, half of them ignored in every round
+    # the root of a bagged tree sums multiplicity-weighted hessians: reg:linear has h = 1, so sum_h = number of draws kept
+    assert abs(float(a.trees[0, 0][0]['sum_h']) - d.n_rows) < 5 * np.sqrt(d.n_rows)

@@ -49,15 +49,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
         if p.returncode:
             raise RuntimeError(f'nvcc failed on {s}')
     if force or procs or not os.path.exists(LIB):
+        # linked beside the target and renamed: whoever copies or loads the tree meanwhile sees a complete library
         subprocess.check_call([NVCC, '-shared', '-gencode', 'arch=compute_100a,code=sm_100a', '-ccbin', '/usr/bin/g++',
-                               '-o', LIB] + objs + ['-ldl'])
+                               '-o', LIB + '.tmp'] + objs + ['-ldl'])
+        os.replace(LIB + '.tmp', LIB)
     os.makedirs(BIN, exist_ok=True)
     for name in ('thundergbm_train', 'thundergbm_predict'):
         src = os.path.join(CSRC, 'cli', name + '.cu')
         exe = os.path.join(BIN, name.replace('_', '-'))
         if force or _newer(exe, [src, LIB]):
-            subprocess.check_call([NVCC] + FLAGS + [src, '-o', exe, '-L' + HERE, '-lthundergbm',
+            subprocess.check_call([NVCC] + FLAGS + [src, '-o', exe + '.tmp', '-L' + HERE, '-lthundergbm',
                                                     '-Xlinker', '-rpath', '-Xlinker', '$ORIGIN/..'])
+            os.replace(exe + '.tmp', exe)
     return LIB
 
 

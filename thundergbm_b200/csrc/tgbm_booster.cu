@@ -65,6 +65,9 @@ struct BoosterImpl {
     bool f32 = false;
     DevBuf<float2> hist_spread;
     DevBuf<double> sum_partial;
+    CutOffsets f32_cuts{};                 // fp32 dense kernel: first bin of every feature, passed by value
+    DevBuf<int> bag_count;                 // bagging: multiplicity of every gradient entry in the round's bootstrap sample
+    DevBuf<unsigned char> ignored_all;     // column sampling: [round][feature] mask of the features left out
     int f32_stride(int pairs) const {
         if (comm && comm->active()) return 1;  // the built histograms are all-reduced: keep them compact
         return pairs <= 2 ? 8 : pairs <= 8 ? 4 : pairs <= 16 ? 2 : 1;
@@ -89,7 +92,7 @@ struct BoosterImpl {
     DevBuf<int> node_tile0[2], tile_left, tile_node[2];
     DevBuf<int> part_base;                    // single-pass partition: records of the nodes before a node
     DevBuf<unsigned long long> part_status;   // single-pass partition: look-back word of every tile
-    bool part_one = true;
+    bool part_one = false;
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
     DevBuf<double> metric_partial, metric_sum;
@@ -356,8 +359,7 @@ void Booster::init(const DataSet &ds) {
     TGBM_CHECK(p.quant_bits >= 8 && p.quant_bits <= 20, "quant_bits must be in [8, 20]");
     TGBM_CHECK(p.hist_mode == 0 || p.hist_mode == 1, "hist_mode must be 0 (fp32) or 1 (exact)");
     m.f32 = p.hist_mode == 0;
-    TGBM_CHECK(!p.bagging, "bagging is not part of the histogram path implemented here");
-    TGBM_CHECK(p.column_sampling_rate >= 1.0f, "column sampling is not part of the histogram path implemented here");
+    TGBM_CHECK(p.column_sampling_rate > 0.f, "column_sampling_rate must be positive");
     int dev = 0;
     TGBM_CUDA(cudaGetDevice(&dev));
     TGBM_CUDA(cudaDeviceGetAttribute(&m.num_sms, cudaDevAttrMultiProcessorCount, dev));
@@ -455,6 +457,28 @@ void Booster::init(const DataSet &ds) {
     }
     m.ypred.zero(m.stream);
     m.maxbits.alloc(2); m.root_sum.alloc(2 * (size_t)K); m.qinfo.alloc(1);
+    if (p.bagging) {
+        TGBM_CHECK((unsigned long long)std::max(p.num_class, 1) * (unsigned long long)m.N_global < (1ull << 32), "bagging: num_class x rows must fit 32 bits");
+        m.bag_count.alloc(n1 * K);
+    }
+    if (p.column_sampling_rate < 1.f) {
+        // Shard::column_sampling (src/thundergbm/builder/shard.cu:8-23), once per round for all trees of the round:
+        // max(1, int(F * rate)) randomly chosen features are put into the IGNORED set -- the reference's rate is the
+        // share that is left out.  Its shuffle draws from std::rand(); here the features with the smallest hash of
+        // (seed, round, feature) are taken, for all rounds in advance (the boosting loop never returns to the host).
+        const int F = m.F, rounds = std::max(p.n_trees, 1);
+        const int n_ignored = std::max(1, (int)(F * p.column_sampling_rate));
+        std::vector<unsigned char> mask((size_t)rounds * F, 0);
+        std::vector<std::pair<uint32_t, int>> key(F);
+        for (int r = 0; r < rounds; ++r) {
+            for (int f = 0; f < F; ++f) key[f] = {mix32(p.sample_seed ^ 0xC01A5EEDu, (uint32_t)r, 0u, (uint32_t)f), f};
+            std::nth_element(key.begin(), key.begin() + std::min(n_ignored, F) - 1, key.end());
+            for (int i = 0; i < std::min(n_ignored, F); ++i) mask[(size_t)r * F + key[i].second] = 1;
+        }
+        m.ignored_all.alloc(mask.size());
+        TGBM_CUDA(cudaMemcpyAsync(m.ignored_all.p, mask.data(), mask.size(), cudaMemcpyHostToDevice, m.stream));
+        TGBM_CUDA(cudaStreamSynchronize(m.stream));
+    }
     m.qinfo_log.alloc(std::max(p.n_trees, 1) + 1);
     m.nodes.alloc(m.n_nodes);
     m.model.alloc((size_t)std::max(p.n_trees, 1) * K * m.n_nodes);
@@ -472,6 +496,7 @@ void Booster::init(const DataSet &ds) {
     m.hist_built.alloc(std::max<size_t>(1, (size_t)1 << std::max(0, depth - 2)) * B1 * 2);
     const int max_pairs = std::max(1, 1 << std::max(0, depth - 2));
     if (m.f32) {
+        for (int f = 0; f < std::min(m.F, 256); ++f) m.f32_cuts.v[f] = m.h_cut_ptr[f];
         m.hist_spread.alloc((size_t)32 * B1);
         m.sum_partial.alloc((size_t)SUM_BLOCKS * K * 2);
         const QuantInfo one{1.0, 1.0, 1.0, 1.0};
@@ -495,7 +520,7 @@ void Booster::init(const DataSet &ds) {
     m.part_base.alloc((size_t)1 << depth);
     m.part_status.alloc(m.max_tiles);
     m.part_status.zero(m.stream);
-    m.part_one = getenv("TGBM_PART_3PASS") == nullptr;
+    m.part_one = getenv("TGBM_PART_ONE") != nullptr;
     m.ctl.alloc(1);
     m.ctl.zero(m.stream);
     m.metric_partial.alloc(1024); m.metric_sum.alloc(1);
@@ -528,7 +553,7 @@ void BoosterImpl::gradient(int round) {
     const bool pointwise = objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC;
     const int logistic = objective == REG_LINEAR ? 0 : 1;
     // the pass that applied the previous tree has already found this round's gradient maxima
-    const bool have_max = pointwise && grad_max_ready && round >= 0 && !f32;
+    const bool have_max = pointwise && grad_max_ready && round >= 0 && !f32 && !p.bagging;
     grad_max_ready = false;
     root_sum.zero(stream);
     if (!have_max) {
@@ -545,6 +570,14 @@ void BoosterImpl::gradient(int round) {
             }
             ++launches;
         }
+    }
+    if (p.bagging && round >= 0 && N) {  // not for the base score (include/thundergbm/booster.h:69-73 comes before any sampling)
+        bag_count.zero(stream);
+        const unsigned long long m_total = (unsigned long long)std::max(p.num_class, 1) * (unsigned long long)N_global;
+        k_bag_draw<<<num_sms * 8, 256, 0, stream>>>(m_total, p.sample_seed, rstate.p, N_global, row_offset, N, K, bag_count.p);
+        maxbits.zero(stream);
+        k_bag_scale<<<std::max(1, std::min(ceil_div((long long)N * K, 256), num_sms * 8)), 256, 0, stream>>>(gh.p, bag_count.p, (size_t)N * K, maxbits.p);
+        launches += 2;
     }
     if (f32) {  // float gradients as they are; root sums in fp64, block partials combined in a fixed order
         k_sum_gh<<<dim3(SUM_BLOCKS, K), 256, 0, stream>>>(gh.p, N, sum_partial.p);
@@ -632,9 +665,11 @@ void BoosterImpl::build_tree(int round, int k) {
                     k_hist_sparse_f32<true><<<f32_ctas, F32_THREADS, 0, stream>>>(sp_row_ptr.p, sp_bin.p, idx_in, ghf, hist_work.p, hist_tile_base.p,
                                                                                   ctl.p, built_f, B, bs);
             } else if (level == 0)
-                k_hist_f32<false><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, nullptr, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs);
+                k_hist_f32<false><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, nullptr, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs,
+                                                                                 f32_cuts, F <= 256);
             else
-                k_hist_f32<true><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, idx_in, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs);
+                k_hist_f32<true><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, idx_in, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs,
+                                                                                f32_cuts, F <= 256);
         } else if (sparse) {
             const int sp_ctas = num_sms;
             const size_t sp_smem = (size_t)std::min(B, SPARSE_SMEM_BINS) * 16;
@@ -662,23 +697,24 @@ void BoosterImpl::build_tree(int round, int k) {
             const float *bf = reinterpret_cast<const float *>(built_f);
             if (sparse) {
                 k_eval_chunk<float><<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
-                                                                              bf, parent_f, full_f, qinfo.p, p.min_child_weight, p.lambda, recs.p, bs);
+                                                                              bf, parent_f, full_f, qinfo.p, p.min_child_weight, p.lambda, recs.p, bs, ignored_all.p, rstate.p, F);
                 k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
             } else {
                 k_eval<float><<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, bf, parent_f, full_f, qinfo.p,
-                                                                 p.min_child_weight, p.lambda, recs.p, cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, bs);
+                                                                 p.min_child_weight, p.lambda, recs.p, cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, bs,
+                                                                 ignored_all.p, rstate.p);
             }
         } else {
         const long long *parent_hist = level == 0 ? nullptr : hist_full.p + full_offset(level - 1);
         if (sparse) {
             k_eval_chunk<long long><<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
                                                                    built, parent_hist, hist_full.p + full_offset(level), qinfo.p,
-                                                                   p.min_child_weight, p.lambda, recs.p, 1);
+                                                                   p.min_child_weight, p.lambda, recs.p, 1, ignored_all.p, rstate.p, F);
             k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
         } else {
             k_eval<long long><<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built, parent_hist,
                                                       hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p,
-                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, 1);
+                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, 1, ignored_all.p, rstate.p);
         }
         }
         // -- move the rows (not after the last level: the finished tree is applied by walking it, see k_predict_walk)

@@ -211,6 +211,7 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
     p.objective = cp->objective ? cp->objective : "reg:linear";
     p.quant_bits = cp->quant_bits; p.keep_nid = cp->keep_nid; p.verbose = cp->verbose; p.rank_seed = cp->rank_seed;
     p.hist_mode = cp->hist_mode;
+    p.bagging = cp->bagging != 0; p.column_sampling_rate = cp->column_sampling_rate; p.sample_seed = cp->sample_seed;
     p.tree_method = "hist";
     return p;
 }
@@ -397,6 +398,7 @@ void tgbm_default_param(TgbmParam *p) {
     p->min_child_weight = d.min_child_weight; p->lambda = d.lambda; p->gamma = d.gamma; p->learning_rate = d.learning_rate;
     p->objective = "reg:linear"; p->quant_bits = d.quant_bits; p->keep_nid = 0; p->verbose = 0; p->profile = 0; p->rank_seed = 0;
     p->hist_mode = tgbm::default_hist_mode();
+    p->bagging = 0; p->column_sampling_rate = 1.f; p->sample_seed = 0;
 }
 
 int tgbm_comm_unique_id(unsigned char id[128]) { return guard([&] { tgbm::comm_get_unique_id(id); }); }

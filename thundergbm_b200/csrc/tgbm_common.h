@@ -83,6 +83,7 @@ struct GBMParam {
     // mode: bit-identical from run to run and for any number of GPUs.
     int hist_mode = 0;
     int quant_bits = 18;        // exact mode: value bits of the fixed-point gradient grid
+    unsigned sample_seed = 0;   // bagging and column sampling (the reference draws from std::rand())
     unsigned rank_seed = 0;     // LambdaRank partner sampling
     int keep_nid = 0;           // tests: keep ins2node_id of every tree
 };

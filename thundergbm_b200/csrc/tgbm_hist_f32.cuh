@@ -26,6 +26,10 @@ __device__ __forceinline__ void red_add_gh(float2 *cell, float g, float h) {
 }
 
 constexpr int F32_THREADS = 512;
+// First global bin of up to 256 features, passed to the dense kernel BY VALUE: kernel parameters live in the constant
+// bank, so the unrolled feature loop reads them without touching the load/store pipe the reductions already saturate
+// (with the offsets in shared memory the top stall was the memory-instruction queue).
+struct CutOffsets { int v[256]; };
 
 // Dense layout.  grid = (CTAs, feature groups of 32); a CTA takes half a 1024-record tile of the level's tile
 // sequence at a time, a thread one record: its 32 bin bytes, its gradient pair, one reduction per present feature.
@@ -33,11 +37,14 @@ template <bool GATHER>
 static __global__ void __launch_bounds__(F32_THREADS)
 k_hist_f32(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__restrict__ rec_idx,
            const float2 *__restrict__ rec_gh, const int4 *__restrict__ seq, const TreeCtl *__restrict__ ctl,
-           const int *__restrict__ cut_ptr, float2 *__restrict__ slab, int B, int cell_stride) {
+           const int *__restrict__ cut_ptr, float2 *__restrict__ slab, int B, int cell_stride,
+           const __grid_constant__ CutOffsets cuts, int cuts_in_param) {
     __shared__ int s_cut[32];
     const int f0 = blockIdx.y * 32, nf = min(32, F - f0);
-    if (threadIdx.x < 32) s_cut[threadIdx.x] = threadIdx.x < nf ? cut_ptr[f0 + threadIdx.x] : 0;
-    __syncthreads();
+    if (!cuts_in_param) {  // more than 256 features: the offsets of the CTA's group through shared memory
+        if (threadIdx.x < 32) s_cut[threadIdx.x] = threadIdx.x < nf ? cut_ptr[f0 + threadIdx.x] : 0;
+        __syncthreads();
+    }
     constexpr int PER_TILE = HIST_THREADS / F32_THREADS;
     const int units = ctl->n_hist_tiles * PER_TILE;
     for (int u = blockIdx.x; u < units; u += gridDim.x) {
@@ -54,7 +61,10 @@ k_hist_f32(const unsigned char *__restrict__ bins, int Fpad, int F, const int *_
 #pragma unroll
         for (int f = 0; f < 32; ++f) {
             const uint32_t bin = (w[f >> 2] >> (8 * (f & 3))) & 0xffu;
-            if (f < nf && bin != MISSING_BIN) red_add_gh(dst + (size_t)(s_cut[f] + bin) * cell_stride, v.x, v.y);
+            if (f < nf && bin != MISSING_BIN) {
+                const int first_bin = cuts_in_param ? cuts.v[(f0 + f) & 255] : s_cut[f];
+                red_add_gh(dst + (size_t)(first_bin + bin) * cell_stride, v.x, v.y);
+            }
         }
     }
 }

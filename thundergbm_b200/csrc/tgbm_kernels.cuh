@@ -292,6 +292,36 @@ static __global__ void k_quantize(const float2 *__restrict__ gh, int n, const un
     }
 }
 
+
+// ------------------------------------------------------------------ row and column sampling
+// RowSampler::do_bagging (src/thundergbm/row_sampler.cu:9-35): M = size of the gradient array (num_class x rows) draws
+// of a uniform index into that array, every entry's (g,h) multiplied by the number of times it was drawn.  The
+// reference seeds thrust's generator from std::rand(); here draw j of round r is a counter-based hash, so that the
+// CPU restatement and any number of ranks draw the same sample.  Every rank makes all the draws and keeps those that
+// land in its own rows.  entry = class * n_global + global row.
+static __global__ void k_bag_draw(unsigned long long m_total, uint32_t seed, const RoundState *__restrict__ rs, long long n_global,
+                                  long long row_offset, int n_local, int K, int *__restrict__ count) {
+    const uint32_t round = (uint32_t)rs->round;
+    for (unsigned long long j = blockIdx.x * (unsigned long long)blockDim.x + threadIdx.x; j < m_total; j += (unsigned long long)gridDim.x * blockDim.x) {
+        const uint32_t r = mix32(seed ^ 0xBA661D6Eu, round, (uint32_t)(j >> 32), (uint32_t)j);
+        const unsigned long long e = ((unsigned long long)r * m_total) >> 32;
+        const long long k = (long long)(e / (unsigned long long)n_global), row = (long long)(e % (unsigned long long)n_global) - row_offset;
+        if (k < K && row >= 0 && row < n_local) atomicAdd(count + k * n_local + row, 1);
+    }
+}
+// gh *= multiplicity; also the maxima of the scaled gradients for the fixed-point grid (every thread of the block calls track_max)
+static __global__ void k_bag_scale(float2 *__restrict__ gh, const int *__restrict__ count, size_t n, unsigned *__restrict__ maxbits) {
+    float mg = 0.f, mh = 0.f;
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float2 v = gh[i];
+        const float c = (float)count[i];
+        v.x = __fmul_rn(v.x, c); v.y = __fmul_rn(v.y, c);
+        gh[i] = v;
+        mg = fmaxf(mg, fabsf(v.x)); mh = fmaxf(mh, v.y);
+    }
+    track_max(mg, mh, maxbits);
+}
+
 // ------------------------------------------------------------------ tree set-up
 // Tree::init2 (src/thundergbm/tree.cu:8-39)
 // root_is_f64: fp32 mode, the root sums are doubles (k_sum_gh_final) instead of integers on the fixed-point grid
@@ -790,8 +820,11 @@ template <typename T>
 __device__ __forceinline__ void eval_feature(int level, int F, int B, const int *__restrict__ cut_ptr, const TreeNode *nodes,
                                              const int *__restrict__ built_right, const T *__restrict__ built,
                                              const T *__restrict__ parent, T *__restrict__ full,
-                                             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, int bs) {
+                                             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, int bs,
+                                             const unsigned char *__restrict__ ignored) {
     // bs: distance of two cells of `built` in cells (1 unless the fp32 histogram kernel spread them out)
+    // ignored: the round's column-sampling mask (Shard::column_sampling, src/thundergbm/builder/shard.cu:8-23; the
+    // masked features take no part in the split search, hist_tree_builder_single.cu:304,663), or null
     __shared__ T sg[2][256], sh[2][256];
     const int f = blockIdx.x, j = blockIdx.y;
     const int b0 = cut_ptr[f], nb = cut_ptr[f + 1] - b0;
@@ -801,7 +834,7 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
     const int off = (1 << level) - 1;
     SplitRec none = {0.f, -1, 0.f, 0.f, 0.f, 0.f};
     const int br = built_right[j];
-    if (nb == 0 || br < 0) {
+    if (nb == 0 || br < 0 || (ignored && ignored[f])) {
         if (lane == 0 && warp < n_children) recs[(size_t)node_local * F + f] = none;
         return;
     }
@@ -895,8 +928,10 @@ static __global__ void __launch_bounds__(64)
 k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0, const int *__restrict__ cut_ptr,
              const int *__restrict__ cut_fid, const TreeNode *__restrict__ nodes, const int *__restrict__ built_right,
              const T *__restrict__ built, const T *__restrict__ parent, T *__restrict__ full,
-             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs, int bs) {
+             const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs, int bs,
+             const unsigned char *__restrict__ ignored_all, const RoundState *__restrict__ rs, int F) {
     __shared__ T sg[2][256], sh[2][256];
+    const unsigned char *ignored = ignored_all ? ignored_all + (size_t)rs->round * F : nullptr;
     const int c = blockIdx.x, j = blockIdx.y;
     const int b0 = chunk_bin0[c], nb = chunk_bin0[c + 1] - b0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -982,7 +1017,7 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int b = lane * 8 + i;
-        if (b < nb) {
+        if (b < nb && !(ignored && ignored[cut_fid[b0 + b]])) {
             const int f = cut_fid[b0 + b];
             const int lastb = cut_ptr[f + 1] - 1 - b0;
             const float mg = __fsub_rn(pg, cell_f(sg[warp][lastb], inv_sg)), mh = __fsub_rn(ph, cell_f(sh[warp][lastb], inv_sh));
@@ -1111,8 +1146,10 @@ static __global__ void __launch_bounds__(64)
 k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes, const int *__restrict__ built_right,
        const T *__restrict__ built, const T *__restrict__ parent, T *__restrict__ full,
        const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, const float *__restrict__ cut_val,
-       float rt_eps, const int *__restrict__ cut_fid, int *__restrict__ ticket, int built_stride) {
-    eval_feature<T>(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs, built_stride);
+       float rt_eps, const int *__restrict__ cut_fid, int *__restrict__ ticket, int built_stride,
+       const unsigned char *__restrict__ ignored_all, const RoundState *__restrict__ rs) {
+    const unsigned char *ignored = ignored_all ? ignored_all + (size_t)rs->round * F : nullptr;
+    eval_feature<T>(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs, built_stride, ignored);
     __shared__ int last;
     __threadfence();  // the block's records are visible before its ticket is
     __syncthreads();

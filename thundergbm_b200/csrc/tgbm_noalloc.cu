@@ -18,7 +18,9 @@
 //    message in tgbm_last_error().  The ranking objectives are refused (their metric needs per-query sort buffers).
 //  * The first call on each device looks the scratch array's device address up (cudaGetSymbolAddress).  The name of
 //    the array in host code is only a handle, not an address the GPU can use, so that lookup is mandatory; its result
-//    is cached per device.  Make this first call outside any stream capture.
+//    is cached per device.  Make this first call outside any stream capture.  The cache does not survive
+//    cudaDeviceReset (or any other re-creation of the device's primary context): a process that resets a device
+//    must not call this function on it afterwards.
 //  * All calls on a device share the one scratch array.  Two calls whose kernels overlap on the GPU (different
 //    streams without an ordering between them) race on it; calls on the same stream are ordered and safe.  Nothing in
 //    the array has to start at zero: every slot that is read is written earlier in the same call.

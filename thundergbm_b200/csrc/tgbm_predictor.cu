@@ -144,37 +144,55 @@ template <bool DENSE_PATH, int RPT>
 __global__ void __launch_bounds__(PT_THREADS)
 k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F,
                 const HNode *__restrict__ model, int n_rounds, int K, int n_nodes, int depth, int chunk_trees, float lr,
-                float base_score, float *__restrict__ out) {
+                float base_score, float *__restrict__ out, double *__restrict__ partial) {
+    // Loop order: class, chunk of trees (staged once per CTA), the CTA's row tiles.  With more than one chunk the running
+    // sums of a row wait in `partial` (double [K][n_rows]; the CSR path keeps its float there) between the chunks, so that
+    // every row still adds its trees in ascending round order.
     extern __shared__ __align__(16) unsigned char pt_sm[];
     constexpr int ROWS = PT_THREADS * RPT;
     float *dense = reinterpret_cast<float *>(pt_sm);                                   // [F][ROWS]
-    HNode *trees = reinterpret_cast<HNode *>(pt_sm + sizeof(float) * (size_t)F * ROWS);  // [chunk_trees][n_nodes]
+    int *s_rp = reinterpret_cast<int *>(pt_sm + sizeof(float) * (size_t)F * ROWS);       // [ROWS + 1] row pointers of the tile
+    HNode *trees = reinterpret_cast<HNode *>(pt_sm + sizeof(float) * (size_t)F * ROWS + sizeof(int) * (ROWS + 8));  // [chunk_trees][n_nodes]
     const float absent = DENSE_PATH ? INFINITY : __uint_as_float(PRED_ABSENT);
     const int n_tiles = (n_rows + ROWS - 1) / ROWS;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        __syncthreads();  // the previous tile's walks are over
-        for (int i = threadIdx.x; i < F * ROWS; i += PT_THREADS) dense[i] = absent;
-        __syncthreads();
-        const int row0 = tile * ROWS;
-#pragma unroll
-        for (int j = 0; j < RPT; ++j) {
-            const int q = j * PT_THREADS + threadIdx.x, i = row0 + q;
-            if (i < n_rows)
-                for (int e = row_ptr[i]; e < row_ptr[i + 1]; ++e) {
+    for (int t = 0; t < K; ++t) {
+        for (int r0 = 0; r0 < n_rounds; r0 += chunk_trees) {
+            const int nc = min(chunk_trees, n_rounds - r0);
+            const bool first = r0 == 0, last = r0 + nc >= n_rounds;
+            __syncthreads();  // the previous chunk's walks are over
+            for (int i = threadIdx.x; i < nc * n_nodes; i += PT_THREADS)
+                trees[i] = model[((size_t)(r0 + i / n_nodes) * K + t) * n_nodes + i % n_nodes];
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                __syncthreads();  // the previous tile's walks are over (and the trees are in place)
+                const int row0 = tile * ROWS;
+                for (int i = threadIdx.x; i < F * ROWS; i += PT_THREADS) dense[i] = absent;
+                for (int i = threadIdx.x; i <= ROWS; i += PT_THREADS) s_rp[i] = row_ptr[min(row0 + i, n_rows)];
+                __syncthreads();
+                // The tile's stored values are one contiguous piece of the CSR arrays: the threads read it side by side
+                // (coalesced, all loads independent) and find the row of every value by binary search in the tile's row
+                // pointers.  One thread per row walking its own values would be a chain of dependent global loads.
+                const int e0 = s_rp[0], e1 = s_rp[ROWS];
+                for (int e = e0 + threadIdx.x; e < e1; e += PT_THREADS) {
                     const int c = col[e];
-                    if (c >= 0 && c < F) dense[c * ROWS + q] = val[e];
+                    const float v = val[e];
+                    int lo = 0, hi = ROWS - 1;  // last q with s_rp[q] <= e
+                    while (lo < hi) {
+                        const int mid = (lo + hi + 1) >> 1;
+                        if (s_rp[mid] <= e) lo = mid; else hi = mid - 1;
+                    }
+                    if (c >= 0 && c < F) dense[c * ROWS + lo] = v;
                 }
-        }
-        for (int t = 0; t < K; ++t) {
-            double dsum[RPT];
-            float fsum[RPT];
+                double dsum[RPT];
+                float fsum[RPT];
 #pragma unroll
-            for (int j = 0; j < RPT; ++j) { dsum[j] = base_score; fsum[j] = base_score; }
-            for (int r0 = 0; r0 < n_rounds; r0 += chunk_trees) {
-                const int nc = min(chunk_trees, n_rounds - r0);
-                __syncthreads();  // the previous chunk is no longer read (and the rows are in place)
-                for (int i = threadIdx.x; i < nc * n_nodes; i += PT_THREADS)
-                    trees[i] = model[((size_t)(r0 + i / n_nodes) * K + t) * n_nodes + i % n_nodes];
+                for (int j = 0; j < RPT; ++j) {
+                    const int i = row0 + j * PT_THREADS + threadIdx.x;
+                    dsum[j] = base_score; fsum[j] = base_score;
+                    if (i < n_rows && !first) {
+                        const double p = partial[(size_t)t * n_rows + i];
+                        dsum[j] = p; fsum[j] = (float)p;  // a float survives the round trip through a double unchanged
+                    }
+                }
                 __syncthreads();
                 for (int c = 0; c < nc; ++c) {
                     const HNode *nd = trees + (size_t)c * n_nodes;
@@ -201,11 +219,13 @@ k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, co
                         else fsum[j] = __fmaf_rn(lr, w, fsum[j]);
                     }
                 }
-            }
 #pragma unroll
-            for (int j = 0; j < RPT; ++j) {
-                const int i = row0 + j * PT_THREADS + threadIdx.x;
-                if (i < n_rows) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
+                for (int j = 0; j < RPT; ++j) {
+                    const int i = row0 + j * PT_THREADS + threadIdx.x;
+                    if (i >= n_rows) continue;
+                    if (last) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
+                    else partial[(size_t)t * n_rows + i] = DENSE_PATH ? dsum[j] : (double)fsum[j];
+                }
             }
         }
     }
@@ -213,21 +233,23 @@ k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, co
 
 template <bool DENSE_PATH>
 static bool launch_predict_tiles(const int *rp, const int *col, const float *val, int N, int F, const HNode *model, int n_rounds, int K,
-                                 int n_nodes, int depth, float lr, float base_score, float *out, int num_sms, cudaStream_t st) {
+                                 int n_nodes, int depth, float lr, float base_score, float *out, int num_sms, cudaStream_t st,
+                                 DevBuf<double> &partial) {
     const size_t budget = 200 * 1024, tree_bytes = sizeof(HNode) * (size_t)n_nodes;
-    for (int rpt : {4, 2, 1}) {
-        const size_t rows_bytes = sizeof(float) * (size_t)F * PT_THREADS * rpt;
+    // fewer rows per tile leave room for more trees per chunk, and every chunk is one more pass over the rows
+    for (int rpt : {2, 1}) {
+        const size_t rows_bytes = sizeof(float) * (size_t)F * PT_THREADS * rpt + sizeof(int) * (PT_THREADS * rpt + 8);
         if (rows_bytes + std::min<size_t>(8, n_rounds) * tree_bytes > budget) continue;  // at least 8 trees (or all) per chunk
-        const int chunk = (int)std::min<size_t>(std::min<size_t>(64, n_rounds), (budget - rows_bytes) / tree_bytes);
+        const int chunk = (int)std::min<size_t>((size_t)n_rounds, (budget - rows_bytes) / tree_bytes);
         const size_t smem = rows_bytes + chunk * tree_bytes;
+        if (chunk < n_rounds && partial.n < (size_t)N * K) partial.alloc((size_t)N * K);  // running sums between the chunks
         const int tiles = (N + PT_THREADS * rpt - 1) / (PT_THREADS * rpt);
         const int grid = std::max(1, std::min(tiles, num_sms));
         auto go = [&](auto kern) {
             TGBM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            kern<<<grid, PT_THREADS, smem, st>>>(rp, col, val, N, F, model, n_rounds, K, n_nodes, depth, chunk, lr, base_score, out);
+            kern<<<grid, PT_THREADS, smem, st>>>(rp, col, val, N, F, model, n_rounds, K, n_nodes, depth, chunk, lr, base_score, out, partial.p);
         };
-        if (rpt == 4) go(k_predict_tiles<DENSE_PATH, 4>);
-        else if (rpt == 2) go(k_predict_tiles<DENSE_PATH, 2>);
+        if (rpt == 2) go(k_predict_tiles<DENSE_PATH, 2>);
         else go(k_predict_tiles<DENSE_PATH, 1>);
         return true;
     }
@@ -308,11 +330,12 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     // kernel serves either whenever a tile of rows and a chunk of trees fit the shared memory of an SM.
     const bool dense_path = smem <= 48 * 1024;
     bool done = false;
+    DevBuf<double> d_partial;
     if (heap && getenv("TGBM_PREDICT_SIMPLE") == nullptr)
         done = dense_path ? launch_predict_tiles<true>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
-                                                       base_score, d_out.p, num_sms, st)
+                                                       base_score, d_out.p, num_sms, st, d_partial)
                           : launch_predict_tiles<false>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
-                                                        base_score, d_out.p, num_sms, st);
+                                                        base_score, d_out.p, num_sms, st, d_partial);
     if (done) {
     } else if (dense_path) {
         k_predict_dense<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds, K,
