@@ -133,12 +133,12 @@ k_predict_csr_staged(const int *__restrict__ row_ptr, const int *__restrict__ co
 //   * the trees of a chunk as 8-byte records in heap order (the node table IS a heap: children of i are 2i+1, 2i+2,
 //     checked on the host), so a step is one 8-byte read of the node and one 4-byte read of the row's feature;
 //   * the rows of a tile spread out as [feature][row] (bank = row: no conflicts whatever features the lanes ask for);
-//   * RPT rows per thread walk a tree level by level side by side -- a walk is a chain of dependent shared-memory
-//     reads, several independent chains per thread keep the pipeline busy.
+//   * 512 threads per CTA, RPT rows per thread walk a tree level by level side by side -- a walk is a chain of
+//     dependent shared-memory reads, many independent chains keep the pipeline busy.
 // Trees are visited in ascending round order for every row, so the sums are those of the one-thread-per-row kernels
 // bit for bit.  CTAs are persistent and loop over the row tiles.
 struct HNode { float v; int fid; };  // split value or leaf weight; feature id, bit 31 = leaf, bit 30 = default right
-constexpr int PT_THREADS = 256;
+constexpr int PT_THREADS = 512;
 
 template <bool DENSE_PATH, int RPT>
 __global__ void __launch_bounds__(PT_THREADS)
@@ -151,8 +151,7 @@ k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, co
     extern __shared__ __align__(16) unsigned char pt_sm[];
     constexpr int ROWS = PT_THREADS * RPT;
     float *dense = reinterpret_cast<float *>(pt_sm);                                   // [F][ROWS]
-    int *s_rp = reinterpret_cast<int *>(pt_sm + sizeof(float) * (size_t)F * ROWS);       // [ROWS + 1] row pointers of the tile
-    HNode *trees = reinterpret_cast<HNode *>(pt_sm + sizeof(float) * (size_t)F * ROWS + sizeof(int) * (ROWS + 8));  // [chunk_trees][n_nodes]
+    HNode *trees = reinterpret_cast<HNode *>(pt_sm + sizeof(float) * (size_t)F * ROWS);  // [chunk_trees][n_nodes]
     const float absent = DENSE_PATH ? INFINITY : __uint_as_float(PRED_ABSENT);
     const int n_tiles = (n_rows + ROWS - 1) / ROWS;
     for (int t = 0; t < K; ++t) {
@@ -166,21 +165,37 @@ k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, co
                 __syncthreads();  // the previous tile's walks are over (and the trees are in place)
                 const int row0 = tile * ROWS;
                 for (int i = threadIdx.x; i < F * ROWS; i += PT_THREADS) dense[i] = absent;
-                for (int i = threadIdx.x; i <= ROWS; i += PT_THREADS) s_rp[i] = row_ptr[min(row0 + i, n_rows)];
                 __syncthreads();
-                // The tile's stored values are one contiguous piece of the CSR arrays: the threads read it side by side
-                // (coalesced, all loads independent) and find the row of every value by binary search in the tile's row
-                // pointers.  One thread per row walking its own values would be a chain of dependent global loads.
-                const int e0 = s_rp[0], e1 = s_rp[ROWS];
-                for (int e = e0 + threadIdx.x; e < e1; e += PT_THREADS) {
-                    const int c = col[e];
-                    const float v = val[e];
-                    int lo = 0, hi = ROWS - 1;  // last q with s_rp[q] <= e
-                    while (lo < hi) {
-                        const int mid = (lo + hi + 1) >> 1;
-                        if (s_rp[mid] <= e) lo = mid; else hi = mid - 1;
+                // A thread spreads out its own rows: the slots it writes are its own column of `dense` (bank = row: no
+                // conflicts), neighbouring threads read neighbouring rows (whole cache lines get used), and the loads
+                // are issued in batches of eight so that the few warps of the CTA cover the memory latency.
+                constexpr int BATCH = 8;
+#pragma unroll
+                for (int j = 0; j < RPT; ++j) {
+                    const int q = j * PT_THREADS + threadIdx.x, i = row0 + q;
+                    if (i >= n_rows) continue;
+                    const int ea = row_ptr[i], ez = row_ptr[i + 1];
+                    for (int eb = ea; eb < ez; eb += BATCH) {
+                        int cc[BATCH];
+                        float vv[BATCH];
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u) {
+                            cc[u] = eb + u < ez ? col[eb + u] : -1;
+                            vv[u] = eb + u < ez ? val[eb + u] : 0.f;
+                        }
+#pragma unroll
+                        for (int u = 0; u < BATCH; ++u)
+                            if (cc[u] >= 0 && cc[u] < F) dense[cc[u] * ROWS + q] = vv[u];
                     }
-                    if (c >= 0 && c < F) dense[c * ROWS + lo] = v;
+                }
+                // the next tile's values on their way into L2 while this one is walked
+                if (tile + (int)gridDim.x < n_tiles) {
+                    const int nr0 = min(row0 + (int)gridDim.x * ROWS, n_rows), nr1 = min(nr0 + ROWS, n_rows);
+                    const int ne0 = row_ptr[nr0], ne1 = row_ptr[nr1];
+                    for (int e = ne0 + threadIdx.x * 32; e < ne1; e += PT_THREADS * 32) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(col + e));
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(val + e));
+                    }
                 }
                 double dsum[RPT];
                 float fsum[RPT];
@@ -234,15 +249,24 @@ k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, co
 template <bool DENSE_PATH>
 static bool launch_predict_tiles(const int *rp, const int *col, const float *val, int N, int F, const HNode *model, int n_rounds, int K,
                                  int n_nodes, int depth, float lr, float base_score, float *out, int num_sms, cudaStream_t st,
-                                 DevBuf<double> &partial) {
+                                 DevBuf<double> &partial, bool plan_only) {
     const size_t budget = 200 * 1024, tree_bytes = sizeof(HNode) * (size_t)n_nodes;
-    // fewer rows per tile leave room for more trees per chunk, and every chunk is one more pass over the rows
-    for (int rpt : {2, 1}) {
-        const size_t rows_bytes = sizeof(float) * (size_t)F * PT_THREADS * rpt + sizeof(int) * (PT_THREADS * rpt + 8);
+    // fewer rows per tile leave room for more trees per chunk, and every chunk is one more pass over the rows: take the
+    // tile size that needs fewer passes (two rows per thread when it is a tie)
+    auto passes = [&](int rpt) -> long {
+        const size_t rows_bytes = sizeof(float) * (size_t)F * PT_THREADS * rpt;
+        if (rows_bytes + std::min<size_t>(8, n_rounds) * tree_bytes > budget) return 1L << 40;
+        const long chunk = (long)std::min<size_t>((size_t)n_rounds, (budget - rows_bytes) / tree_bytes);
+        return (n_rounds + chunk - 1) / chunk;
+    };
+    const int order[2] = {passes(2) <= passes(1) ? 2 : 1, passes(2) <= passes(1) ? 1 : 2};
+    for (int rpt : order) {
+        const size_t rows_bytes = sizeof(float) * (size_t)F * PT_THREADS * rpt;
         if (rows_bytes + std::min<size_t>(8, n_rounds) * tree_bytes > budget) continue;  // at least 8 trees (or all) per chunk
         const int chunk = (int)std::min<size_t>((size_t)n_rounds, (budget - rows_bytes) / tree_bytes);
         const size_t smem = rows_bytes + chunk * tree_bytes;
         if (chunk < n_rounds && partial.n < (size_t)N * K) partial.alloc((size_t)N * K);  // running sums between the chunks
+        if (plan_only) return true;
         const int tiles = (N + PT_THREADS * rpt - 1) / (PT_THREADS * rpt);
         const int grid = std::max(1, std::min(tiles, num_sms));
         auto go = [&](auto kern) {
@@ -325,17 +349,21 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     int dev = 0, num_sms = 148;
     TGBM_CUDA(cudaGetDevice(&dev));
     TGBM_CUDA(cudaDeviceGetAttribute(&num_sms, cudaDevAttrMultiProcessorCount, dev));
-    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
     // The reference chooses its arithmetic by F * 128 * 4 <= 48 KB (predictor.cu:88); that choice is kept, the tiled
     // kernel serves either whenever a tile of rows and a chunk of trees fit the shared memory of an SM.
     const bool dense_path = smem <= 48 * 1024;
     bool done = false;
     DevBuf<double> d_partial;
-    if (heap && getenv("TGBM_PREDICT_SIMPLE") == nullptr)
-        done = dense_path ? launch_predict_tiles<true>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
-                                                       base_score, d_out.p, num_sms, st, d_partial)
+    const bool tiled = heap && getenv("TGBM_PREDICT_SIMPLE") == nullptr;
+    auto tiles = [&](bool plan_only) {
+        return dense_path ? launch_predict_tiles<true>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
+                                                       base_score, d_out.p, num_sms, st, d_partial, plan_only)
                           : launch_predict_tiles<false>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
-                                                        base_score, d_out.p, num_sms, st, d_partial);
+                                                        base_score, d_out.p, num_sms, st, d_partial, plan_only);
+    };
+    if (tiled) tiles(true);  // scratch for the running sums is allocated here, outside the timed kernel
+    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
+    if (tiled) done = tiles(false);
     if (done) {
     } else if (dense_path) {
         k_predict_dense<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds, K,
