@@ -172,7 +172,7 @@ def oracle_run(config, n_rows, n_trees: int, threads: int):
     return orc.train(d, n_trees=n_trees, hist_mode=1, n_threads=threads, **WORKLOADS[config][2])
 
 
-def reference_gpu_run(config, n_rows, n_trees: int):
+def reference_gpu_run(config, n_rows, n_trees: int, repeat: bool = True):
     """The reference itself (built by oracle/build_ref.sh into oracle/_ref/, GPU-only code) on the full workload on
     cuda:0 -- an extra figure beside the CPU arm: its own 'training time' (src/thundergbm/trainer.cu:42-50), the
     wall clock of TreeTrainer::train including its set-up, its final training metric and, for classification, the
@@ -195,19 +195,31 @@ def reference_gpu_run(config, n_rows, n_trees: int):
             env['LD_LIBRARY_PATH'] = os.path.join(ROOT, 'oracle', '_ref', 'lib') + ':' + env.get('LD_LIBRARY_PATH', '')
             cmd = [harness, path, tmp, 'objective=' + params['objective'], f"depth={params['depth']}", f'n_trees={n_trees}',
                    f"max_num_bin={params['max_num_bin']}", f"learning_rate={params['learning_rate']}", 'tree_method=hist', 'dump_bins=0']
-            out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1200)
-            if out.returncode != 0:
-                return {'unavailable': f'ref_harness exit {out.returncode}'}
-            raw = np.fromfile(os.path.join(tmp, 'raw_pred.f32'), np.float32)
-        t_train = float(re.search(r'training time = ([0-9.eE+-]+)', out.stdout).group(1))
-        t_wall = float(re.search(r'train_wall_s ([0-9.eE+-]+)', out.stdout).group(1))
-        vals = re.findall(r'\[(\d+)/\d+\] [^=]+ = ([0-9.eE+-]+)', out.stdout)
-        label = np.unique(d.y.astype(np.int32)).astype(np.float32)
-        ll = logloss_terms(params['objective'], raw, d.y, label)
-        return {'value': t_train * 100.0 / n_trees, 'unit': 's/100 rounds', 'rounds': n_trees,
-                'e2e_value': t_wall * 100.0 / n_trees, 'final_train_metric': float(vals[-1][1]) if vals else None,
-                'final_train_logloss': ll[0] / ll[1] if ll else None,
-                'kind': 'the reference built for sm_100a by oracle/build_ref.sh, same workload, 1 GPU'}
+            def one_run():
+                out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1200)
+                if out.returncode != 0:
+                    return None
+                raw = np.fromfile(os.path.join(tmp, 'raw_pred.f32'), np.float32)
+                t_train = float(re.search(r'training time = ([0-9.eE+-]+)', out.stdout).group(1))
+                t_wall = float(re.search(r'train_wall_s ([0-9.eE+-]+)', out.stdout).group(1))
+                vals = re.findall(r'\[(\d+)/\d+\] [^=]+ = ([0-9.eE+-]+)', out.stdout)
+                ll = logloss_terms(params['objective'], raw, d.y, label)
+                return t_train, t_wall, float(vals[-1][1]) if vals else None, ll[0] / ll[1] if ll else None
+            label = np.unique(d.y.astype(np.int32)).astype(np.float32)
+            runs = [one_run() for _ in range(2 if repeat else 1)]
+        if any(r is None for r in runs):
+            return {'unavailable': 'ref_harness failed'}
+        t_train, t_wall, metric, ll = runs[0]
+        res = {'value': t_train * 100.0 / n_trees, 'unit': 's/100 rounds', 'rounds': n_trees,
+               'e2e_value': t_wall * 100.0 / n_trees, 'final_train_metric': metric, 'final_train_logloss': ll,
+               'kind': 'the reference built for sm_100a by oracle/build_ref.sh, same workload, 1 GPU'}
+        if len(runs) > 1:  # how far two runs of the reference itself end up from each other (unordered float atomics)
+            res['second_run'] = {'value': runs[1][0] * 100.0 / n_trees, 'final_train_metric': runs[1][2], 'final_train_logloss': runs[1][3]}
+            if metric is not None and runs[1][2] is not None:
+                res['spread_metric'] = abs(metric - runs[1][2])
+            if ll is not None and runs[1][3] is not None:
+                res['spread_logloss'] = abs(ll - runs[1][3])
+        return res
     except Exception as e:  # noqa: BLE001 -- an extra figure must never break the arm
         return {'unavailable': f'{type(e).__name__}: {e}'[:200]}
 
@@ -237,7 +249,9 @@ def run_reference(args):
         'cpu_baseline': {'value': s_round * 100.0, 'unit': 's/100 trees', 'cores': cores, 'kind': 'port', 'sample': sample},
         'e2e': {'value': s_round * 100.0, 'unit': 's/100 trees', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
         'gpu_launches': 0,
-        'reference_gpu': reference_gpu_run(args.config, n_rows, k),
+        # warm-up + timed rounds, so that its final metric and logloss describe the same number of rounds as the
+        # `final_train_*` figures of the repo's own arm
+        'reference_gpu': reference_gpu_run(args.config, n_rows, w + k),
     }
     print(json.dumps(line), flush=True)
 
@@ -445,7 +459,7 @@ def main():
                                      'exact = integer sums on a fixed-point grid (deterministic)',
                    'rows_per_gpu': hi - lo, 'parallelism': f'rows sharded over {world} GPU(s), NCCL all-reduce of level histograms',
                    'l2': 'inputs larger than L2 (bin data %.0f MB per GPU)' % (max(data.nnz, (hi - lo) * info.fpad) / 1e6),
-                   'trees_per_round': int(info.trees_per_round), 'final_train_metric': head['final_metric'],
+                   'trees_per_round': int(info.trees_per_round), 'rounds_trained': w + k, 'final_train_metric': head['final_metric'],
                    'final_train_logloss': head['logloss'], 'init_s': head['t_init'], 'datagen_s': t_gen},
         'roofline': head['roofline'],
         'e2e': e2e, 'gpu_launches': head['launches'], 'clocks': clocks, 'predict': predict,

@@ -861,7 +861,10 @@ void tgo_predict_raw(int n_rows, const int *row_ptr, const int *col, const float
                 while (!nd[cur].is_leaf) {
                     const int f = nd[cur].split_feature_id;
                     const int *it = std::lower_bound(ci, ci + len, f);
-                    if (it != ci + len && *it == f) cur = vi[it - ci] < nd[cur].split_value ? nd[cur].lch_index : nd[cur].rch_index;
+                    // the dense path marks absent features with +inf and tests `fval < INFINITY` (predictor.cu:95-96, :121):
+                    // a stored +inf or NaN is taken for absent there; the CSR path compares whatever is stored
+                    const bool found = it != ci + len && *it == f && (!dense_path || vi[it - ci] < INFINITY);
+                    if (found) cur = vi[it - ci] < nd[cur].split_value ? nd[cur].lch_index : nd[cur].rch_index;
                     else cur = nd[cur].default_right ? nd[cur].rch_index : nd[cur].lch_index;
                 }
                 const float w = nd[cur].base_weight;

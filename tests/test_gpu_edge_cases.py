@@ -157,3 +157,37 @@ def test_full_size_properties(gpu):
     m = b.metrics()
     assert m[-1] < m[0] + 1e-6
     b.close()
+
+
+@pytest.mark.parametrize('n_features', [12, 40, 300])
+def test_predict_raw_special_values(gpu, orc, n_features):
+    """predict_raw on values that sit exactly on thresholds, on -0.0 / +0.0, on +-inf and NaN, on absent features and on
+    features the model never saw -- for the reference's dense arithmetic (F * 128 * 4 <= 48 KB: double sums, +inf means
+    absent) and its CSR arithmetic (float sums, fused multiply-add).  Bit-identical to the oracle."""
+    from thundergbm_b200.booster import Booster, predict_raw
+    from thundergbm_b200.synth import dense_to_csr
+    rng = np.random.default_rng(n_features)
+    n = 3000
+    x = rng.standard_normal((n, n_features)).astype(np.float32)
+    x[rng.random(x.shape) < 0.3] = 0.0                       # dropped by the CSR conversion: absent
+    y = (x[:, 0] + 0.5 * x[:, 1] * x[:, 2] + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    d = dense_to_csr(x, y)
+    b = Booster(d, objective='reg:linear', depth=5, n_trees=12, learning_rate=0.3, max_num_bin=32)
+    b.boost(12)
+    trees, base = b.trees(), b.info.base_score
+    b.close()
+    # test rows: every threshold of the model, its float neighbours, and the special values, in random columns
+    thr = trees['split_value'][(trees['is_valid'] != 0) & (trees['is_leaf'] == 0)]
+    pool = np.concatenate([thr, np.nextafter(thr, np.float32(np.inf)), np.nextafter(thr, np.float32(-np.inf)),
+                           np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e30, -1e30], np.float32)]).astype(np.float32)
+    m = 5000
+    xt = pool[rng.integers(0, pool.size, (m, n_features + 3))]   # three more columns than the model was trained on
+    keep = rng.random(xt.shape) < 0.7
+    rows, cols = np.nonzero(keep)
+    from thundergbm_b200.synth import CsrData
+    rp = np.zeros(m + 1, np.int32)
+    np.cumsum(keep.sum(1), out=rp[1:])
+    dt = CsrData(m, n_features + 3, rp, cols.astype(np.int32), xt[rows, cols].astype(np.float32), np.zeros(m, np.float32))
+    got = predict_raw(dt, trees, 0.3, base)
+    want = orc.predict_raw(dt, trees, 0.3, base, n_features=n_features + 3)
+    assert np.array_equal(got, want)

@@ -280,6 +280,140 @@ static bool launch_predict_tiles(const int *rp, const int *col, const float *val
     return false;
 }
 
+
+// ---- traversal on ranks ------------------------------------------------------------------------------------------
+// A model compares feature values with a few hundred distinct thresholds per feature at most (it was trained on at
+// most 255 bins).  With the thresholds of feature f sorted, s_0 < s_1 < ..., and r(v) = #{i : s_i <= v}, the test the
+// reference makes at a node with threshold s_t,  v < s_t  (predictor.cu:89-91, :158-160), is exactly  r(v) <= t.  So
+// every row is converted ONCE to one byte per feature (its rank, 255 = absent) and all trees are walked on bytes:
+// a row of up to 32 features sits in 8 registers, the whole shared memory holds trees (8-byte records in heap order),
+// and four rows per thread walk side by side.  Same comparisons, same order of the sums: the scores are those of the
+// float kernels bit for bit.  Used when no feature has more than 254 thresholds and every tree is a heap.
+struct RNode { int flags; float weight; };  // threshold rank (bits 0-7) | default right (8) | leaf (9) | feature << 16
+constexpr int RK_ROWS = 512;     // rows of a block of k_rank_rows
+constexpr int RK_THREADS = 256;
+
+// CSR values -> ranks.  A block owns RK_ROWS consecutive rows = one contiguous piece of the CSR arrays; its warps read
+// that piece 32 values at a time (coalesced) and find the row of every value in the block's row pointers: a 32-ary
+// search for the warp's first value, then a walk over the few row boundaries inside the warp's 32 values.
+template <bool DENSE_PATH>
+__global__ void __launch_bounds__(RK_THREADS)
+k_rank_rows(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F, int Fpad,
+            const int *__restrict__ thr_ptr, const float *__restrict__ thr, unsigned char *__restrict__ bins) {
+    __shared__ int s_rp[RK_ROWS + 1];
+    const int row0 = blockIdx.x * RK_ROWS;
+    for (int i = threadIdx.x; i <= RK_ROWS; i += RK_THREADS) s_rp[i] = row_ptr[min(row0 + i, n_rows)];
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e0 = s_rp[0], e1 = s_rp[RK_ROWS];
+    for (int base = e0 + warp * 32; base < e1; base += RK_THREADS) {
+        const int e = base + lane;
+        int c = -1;
+        float v = 0.f;
+        if (e < e1) { c = col[e]; v = val[e]; }
+        // row of the warp's first value: the last q with s_rp[q] <= base (RK_ROWS = 32 * 16)
+        const int blk = __popc(__ballot_sync(0xffffffffu, s_rp[16 * lane] <= base)) - 1;
+        const int q0 = 16 * blk + __popc(__ballot_sync(0xffffffffu, lane < 16 && s_rp[16 * blk + lane] <= base)) - 1;
+        int q = q0;
+        for (int k = 1; q0 + k <= RK_ROWS; ++k) {  // row boundaries inside the warp's values
+            const int nb = s_rp[q0 + k];
+            if (nb > base + 31) break;
+            if (nb <= e) q = q0 + k;
+        }
+        if (c >= 0 && c < F) {
+            int lo = thr_ptr[c];
+            const int first = lo;
+            int hi = thr_ptr[c + 1];
+            const int n_thr = hi - first;
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (thr[mid] <= v) lo = mid + 1; else hi = mid;
+            }
+            int r = lo - first;
+            if (DENSE_PATH) { if (!(v < INFINITY)) r = 255; }  // the dense path marks absent features with +inf (predictor.cu:100)
+            else if (v != v) r = n_thr;                         // no threshold is above a NaN: always right
+            bins[(size_t)(row0 + q) * Fpad + c] = (unsigned char)r;
+        }
+    }
+}
+
+template <bool DENSE_PATH, bool REG_ROWS>
+__global__ void __launch_bounds__(256)
+k_predict_ranks(const unsigned char *__restrict__ bins, int Fpad, int F, int n_rows, const RNode *__restrict__ model, int n_rounds, int K,
+                int n_nodes, int depth, int chunk_trees, float lr, float base_score, float *__restrict__ out, double *__restrict__ partial) {
+    extern __shared__ __align__(16) unsigned char rk_sm[];
+    RNode *trees = reinterpret_cast<RNode *>(rk_sm);  // [chunk_trees][n_nodes]
+    constexpr int RPT = 4, ROWS = 256 * RPT;
+    const int n_tiles = (n_rows + ROWS - 1) / ROWS;
+    for (int t = 0; t < K; ++t) {
+        for (int r0 = 0; r0 < n_rounds; r0 += chunk_trees) {
+            const int nc = min(chunk_trees, n_rounds - r0);
+            const bool first = r0 == 0, last = r0 + nc >= n_rounds;
+            __syncthreads();  // the previous chunk's walks are over
+            for (int i = threadIdx.x; i < nc * n_nodes; i += 256)
+                trees[i] = model[((size_t)(r0 + i / n_nodes) * K + t) * n_nodes + i % n_nodes];
+            __syncthreads();
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                uint32_t w[RPT][8];
+                const unsigned char *rowp[RPT];
+                double dsum[RPT];
+                float fsum[RPT];
+#pragma unroll
+                for (int j = 0; j < RPT; ++j) {
+                    const int i = min(tile * ROWS + j * 256 + (int)threadIdx.x, n_rows - 1);
+                    rowp[j] = bins + (size_t)i * Fpad;
+                    if (REG_ROWS) {
+                        const uint4 a = reinterpret_cast<const uint4 *>(rowp[j])[0], b = reinterpret_cast<const uint4 *>(rowp[j])[1];
+                        w[j][0] = a.x; w[j][1] = a.y; w[j][2] = a.z; w[j][3] = a.w; w[j][4] = b.x; w[j][5] = b.y; w[j][6] = b.z; w[j][7] = b.w;
+                    }
+                    dsum[j] = base_score; fsum[j] = base_score;
+                    if (!first) { const double p = partial[(size_t)t * n_rows + i]; dsum[j] = p; fsum[j] = (float)p; }
+                }
+                for (int c = 0; c < nc; ++c) {
+                    const RNode *nd = trees + (size_t)c * n_nodes;
+                    int cur[RPT];
+#pragma unroll
+                    for (int j = 0; j < RPT; ++j) cur[j] = 0;
+                    for (int lvl = 0; lvl < depth; ++lvl) {
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) {
+                            const int fl = nd[cur[j]].flags;
+                            if (!(fl & 0x200)) {
+                                const unsigned f = (unsigned)fl >> 16;
+                                int b = MISSING_BIN;
+                                if (REG_ROWS) {
+                                    const uint32_t a0 = (f & 16) ? w[j][4] : w[j][0], a1 = (f & 16) ? w[j][5] : w[j][1],
+                                                   a2 = (f & 16) ? w[j][6] : w[j][2], a3 = (f & 16) ? w[j][7] : w[j][3];
+                                    const uint32_t b0 = (f & 8) ? a2 : a0, b1 = (f & 8) ? a3 : a1;
+                                    b = (((f & 4) ? b1 : b0) >> (8 * (f & 3))) & 0xffu;
+                                    if ((int)f >= F) b = MISSING_BIN;  // a feature the data does not have
+                                } else if ((int)f < F) {
+                                    b = rowp[j][f];
+                                }
+                                const bool left = (b == MISSING_BIN) ? !(fl & 0x100) : (b <= (fl & 0xff));
+                                cur[j] = 2 * cur[j] + (left ? 1 : 2);
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < RPT; ++j) {
+                        const float wt = nd[cur[j]].weight;
+                        if (DENSE_PATH) dsum[j] += (double)__fmul_rn(lr, wt);
+                        else fsum[j] = __fmaf_rn(lr, wt, fsum[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < RPT; ++j) {
+                    const int i = tile * ROWS + j * 256 + (int)threadIdx.x;
+                    if (i >= n_rows) continue;
+                    if (last) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
+                    else partial[(size_t)t * n_rows + i] = DENSE_PATH ? dsum[j] : (double)fsum[j];
+                }
+            }
+        }
+    }
+}
+
 void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model, float learning_rate, float base_score,
                  std::vector<float> &out, float *kernel_ms) {
     const int N = ds.n_rows;
@@ -354,7 +488,59 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     const bool dense_path = smem <= 48 * 1024;
     bool done = false;
     DevBuf<double> d_partial;
-    const bool tiled = heap && getenv("TGBM_PREDICT_SIMPLE") == nullptr;
+    const bool heap_ok = heap && getenv("TGBM_PREDICT_SIMPLE") == nullptr;
+    // ---- ranks: thresholds per feature, nodes with threshold ranks
+    std::vector<int> thr_ptr;
+    std::vector<float> thr;
+    std::vector<RNode> rflat;
+    bool ranks = heap_ok && getenv("TGBM_PREDICT_FLOAT") == nullptr && sizeof(RNode) * (size_t)n_nodes * std::min(8, n_rounds) <= 200 * 1024 && F < 65536;
+    if (ranks) {
+        std::vector<std::vector<float>> per(F);
+        for (size_t i = 0; i < flat.size(); ++i) {
+            const PNode &nd = flat[i];
+            if (nd.fid & 0x80000000) continue;
+            const int f = nd.fid & 0x3fffffff;
+            if (f < F) per[f].push_back(nd.v == 0.f ? 0.f : nd.v);  // -0 and +0 compare equal: one threshold
+            if (nd.v != nd.v) ranks = false;                        // a NaN threshold has no rank
+        }
+        thr_ptr.assign(F + 1, 0);
+        for (int f = 0; f < F && ranks; ++f) {
+            std::sort(per[f].begin(), per[f].end());
+            per[f].erase(std::unique(per[f].begin(), per[f].end()), per[f].end());
+            if (per[f].size() > 254) ranks = false;
+            thr_ptr[f + 1] = thr_ptr[f] + (int)per[f].size();
+        }
+        if (ranks) {
+            thr.reserve(thr_ptr[F] + 1);
+            for (int f = 0; f < F; ++f) thr.insert(thr.end(), per[f].begin(), per[f].end());
+            rflat.resize(flat.size());
+            for (size_t i = 0; i < flat.size(); ++i) {
+                const PNode &nd = flat[i];
+                RNode &o = rflat[i];
+                if (nd.fid & 0x80000000) { o.flags = 0x200; o.weight = nd.v; continue; }
+                const int f = nd.fid & 0x3fffffff;
+                int t = 0;
+                if (f < F) t = (int)(std::lower_bound(per[f].begin(), per[f].end(), nd.v == 0.f ? 0.f : nd.v) - per[f].begin());
+                o.flags = t | ((nd.fid & 0x40000000) ? 0x100 : 0) | (int)((unsigned)std::min(f, 65535) << 16);
+                o.weight = 0.f;
+            }
+        }
+    }
+    DevBuf<int> d_thr_ptr;
+    DevBuf<float> d_thr;
+    DevBuf<RNode> d_rmodel;
+    DevBuf<unsigned char> d_bins;
+    const int Fpad = (F + 31) / 32 * 32;
+    int rk_chunk = 0;
+    if (ranks) {
+        d_thr_ptr.alloc(F + 1); d_thr.alloc(std::max<size_t>(thr.size(), 1)); d_rmodel.alloc(rflat.size()); d_bins.alloc((size_t)N * Fpad);
+        TGBM_CUDA(cudaMemcpyAsync(d_thr_ptr.p, thr_ptr.data(), sizeof(int) * (F + 1), cudaMemcpyHostToDevice, st));
+        if (!thr.empty()) TGBM_CUDA(cudaMemcpyAsync(d_thr.p, thr.data(), sizeof(float) * thr.size(), cudaMemcpyHostToDevice, st));
+        TGBM_CUDA(cudaMemcpyAsync(d_rmodel.p, rflat.data(), sizeof(RNode) * rflat.size(), cudaMemcpyHostToDevice, st));
+        rk_chunk = (int)std::min<size_t>((size_t)n_rounds, (size_t)(216 * 1024) / (sizeof(RNode) * (size_t)n_nodes));
+        if (rk_chunk < n_rounds) d_partial.alloc((size_t)N * K);
+    }
+    const bool tiled = heap_ok && !ranks;
     auto tiles = [&](bool plan_only) {
         return dense_path ? launch_predict_tiles<true>(d_rp.p, d_col.p, d_val.p, N, F, d_hmodel.p, n_rounds, K, n_nodes, depth, learning_rate,
                                                        base_score, d_out.p, num_sms, st, d_partial, plan_only)
@@ -364,6 +550,22 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     if (tiled) tiles(true);  // scratch for the running sums is allocated here, outside the timed kernel
     if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
     if (tiled) done = tiles(false);
+    if (ranks) {
+        TGBM_CUDA(cudaMemsetAsync(d_bins.p, MISSING_BIN, d_bins.bytes(), st));
+        const int rk_blocks = (N + RK_ROWS - 1) / RK_ROWS;
+        if (dense_path) k_rank_rows<true><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+        else k_rank_rows<false><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+        const size_t rk_smem = sizeof(RNode) * (size_t)n_nodes * rk_chunk;
+        const int grid = std::max(1, std::min((N + 1023) / 1024, num_sms));
+        auto go = [&](auto kern) {
+            TGBM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rk_smem));
+            kern<<<grid, 256, rk_smem, st>>>(d_bins.p, Fpad, F, N, d_rmodel.p, n_rounds, K, n_nodes, depth, rk_chunk, learning_rate, base_score,
+                                             d_out.p, d_partial.p);
+        };
+        if (dense_path) { if (Fpad == 32) go(k_predict_ranks<true, true>); else go(k_predict_ranks<true, false>); }
+        else { if (Fpad == 32) go(k_predict_ranks<false, true>); else go(k_predict_ranks<false, false>); }
+        done = true;
+    }
     if (done) {
     } else if (dense_path) {
         k_predict_dense<<<(N + PRED_ROWS - 1) / PRED_ROWS, PRED_ROWS, smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_model.p, n_rounds, K,
