@@ -8,6 +8,7 @@
 #include <algorithm>
 #include <chrono>
 #include <cmath>
+#include <cstddef>
 #include <cstdlib>
 #include <cstring>
 
@@ -66,6 +67,7 @@ struct BoosterImpl {
     DevBuf<float2> hist_spread;
     DevBuf<double> sum_partial;
     CutOffsets f32_cuts{};                 // fp32 dense kernel: first bin of every feature, passed by value
+    bool f32_staged = true;                // fp32 dense kernel, gather levels: record tiles staged by bulk copies
     DevBuf<int> bag_count;                 // bagging: multiplicity of every gradient entry in the round's bootstrap sample
     DevBuf<unsigned char> ignored_all;     // column sampling: [round][feature] mask of the features left out
     int f32_stride(int pairs) const {
@@ -484,7 +486,9 @@ void Booster::init(const DataSet &ds) {
     m.model.alloc((size_t)std::max(p.n_trees, 1) * K * m.n_nodes);
     m.metric.alloc(std::max(p.n_trees, 1));
     for (int i = 0; i < 2; ++i) {
-        m.rec_idx[i].alloc(2 * n1); m.rec_gh[i].alloc(2 * n1);  // left children in the first half, right children in the second
+        // left children in the first half, right children in the second (single-pass partition); the bulk copies that
+        // stage a unit of records read up to a unit beyond the last record
+        m.rec_idx[i].alloc(2 * n1 + 2 * F32_THREADS); m.rec_gh[i].alloc(2 * n1 + 2 * F32_THREADS);
         m.seg_begin[i].alloc((size_t)1 << depth); m.seg_cnt[i].alloc((size_t)1 << depth);
         m.seg_begin[i].zero(m.stream); m.seg_cnt[i].zero(m.stream);
     }
@@ -521,6 +525,7 @@ void Booster::init(const DataSet &ds) {
     m.part_status.alloc(m.max_tiles);
     m.part_status.zero(m.stream);
     m.part_one = getenv("TGBM_PART_ONE") != nullptr;
+    m.f32_staged = getenv("TGBM_NO_BULK_COPY") == nullptr;
     m.ctl.alloc(1);
     m.ctl.zero(m.stream);
     m.metric_partial.alloc(1024); m.metric_sum.alloc(1);
@@ -666,10 +671,10 @@ void BoosterImpl::build_tree(int round, int k) {
                                                                                   ctl.p, built_f, B, bs);
             } else if (level == 0)
                 k_hist_f32<false><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, nullptr, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs,
-                                                                                 f32_cuts, F <= 256);
+                                                                                 f32_cuts, F <= 256, 0);
             else
                 k_hist_f32<true><<<dim3(f32_ctas, G), F32_THREADS, 0, stream>>>(bins.p, Fpad, F, idx_in, ghf, hist_seq.p, ctl.p, cut_ptr.p, built_f, B, bs,
-                                                                                f32_cuts, F <= 256);
+                                                                                f32_cuts, F <= 256, f32_staged ? 1 : 0);
         } else if (sparse) {
             const int sp_ctas = num_sms;
             const size_t sp_smem = (size_t)std::min(B, SPARSE_SMEM_BINS) * 16;
@@ -865,6 +870,13 @@ void Booster::sync() {
     if (impl_->comm && impl_->comm->active()) impl_->comm->wait(impl_->stream);  // bounded: a rank may have left
     else TGBM_CUDA(cudaStreamSynchronize(impl_->stream));
     TGBM_CUDA(cudaGetLastError());
+    // bounded waits inside the kernels (look-back of the single-pass partition, bulk-copy barriers of the fp32 histogram
+    // kernel) report here instead of spinning: the results of the run are not to be trusted
+    if (impl_->ctl.p) {
+        int err = 0;
+        TGBM_CUDA(cudaMemcpy(&err, reinterpret_cast<const char *>(impl_->ctl.p) + offsetof(TreeCtl, error), sizeof(int), cudaMemcpyDeviceToHost));
+        TGBM_CHECK(err == 0, "a bounded wait inside a kernel ran out (code " + std::to_string(err) + "); the trees of this run are invalid");
+    }
 }
 
 int Booster::rounds_done() const { return impl_->rounds; }

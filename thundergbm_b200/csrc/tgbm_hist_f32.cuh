@@ -31,29 +31,101 @@ constexpr int F32_THREADS = 512;
 // (with the offsets in shared memory the top stall was the memory-instruction queue).
 struct CutOffsets { int v[256]; };
 
+// ---- bulk-copy staging of the record tiles (gather levels) ---------------------------------------------------------
+// At the levels below the root a CTA reads, for every unit of F32_THREADS records, the unit's row ids and gradient
+// pairs: two contiguous pieces of rec_idx / rec_gh.  They are brought into shared memory by the copy engine
+// (cp.async.bulk global -> shared, completion counted on an mbarrier; a plain one-CTA copy from this GPU's own memory)
+// one unit ahead of the threads, so that the only global loads left on a thread's critical path are its bin row and the
+// reductions.  A bulk copy needs 16-byte aligned addresses and sizes: a unit starts at any record, so the copy starts
+// at the aligned record before it and is a few records longer; the threads index from the remainder.
+// Every wait on the barrier is bounded; a wait that runs out records itself in ctl->error and the CTA stops.
+constexpr int STAGE_IDX = F32_THREADS + 4;   // ints per staged row-id piece   (2064 bytes)
+constexpr int STAGE_GH = F32_THREADS + 2;    // float2 per staged gradient piece (4112 bytes)
+constexpr int STAGE_WAIT_LIMIT = 1 << 22;
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+// true when the phase with the given parity has completed; false after STAGE_WAIT_LIMIT polls
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+    for (int it = 0; it < STAGE_WAIT_LIMIT; ++it) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(done) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
 // Dense layout.  grid = (CTAs, feature groups of 32); a CTA takes half a 1024-record tile of the level's tile
 // sequence at a time, a thread one record: its 32 bin bytes, its gradient pair, one reduction per present feature.
 template <bool GATHER>
 static __global__ void __launch_bounds__(F32_THREADS)
 k_hist_f32(const unsigned char *__restrict__ bins, int Fpad, int F, const int *__restrict__ rec_idx,
-           const float2 *__restrict__ rec_gh, const int4 *__restrict__ seq, const TreeCtl *__restrict__ ctl,
+           const float2 *__restrict__ rec_gh, const int4 *__restrict__ seq, TreeCtl *__restrict__ ctl,
            const int *__restrict__ cut_ptr, float2 *__restrict__ slab, int B, int cell_stride,
-           const __grid_constant__ CutOffsets cuts, int cuts_in_param) {
+           const __grid_constant__ CutOffsets cuts, int cuts_in_param, int staged) {
     __shared__ int s_cut[32];
+    __shared__ __align__(16) int s_idx[2][STAGE_IDX];
+    __shared__ __align__(16) float2 s_gh[2][STAGE_GH];
+    __shared__ __align__(8) uint64_t s_bar[2];
+    __shared__ int s_fail;
     const int f0 = blockIdx.y * 32, nf = min(32, F - f0);
     if (!cuts_in_param) {  // more than 256 features: the offsets of the CTA's group through shared memory
         if (threadIdx.x < 32) s_cut[threadIdx.x] = threadIdx.x < nf ? cut_ptr[f0 + threadIdx.x] : 0;
-        __syncthreads();
     }
     constexpr int PER_TILE = HIST_THREADS / F32_THREADS;
     const int units = ctl->n_hist_tiles * PER_TILE;
-    for (int u = blockIdx.x; u < units; u += gridDim.x) {
+    const bool stage = GATHER && staged;
+    auto unit_first = [&](int u) { const int4 e = seq[u / PER_TILE]; return e.x + (u % PER_TILE) * F32_THREADS; };
+    auto issue = [&](int u, int buf) {  // thread 0: both pieces of unit u into buffer buf
+        const int p0 = unit_first(u);
+        const int a_idx = p0 & ~3, a_gh = p0 & ~1;
+        mbar_expect_tx(&s_bar[buf], (uint32_t)(STAGE_IDX * sizeof(int) + STAGE_GH * sizeof(float2)));
+        bulk_g2s(s_idx[buf], rec_idx + a_idx, (uint32_t)(STAGE_IDX * sizeof(int)), &s_bar[buf]);
+        bulk_g2s(s_gh[buf], rec_gh + a_gh, (uint32_t)(STAGE_GH * sizeof(float2)), &s_bar[buf]);
+    };
+    if (stage) {
+        if (threadIdx.x == 0) {
+            mbar_init(&s_bar[0], 1); mbar_init(&s_bar[1], 1);
+            s_fail = 0;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    __syncthreads();
+    if (stage && threadIdx.x == 0 && (int)blockIdx.x < units) issue(blockIdx.x, 0);
+    int n_done = 0;  // units this CTA has consumed: buffer = n_done & 1, parity = (n_done >> 1) & 1
+    for (int u = blockIdx.x; u < units; u += gridDim.x, ++n_done) {
         const int4 e = seq[u / PER_TILE];  // first record, records, histogram slot
         const int q = (u % PER_TILE) * F32_THREADS + threadIdx.x;
-        if (q >= e.y) continue;
-        const int p = e.x + q;
-        const int r = GATHER ? rec_idx[p] : p;
-        const float2 v = rec_gh[p];
+        int r = -1;
+        float2 v = make_float2(0.f, 0.f);
+        if (stage) {
+            const int buf = n_done & 1;
+            if (threadIdx.x == 0 && u + (int)gridDim.x < units) issue(u + gridDim.x, buf ^ 1);  // one unit ahead
+            if (!mbar_wait(&s_bar[buf], (n_done >> 1) & 1)) { s_fail = 1; atomicCAS(&ctl->error, 0, 0x40000000 | u); }
+            const int p0 = e.x + (u % PER_TILE) * F32_THREADS;
+            if (q < e.y) { r = s_idx[buf][(p0 & 3) + threadIdx.x]; v = s_gh[buf][(p0 & 1) + threadIdx.x]; }
+            __syncthreads();  // every thread holds its record: the buffer may be refilled two units from now
+            if (s_fail) {  // leave only when the copy that is still on its way has landed (bounded as well)
+                if (threadIdx.x == 0 && u + (int)gridDim.x < units) mbar_wait(&s_bar[buf ^ 1], ((n_done + 1) >> 1) & 1);
+                return;
+            }
+            if (threadIdx.x == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        } else if (q < e.y) {
+            const int p = e.x + q;
+            r = GATHER ? rec_idx[p] : p;
+            v = rec_gh[p];
+        }
+        if (r < 0) continue;
         const uint4 *row = reinterpret_cast<const uint4 *>(bins + (size_t)r * Fpad + f0);
         const uint4 a = row[0], b = row[1];
         const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};

@@ -215,16 +215,18 @@ k_predict_tiles(const int *__restrict__ row_ptr, const int *__restrict__ col, co
 #pragma unroll
                     for (int j = 0; j < RPT; ++j) cur[j] = 0;
                     for (int lvl = 0; lvl < depth; ++lvl) {
+                        HNode h[RPT];
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) h[j] = nd[cur[j]];
+                        float fv[RPT];
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) fv[j] = dense[min(h[j].fid & 0x3fffffff, F - 1) * ROWS + j * PT_THREADS + threadIdx.x];
 #pragma unroll
                         for (int j = 0; j < RPT; ++j) {
-                            const HNode h = nd[cur[j]];
-                            if (h.fid >= 0) {  // not a leaf
-                                const int f = h.fid & 0x3fffffff;
-                                const float fv = f < F ? dense[f * ROWS + j * PT_THREADS + threadIdx.x] : absent;
-                                const bool present = DENSE_PATH ? (fv < INFINITY) : (__float_as_uint(fv) != PRED_ABSENT);
-                                const bool right = present ? !(fv < h.v) : (h.fid & 0x40000000) != 0;
-                                cur[j] = 2 * cur[j] + 1 + (right ? 1 : 0);
-                            }
+                            const float v = (h[j].fid & 0x3fffffff) < F ? fv[j] : absent;
+                            const bool present = DENSE_PATH ? (v < INFINITY) : (__float_as_uint(v) != PRED_ABSENT);
+                            const bool right = present ? !(v < h[j].v) : (h[j].fid & 0x40000000) != 0;
+                            cur[j] = h[j].fid >= 0 ? 2 * cur[j] + 1 + (right ? 1 : 0) : cur[j];
                         }
                     }
 #pragma unroll
@@ -306,105 +308,135 @@ k_rank_rows(const int *__restrict__ row_ptr, const int *__restrict__ col, const 
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e0 = s_rp[0], e1 = s_rp[RK_ROWS];
-    for (int base = e0 + warp * 32; base < e1; base += RK_THREADS) {
-        const int e = base + lane;
-        int c = -1;
-        float v = 0.f;
-        if (e < e1) { c = col[e]; v = val[e]; }
-        // row of the warp's first value: the last q with s_rp[q] <= base (RK_ROWS = 32 * 16)
-        const int blk = __popc(__ballot_sync(0xffffffffu, s_rp[16 * lane] <= base)) - 1;
-        const int q0 = 16 * blk + __popc(__ballot_sync(0xffffffffu, lane < 16 && s_rp[16 * blk + lane] <= base)) - 1;
-        int q = q0;
-        for (int k = 1; q0 + k <= RK_ROWS; ++k) {  // row boundaries inside the warp's values
-            const int nb = s_rp[q0 + k];
-            if (nb > base + 31) break;
-            if (nb <= e) q = q0 + k;
+    constexpr int UNROLL = 4;  // pieces of 32 values per warp and iteration: their loads are issued together
+    for (int base0 = e0 + warp * 32 * UNROLL; base0 < e1; base0 += RK_THREADS * UNROLL) {
+        int cc[UNROLL];
+        float vv[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int e = base0 + 32 * u + lane;
+            cc[u] = e < e1 ? col[e] : -1;
+            vv[u] = e < e1 ? val[e] : 0.f;
         }
-        if (c >= 0 && c < F) {
-            int lo = thr_ptr[c];
-            const int first = lo;
-            int hi = thr_ptr[c + 1];
-            const int n_thr = hi - first;
-            while (lo < hi) {
-                const int mid = (lo + hi) >> 1;
-                if (thr[mid] <= v) lo = mid + 1; else hi = mid;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int base = base0 + 32 * u, e = base + lane;
+            if (base >= e1) break;
+            const int c = cc[u];
+            const float v = vv[u];
+            // row of the piece's first value: the last q with s_rp[q] <= base (RK_ROWS = 32 * 16)
+            const int blk = __popc(__ballot_sync(0xffffffffu, s_rp[16 * lane] <= base)) - 1;
+            const int q0 = 16 * blk + __popc(__ballot_sync(0xffffffffu, lane < 16 && s_rp[16 * blk + lane] <= base)) - 1;
+            int q = q0;
+            for (int k = 1; q0 + k <= RK_ROWS; ++k) {  // row boundaries inside the piece
+                const int nb = s_rp[q0 + k];
+                if (nb > base + 31) break;
+                if (nb <= e) q = q0 + k;
             }
-            int r = lo - first;
-            if (DENSE_PATH) { if (!(v < INFINITY)) r = 255; }  // the dense path marks absent features with +inf (predictor.cu:100)
-            else if (v != v) r = n_thr;                         // no threshold is above a NaN: always right
-            bins[(size_t)(row0 + q) * Fpad + c] = (unsigned char)r;
+            if (c >= 0 && c < F) {
+                int lo = thr_ptr[c];
+                const int first = lo;
+                int hi = thr_ptr[c + 1];
+                const int n_thr = hi - first;
+                while (lo < hi) {
+                    const int mid = (lo + hi) >> 1;
+                    if (thr[mid] <= v) lo = mid + 1; else hi = mid;
+                }
+                int r = lo - first;
+                if (DENSE_PATH) { if (!(v < INFINITY)) r = 255; }  // the dense path marks absent features with +inf (predictor.cu:95)
+                else if (v != v) r = n_thr;                         // no threshold is above a NaN: always right
+                bins[(size_t)(row0 + q) * Fpad + c] = (unsigned char)r;
+            }
         }
     }
 }
 
-template <bool DENSE_PATH, bool REG_ROWS>
-__global__ void __launch_bounds__(256)
+constexpr int PR_THREADS = 512;
+constexpr int PR_RPT = 4;
+constexpr int PR_ROWS = PR_THREADS * PR_RPT;
+// WORD_ROWS: rows of at most 32 features.  A row's eight 32-bit words are spread out in shared memory as [word][row]
+// (bank = row: no conflicts whatever word a lane asks for) plus a ninth word of absent marks that nodes on features the
+// data does not have point at; a step costs one read of the node's flags, one read of a word, a shift and a mask -- the
+// kernel is bound by instruction issue, and picking a byte out of eight registers costs twice as many instructions.
+// Otherwise the rank bytes are read from global memory (L1) at every step.
+// Node flags: threshold rank (bits 0-7) | default right (8) | leaf (9) | bit offset of the byte in its word (10-14) |
+// word index (WORD_ROWS) or feature id (16-31).
+template <bool DENSE_PATH, bool WORD_ROWS>
+__global__ void __launch_bounds__(PR_THREADS)
 k_predict_ranks(const unsigned char *__restrict__ bins, int Fpad, int F, int n_rows, const RNode *__restrict__ model, int n_rounds, int K,
                 int n_nodes, int depth, int chunk_trees, float lr, float base_score, float *__restrict__ out, double *__restrict__ partial) {
     extern __shared__ __align__(16) unsigned char rk_sm[];
-    RNode *trees = reinterpret_cast<RNode *>(rk_sm);  // [chunk_trees][n_nodes]
-    constexpr int RPT = 4, ROWS = 256 * RPT;
+    constexpr int RPT = PR_RPT, ROWS = PR_ROWS;
+    uint32_t *words = reinterpret_cast<uint32_t *>(rk_sm);                          // [9][ROWS] (WORD_ROWS only)
+    int *tflags = reinterpret_cast<int *>(rk_sm) + (WORD_ROWS ? 9 * ROWS : 0);      // [chunk_trees][n_nodes]
+    float *tweight = reinterpret_cast<float *>(tflags) + (size_t)chunk_trees * n_nodes;
     const int n_tiles = (n_rows + ROWS - 1) / ROWS;
+    if (WORD_ROWS)
+        for (int i = threadIdx.x; i < ROWS; i += PR_THREADS) words[8 * ROWS + i] = 0xffffffffu;
     for (int t = 0; t < K; ++t) {
         for (int r0 = 0; r0 < n_rounds; r0 += chunk_trees) {
             const int nc = min(chunk_trees, n_rounds - r0);
             const bool first = r0 == 0, last = r0 + nc >= n_rounds;
             __syncthreads();  // the previous chunk's walks are over
-            for (int i = threadIdx.x; i < nc * n_nodes; i += 256)
-                trees[i] = model[((size_t)(r0 + i / n_nodes) * K + t) * n_nodes + i % n_nodes];
+            for (int i = threadIdx.x; i < nc * n_nodes; i += PR_THREADS) {
+                const RNode nd = model[((size_t)(r0 + i / n_nodes) * K + t) * n_nodes + i % n_nodes];
+                tflags[i] = nd.flags; tweight[i] = nd.weight;
+            }
             __syncthreads();
             for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-                uint32_t w[RPT][8];
                 const unsigned char *rowp[RPT];
                 double dsum[RPT];
                 float fsum[RPT];
 #pragma unroll
                 for (int j = 0; j < RPT; ++j) {
-                    const int i = min(tile * ROWS + j * 256 + (int)threadIdx.x, n_rows - 1);
+                    const int slot = j * PR_THREADS + threadIdx.x;
+                    const int i = min(tile * ROWS + slot, n_rows - 1);
                     rowp[j] = bins + (size_t)i * Fpad;
-                    if (REG_ROWS) {
+                    if (WORD_ROWS) {  // a thread spreads out its own rows and reads only them back: no barrier needed
                         const uint4 a = reinterpret_cast<const uint4 *>(rowp[j])[0], b = reinterpret_cast<const uint4 *>(rowp[j])[1];
-                        w[j][0] = a.x; w[j][1] = a.y; w[j][2] = a.z; w[j][3] = a.w; w[j][4] = b.x; w[j][5] = b.y; w[j][6] = b.z; w[j][7] = b.w;
+                        words[0 * ROWS + slot] = a.x; words[1 * ROWS + slot] = a.y; words[2 * ROWS + slot] = a.z; words[3 * ROWS + slot] = a.w;
+                        words[4 * ROWS + slot] = b.x; words[5 * ROWS + slot] = b.y; words[6 * ROWS + slot] = b.z; words[7 * ROWS + slot] = b.w;
                     }
                     dsum[j] = base_score; fsum[j] = base_score;
                     if (!first) { const double p = partial[(size_t)t * n_rows + i]; dsum[j] = p; fsum[j] = (float)p; }
                 }
                 for (int c = 0; c < nc; ++c) {
-                    const RNode *nd = trees + (size_t)c * n_nodes;
+                    const int *ndf = tflags + (size_t)c * n_nodes;
+                    const float *ndw = tweight + (size_t)c * n_nodes;
                     int cur[RPT];
 #pragma unroll
                     for (int j = 0; j < RPT; ++j) cur[j] = 0;
                     for (int lvl = 0; lvl < depth; ++lvl) {
+                        // all rows' node reads first, then their feature reads, then branch-free steps: the walks of a
+                        // thread's rows overlap
+                        int fl[RPT];
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) fl[j] = ndf[cur[j]];
+                        uint32_t wd[RPT];
 #pragma unroll
                         for (int j = 0; j < RPT; ++j) {
-                            const int fl = nd[cur[j]].flags;
-                            if (!(fl & 0x200)) {
-                                const unsigned f = (unsigned)fl >> 16;
-                                int b = MISSING_BIN;
-                                if (REG_ROWS) {
-                                    const uint32_t a0 = (f & 16) ? w[j][4] : w[j][0], a1 = (f & 16) ? w[j][5] : w[j][1],
-                                                   a2 = (f & 16) ? w[j][6] : w[j][2], a3 = (f & 16) ? w[j][7] : w[j][3];
-                                    const uint32_t b0 = (f & 8) ? a2 : a0, b1 = (f & 8) ? a3 : a1;
-                                    b = (((f & 4) ? b1 : b0) >> (8 * (f & 3))) & 0xffu;
-                                    if ((int)f >= F) b = MISSING_BIN;  // a feature the data does not have
-                                } else if ((int)f < F) {
-                                    b = rowp[j][f];
-                                }
-                                const bool left = (b == MISSING_BIN) ? !(fl & 0x100) : (b <= (fl & 0xff));
-                                cur[j] = 2 * cur[j] + (left ? 1 : 2);
-                            }
+                            const unsigned hi = (unsigned)fl[j] >> 16;
+                            if (WORD_ROWS) wd[j] = words[hi * ROWS + j * PR_THREADS + threadIdx.x];
+                            else wd[j] = hi < (unsigned)F ? rowp[j][hi] : (unsigned)MISSING_BIN;
+                        }
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) {
+                            const int b = WORD_ROWS ? (int)((wd[j] >> ((fl[j] >> 10) & 31)) & 0xffu) : (int)wd[j];
+                            const bool left = (b == MISSING_BIN) ? !(fl[j] & 0x100) : (b <= (fl[j] & 0xff));
+                            const int next = 2 * cur[j] + (left ? 1 : 2);
+                            cur[j] = (fl[j] & 0x200) ? cur[j] : next;
                         }
                     }
 #pragma unroll
                     for (int j = 0; j < RPT; ++j) {
-                        const float wt = nd[cur[j]].weight;
+                        const float wt = ndw[cur[j]];
                         if (DENSE_PATH) dsum[j] += (double)__fmul_rn(lr, wt);
                         else fsum[j] = __fmaf_rn(lr, wt, fsum[j]);
                     }
                 }
 #pragma unroll
                 for (int j = 0; j < RPT; ++j) {
-                    const int i = tile * ROWS + j * 256 + (int)threadIdx.x;
+                    const int i = tile * ROWS + j * PR_THREADS + (int)threadIdx.x;
                     if (i >= n_rows) continue;
                     if (last) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
                     else partial[(size_t)t * n_rows + i] = DENSE_PATH ? dsum[j] : (double)fsum[j];
@@ -493,7 +525,7 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     std::vector<int> thr_ptr;
     std::vector<float> thr;
     std::vector<RNode> rflat;
-    bool ranks = heap_ok && getenv("TGBM_PREDICT_FLOAT") == nullptr && sizeof(RNode) * (size_t)n_nodes * std::min(8, n_rounds) <= 200 * 1024 && F < 65536;
+    bool ranks = heap_ok && getenv("TGBM_PREDICT_FLOAT") == nullptr && sizeof(RNode) * (size_t)n_nodes * std::min(8, n_rounds) <= 140 * 1024 && F < 65536;
     if (ranks) {
         std::vector<std::vector<float>> per(F);
         for (size_t i = 0; i < flat.size(); ++i) {
@@ -521,7 +553,10 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
                 const int f = nd.fid & 0x3fffffff;
                 int t = 0;
                 if (f < F) t = (int)(std::lower_bound(per[f].begin(), per[f].end(), nd.v == 0.f ? 0.f : nd.v) - per[f].begin());
-                o.flags = t | ((nd.fid & 0x40000000) ? 0x100 : 0) | (int)((unsigned)std::min(f, 65535) << 16);
+                // rows of up to 32 features are walked on words: bits 16-31 = word index (8 = the word of absent marks, for a
+                // feature the data does not have), bits 10-14 = bit offset of the byte; else bits 16-31 = feature id
+                const unsigned hi = (F <= 32) ? (f < F ? (unsigned)(f >> 2) : 8u) : (unsigned)std::min(f, 65535);
+                o.flags = t | ((nd.fid & 0x40000000) ? 0x100 : 0) | ((F <= 32 && f < F) ? ((f & 3) * 8) << 10 : 0) | (int)(hi << 16);
                 o.weight = 0.f;
             }
         }
@@ -537,7 +572,8 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
         TGBM_CUDA(cudaMemcpyAsync(d_thr_ptr.p, thr_ptr.data(), sizeof(int) * (F + 1), cudaMemcpyHostToDevice, st));
         if (!thr.empty()) TGBM_CUDA(cudaMemcpyAsync(d_thr.p, thr.data(), sizeof(float) * thr.size(), cudaMemcpyHostToDevice, st));
         TGBM_CUDA(cudaMemcpyAsync(d_rmodel.p, rflat.data(), sizeof(RNode) * rflat.size(), cudaMemcpyHostToDevice, st));
-        rk_chunk = (int)std::min<size_t>((size_t)n_rounds, (size_t)(216 * 1024) / (sizeof(RNode) * (size_t)n_nodes));
+        const size_t rk_rows_bytes = F <= 32 ? sizeof(uint32_t) * 9 * PR_ROWS : 0;
+        rk_chunk = (int)std::min<size_t>((size_t)n_rounds, ((size_t)(216 * 1024) - rk_rows_bytes) / (sizeof(RNode) * (size_t)n_nodes));
         if (rk_chunk < n_rounds) d_partial.alloc((size_t)N * K);
     }
     const bool tiled = heap_ok && !ranks;
@@ -555,15 +591,22 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
         const int rk_blocks = (N + RK_ROWS - 1) / RK_ROWS;
         if (dense_path) k_rank_rows<true><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
         else k_rank_rows<false><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
-        const size_t rk_smem = sizeof(RNode) * (size_t)n_nodes * rk_chunk;
-        const int grid = std::max(1, std::min((N + 1023) / 1024, num_sms));
+        const size_t rk_smem = sizeof(RNode) * (size_t)n_nodes * rk_chunk + (F <= 32 ? sizeof(uint32_t) * 9 * PR_ROWS : 0);
+        const int grid = std::max(1, std::min((N + PR_ROWS - 1) / PR_ROWS, num_sms));
+        if (getenv("TGBM_TIMING")) {  // how the time splits between the conversion and the walk
+            cudaEvent_t em;
+            cudaEventCreate(&em); cudaEventRecord(em, st); cudaEventSynchronize(em);
+            float ms = 0;
+            if (gd.e0) { cudaEventElapsedTime(&ms, gd.e0, em); fprintf(stderr, "[tgbm predict] rows -> ranks %8.3f ms\n", ms); }
+            cudaEventDestroy(em);
+        }
         auto go = [&](auto kern) {
             TGBM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rk_smem));
-            kern<<<grid, 256, rk_smem, st>>>(d_bins.p, Fpad, F, N, d_rmodel.p, n_rounds, K, n_nodes, depth, rk_chunk, learning_rate, base_score,
+            kern<<<grid, PR_THREADS, rk_smem, st>>>(d_bins.p, Fpad, F, N, d_rmodel.p, n_rounds, K, n_nodes, depth, rk_chunk, learning_rate, base_score,
                                              d_out.p, d_partial.p);
         };
-        if (dense_path) { if (Fpad == 32) go(k_predict_ranks<true, true>); else go(k_predict_ranks<true, false>); }
-        else { if (Fpad == 32) go(k_predict_ranks<false, true>); else go(k_predict_ranks<false, false>); }
+        if (dense_path) { if (F <= 32) go(k_predict_ranks<true, true>); else go(k_predict_ranks<true, false>); }
+        else { if (F <= 32) go(k_predict_ranks<false, true>); else go(k_predict_ranks<false, false>); }
         done = true;
     }
     if (done) {
