@@ -256,6 +256,55 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def e2e_child(args):
+    """The end-to-end leg, run by rank 0 in a process of its own (so that a fault in it cannot take the benchmark line with it
+    and the parent can bound its time): K rounds through the reference's C entry point with host CSR buffers in pinned memory,
+    n_device = the number of GPUs of the run.  Prints one JSON object."""
+    import torch
+    from thundergbm_b200 import _lib
+    rows_default, _, PARAMS, desc = WORKLOADS[args.config]
+    n_rows = args.rows or rows_default
+    k, world = args.steps, args.gpus
+    lib = _lib.lib()
+    full = make_shard(args.config, n_rows, 0, 1)[0]
+
+    def pin(a, dt):  # the caller's CSR sits in pinned host memory (page-locked once, outside the timed region)
+        return torch.from_numpy(np.ascontiguousarray(a, dt)).pin_memory().numpy()
+    val = pin(full.val, np.float32); rp = pin(full.row_ptr, np.int32)
+    col = pin(full.col, np.int32); y = pin(full.y, np.float32)
+    grp = np.ascontiguousarray(full.group, np.int32)
+
+    def scikit_call(n_trees):
+        model = C.c_void_p(None)
+        num_class = C.c_int(2); per_iter = C.c_int(0)
+        group_label = (C.c_float * 64)()
+        t_a = time.perf_counter()
+        lib.sparse_train_scikit(full.n_rows, val.ctypes.data_as(C.c_void_p), rp.ctypes.data_as(C.c_void_p),
+                                col.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), PARAMS['depth'], n_trees, world,
+                                PARAMS['min_child_weight'], PARAMS['lambda'], PARAMS['gamma'], PARAMS['max_num_bin'], 0,
+                                1.0, 0, 1, PARAMS['learning_rate'], PARAMS['objective'].encode(), C.byref(num_class),
+                                b'hist', C.byref(model), C.byref(per_iter), group_label,
+                                grp.ctypes.data_as(C.c_void_p) if grp.size else None, int(grp.size))
+        dt = time.perf_counter() - t_a
+        if not model.value:
+            raise SystemExit('sparse_train_scikit failed: ' + lib.tgbm_last_error().decode())
+        n_nodes = C.c_int(0)
+        lib.get_n_nodes(C.byref(model), C.byref(n_nodes), 1, 1)
+        lib.model_free(C.byref(model))
+        return dt, per_iter.value, n_nodes.value
+    scikit_call(3)  # untimed warm-up of the same entry point
+    times = []
+    for _ in range(max(1, args.e2e_repeats)):
+        dt, per_iter, n_nodes = scikit_call(k)
+        times.append(dt)
+    h2d = val.nbytes + rp.nbytes + col.nbytes + y.nbytes
+    d2h = k * per_iter * n_nodes * 48
+    print(json.dumps({'value': float(np.median(times)) * 100.0 / k, 'unit': 's/100 trees', 'h2d_bytes_per_step': h2d / k,
+                      'd2h_bytes_per_step': d2h / k, 'calls_s': times, 'hist_mode': 'fp32 (library default on this entry point)',
+                      'note': f'median wall clock of {len(times)} calls of sparse_train_scikit(n_device={world}) with {k} rounds each, '
+                              f'CSR in pinned host memory; scaled by 100/{k}; the calls run in a child process of rank 0'}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
@@ -269,7 +318,12 @@ def main():
     ap.add_argument('--e2e-repeats', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--e2e-child', action='store_true', help=argparse.SUPPRESS)
+    ap.add_argument('--e2e-timeout', type=float, default=300.0, help='seconds the end-to-end leg may take before it is given up')
     args = ap.parse_args()
+    if args.e2e_child:
+        e2e_child(args)
+        return
     if args.impl == 'reference':
         run_reference(args)
         return
@@ -404,44 +458,30 @@ def main():
     e2e = None
     if not args.no_e2e:
         barrier()
+        # With N > 1 rank 0 makes the call (n_device = N: one host thread per GPU inside it) and the other ranks wait on
+        # the HOST (a key in the rendezvous store), not inside a collective: their GPUs must be idle for the call.
+        store = dist.distributed_c10d._get_default_store() if world > 1 else None
+        if rank != 0 and store is not None:
+            import datetime
+            store.wait(['tgbm_e2e_done'], datetime.timedelta(seconds=3600))
         if rank == 0:
-            lib = _lib.lib()
-            full = data if world == 1 else make_shard(args.config, n_rows, 0, 1)[0]
-            # the caller's CSR sits in pinned host memory (page-locked once, outside the timed region)
-            def pin(a, dt):
-                return torch.from_numpy(np.ascontiguousarray(a, dt)).pin_memory().numpy()
-            val = pin(full.val, np.float32); rp = pin(full.row_ptr, np.int32)
-            col = pin(full.col, np.int32); y = pin(full.y, np.float32)
-            grp = np.ascontiguousarray(full.group, np.int32)
-
-            def scikit_call(n_trees):
-                model = C.c_void_p(None)
-                num_class = C.c_int(2); per_iter = C.c_int(0)
-                group_label = (C.c_float * 64)()
-                t_a = time.perf_counter()
-                lib.sparse_train_scikit(full.n_rows, val.ctypes.data_as(C.c_void_p), rp.ctypes.data_as(C.c_void_p),
-                                        col.ctypes.data_as(C.c_void_p), y.ctypes.data_as(C.c_void_p), PARAMS['depth'], n_trees, world,
-                                        PARAMS['min_child_weight'], PARAMS['lambda'], PARAMS['gamma'], PARAMS['max_num_bin'], 0,
-                                        1.0, 0, 1, PARAMS['learning_rate'], PARAMS['objective'].encode(), C.byref(num_class),
-                                        b'hist', C.byref(model), C.byref(per_iter), group_label,
-                                        grp.ctypes.data_as(C.c_void_p) if grp.size else None, int(grp.size))
-                dt = time.perf_counter() - t_a
-                if not model.value:
-                    raise SystemExit('sparse_train_scikit failed: ' + lib.tgbm_last_error().decode())
-                lib.model_free(C.byref(model))
-                return dt, per_iter.value
-            scikit_call(3)  # untimed warm-up of the same entry point (allocator state after the first booster's frees)
-            times = []
-            for _ in range(max(1, args.e2e_repeats)):
-                dt, per_iter = scikit_call(k)
-                times.append(dt)
-            h2d = val.nbytes + rp.nbytes + col.nbytes + y.nbytes
-            d2h = k * per_iter * info.n_nodes * 48
-            e2e_s = float(np.median(times))
-            e2e = {'value': e2e_s * 100.0 / k, 'unit': 's/100 trees', 'h2d_bytes_per_step': h2d / k, 'd2h_bytes_per_step': d2h / k,
-                   'calls_s': times, 'hist_mode': 'fp32 (library default on this entry point)',
-                   'note': f'median wall clock of {len(times)} calls of sparse_train_scikit(n_device={world}) with {k} rounds each, '
-                           f'CSR in pinned host memory; scaled by 100/{k}'}
+            cmd = [sys.executable, os.path.abspath(__file__), '--e2e-child', '--config', args.config, '--rows', str(n_rows), '--gpus', str(world),
+                   '--steps', str(k), '--e2e-repeats', str(args.e2e_repeats)]
+            env = {key: v for key, v in os.environ.items() if key not in ('RANK', 'LOCAL_RANK', 'WORLD_SIZE', 'MASTER_ADDR', 'MASTER_PORT',
+                                                                          'TORCHELASTIC_RUN_ID', 'GROUP_RANK', 'ROLE_RANK', 'LOCAL_WORLD_SIZE')}
+            try:
+                out = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=args.e2e_timeout)
+                lines = [l for l in out.stdout.splitlines() if l.startswith('{')]
+                if out.returncode == 0 and lines:
+                    e2e = json.loads(lines[-1])
+                else:
+                    e2e = {'value': None, 'unit': 's/100 trees', 'h2d_bytes_per_step': None, 'd2h_bytes_per_step': None,
+                           'error': (out.stderr or out.stdout)[-400:]}
+            except subprocess.TimeoutExpired:
+                e2e = {'value': None, 'unit': 's/100 trees', 'h2d_bytes_per_step': None, 'd2h_bytes_per_step': None,
+                       'error': f'the end-to-end call did not finish within {args.e2e_timeout:.0f} s'}
+            if store is not None:
+                store.set('tgbm_e2e_done', '1')
         barrier()
 
     if rank != 0:

@@ -93,7 +93,8 @@ struct BoosterImpl {
     DevBuf<SplitRec> recs;
     DevBuf<int> node_tile0[2], tile_left, tile_node[2];
     DevBuf<int> part_base;                    // single-pass partition: records of the nodes before a node
-    DevBuf<unsigned long long> part_status;   // single-pass partition: look-back word of every tile
+    DevBuf<unsigned long long> part_status;   // single-pass partition: left count of every tile
+    DevBuf<unsigned long long> part_group;    // ... and of every aligned group of 32 tiles (count of contributors << 32 | sum)
     bool part_one = false;
     DevBuf<unsigned> bits;
     DevBuf<TreeCtl> ctl;
@@ -190,8 +191,11 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     {
         DevBuf<unsigned long long> keys, keys2;
         DevBuf<long long> d_nu;
-        try { keys.alloc(std::max<size_t>(nnz, 1)); keys2.alloc(std::max<size_t>(nnz, 1)); d_nu.alloc(1); }
-        catch (const std::exception &e) { local_err = e.what(); }
+        DevBuf<long long> counts, mine;
+        try {
+            keys.alloc(std::max<size_t>(nnz, 1)); keys2.alloc(std::max<size_t>(nnz, 1)); d_nu.alloc(1);
+            if (multi) { counts.alloc(comm->world); mine.alloc(1); }
+        } catch (const std::exception &e) { local_err = e.what(); }
         auto sort_unique = [&](size_t n) -> long long {  // keys -> keys (sorted distinct), returns the count
             if (n == 0) return 0;
             size_t tb = 0;
@@ -220,10 +224,6 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         agree("sorting its feature values");
         if (multi) {
             // union of the ranks' distinct keys: all-gather (padded to the largest rank), then sort + unique again
-            DevBuf<long long> counts;
-            counts.alloc(comm->world);
-            DevBuf<long long> mine;
-            mine.alloc(1);
             TGBM_CUDA(cudaMemcpyAsync(mine.p, &nu, sizeof(long long), cudaMemcpyHostToDevice, stream));
             comm->allgather(mine.p, counts.p, 1, Comm::I64, stream);
             std::vector<long long> hc(comm->world);
@@ -385,9 +385,13 @@ void Booster::init(const DataSet &ds) {
         if (multi) m.comm->agree(local_err, what, m.stream);
         else if (!local_err.empty()) throw Error(local_err);
     };
+    // (buffers of the collectives are allocated inside the local phases too: between an agreement and the launch of the
+    // collective no rank makes a call that could wait for another device -- cudaMalloc can, once peer access is on)
+    DevBuf<long long> mine, all;
     locally([&] {
         if (need_group_file(m.objective)) RankState::validate(ds, m.N);
         m.upload_csr(ds);
+        if (multi) { mine.alloc(3); all.alloc(3 * (size_t)m.comm->world); }
     });
     agree("loading its rows");
 
@@ -396,8 +400,6 @@ void Booster::init(const DataSet &ds) {
     m.row_offset = 0;
     long long first_group = 0, total_groups = (long long)ds.group.size();
     if (multi) {
-        DevBuf<long long> mine, all;
-        mine.alloc(3); all.alloc(3 * (size_t)m.comm->world);
         long long h[3] = {m.N, m.F, (long long)ds.group.size()};
         TGBM_CUDA(cudaMemcpyAsync(mine.p, h, sizeof(h), cudaMemcpyHostToDevice, m.stream));
         m.comm->allgather(mine.p, all.p, 3, Comm::I64, m.stream);
@@ -524,6 +526,8 @@ void Booster::init(const DataSet &ds) {
     m.part_base.alloc((size_t)1 << depth);
     m.part_status.alloc(m.max_tiles);
     m.part_status.zero(m.stream);
+    m.part_group.alloc(m.max_tiles / 32 + 2);
+    m.part_group.zero(m.stream);
     m.part_one = getenv("TGBM_PART_ONE") != nullptr;
     m.f32_staged = getenv("TGBM_NO_BULK_COPY") == nullptr;
     m.ctl.alloc(1);
@@ -638,7 +642,7 @@ void BoosterImpl::build_tree(int round, int k) {
                                                             seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p, f32 ? 1 : 0);
     k_plan_root<<<1, 1024, 0, stream>>>(seg_begin[0].p, seg_cnt[0].p, gcnt.p, nodes.p, built_right.p, hist_work.p, hist_tile_base.p,
                                         node_tile0[0].p, ctl.p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[0].p, part_base.p,
-                                        seg_begin[1].p, seg_cnt[1].p);
+                                        seg_begin[1].p, seg_cnt[1].p, part_group.p, (int)part_group.n);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * (2048 / PART_THREADS)));
@@ -733,14 +737,14 @@ void BoosterImpl::build_tree(int round, int k) {
             if (sparse)
                 k_part_one<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, tile_node[cur].p,
                                                                          part_base.p, ctl.p, idx_in, gh_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p,
-                                                                         part_status.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
+                                                                         part_status.p, part_group.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
             else
                 k_part_one<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, tile_node[cur].p,
                                                                           part_base.p, ctl.p, idx_in, gh_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p,
-                                                                          part_status.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
+                                                                          part_status.p, part_group.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
             k_plan_next<<<1, 1024, 0, stream>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, seg_cnt[nxt].p, nodes.p, ctl.p, by_hessian, built_right.p,
                                                 hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p,
-                                                part_base.p, seg_begin[cur].p, seg_cnt[cur].p);
+                                                part_base.p, seg_begin[cur].p, seg_cnt[cur].p, part_group.p, (int)part_group.n);
             if (profile_on) { cudaEventRecord(pv.b, stream); events.push_back(pv); }
             launches += 2;
             continue;
@@ -759,7 +763,7 @@ void BoosterImpl::build_tree(int round, int k) {
         TGBM_CUDA(cudaStreamWaitEvent(stream2, ev_scan, 0));
         k_plan_next<<<1, 1024, 0, stream2>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, nodes.p, ctl.p, by_hessian, built_right.p,
                                              hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p,
-                                             part_base.p, nullptr, nullptr);
+                                             part_base.p, nullptr, nullptr, nullptr, 0);
         TGBM_CUDA(cudaEventRecord(ev_plan, stream2));
         k_part_scatter<<<std::max(1, part_ctas - 1024 / PART_THREADS), PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p,
                                                                                 node_tile0[cur].p, ctl.p, idx_in, gh_in, bits.p, tile_left.p,
@@ -829,7 +833,11 @@ void BoosterImpl::run_round(int round) {
         round_metric(round);
     };
     static const bool graph_with_comm = getenv("TGBM_NO_GRAPH_COMM") == nullptr;  // the round's collectives are captured with it
-    const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid &&
+    // Ranks that are threads of ONE process do not replay graphs: instantiating a graph allocates device memory, and with
+    // peer access enabled such a call can wait for the other devices of the process -- whose collective kernels may
+    // already be waiting for this rank's.  (Between processes there is no such coupling.)
+    const bool in_process_group = comm && comm->active() && comm->host;
+    const bool graph_ok = graphs_allowed && round >= 1 && !profile_on && !p.keep_nid && !in_process_group &&
                           (graph_with_comm || !(comm && comm->active()));
     if (!graph_ok) { direct(); return; }
     if (!round_exec) {

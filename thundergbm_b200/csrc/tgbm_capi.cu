@@ -108,7 +108,9 @@ std::vector<std::vector<tgbm::Tree>> train_in_process(tgbm::GBMParam &p, const t
     TGBM_CUDA(cudaGetDevice(&caller_dev));
     unsigned char id[128];
     tgbm::comm_get_unique_id(id);
-    auto group = std::make_shared<tgbm::HostGroup>(n_dev, 600.0);
+    double group_timeout_s = 120.0;  // how long a rank waits for the others at a meeting point (TGBM_GROUP_TIMEOUT_S)
+    if (const char *e = getenv("TGBM_GROUP_TIMEOUT_S")) group_timeout_s = atof(e) > 0 ? atof(e) : group_timeout_s;
+    auto group = std::make_shared<tgbm::HostGroup>(n_dev, group_timeout_s);
     // row blocks: rows n*r/W, moved to the next query-group boundary when there are groups
     std::vector<int> row_lo(n_dev + 1, 0), grp_lo(n_dev + 1, 0);
     {

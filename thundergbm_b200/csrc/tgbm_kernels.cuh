@@ -1173,7 +1173,8 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
 __device__ inline int tile_owner(const int *__restrict__ node_tile0, int nl, int t);
 __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int *__restrict__ node_tile0,
                                  int *__restrict__ tile_node, TreeCtl *__restrict__ ctl, bool count_rows, int *__restrict__ part_base,
-                                 int *__restrict__ child_begin, int *__restrict__ child_cnt) {
+                                 int *__restrict__ child_begin, int *__restrict__ child_cnt,
+                                 unsigned long long *__restrict__ group_sum, int n_group_words) {
     __shared__ int scratch[33];
     __shared__ unsigned long long rows;
     const int nl = 1 << level;
@@ -1185,6 +1186,8 @@ __device__ inline void part_plan(int level, const int *__restrict__ seg_cnt, int
                         if (seg_cnt[n] == 0 && child_cnt) { child_cnt[2 * n] = 0; child_cnt[2 * n + 1] = 0; child_begin[2 * n] = b; child_begin[2 * n + 1] = b; }
                     }, scratch);
     if (threadIdx.x == 0) { ctl->part_ticket = 0; ctl->part_epoch = (ctl->part_epoch + 1) & 0x3fffffffu; }
+    if (group_sum)
+        for (int g = threadIdx.x; g < n_group_words; g += 1024) group_sum[g] = 0;
     if (threadIdx.x == 0) rows = 0;
     __syncthreads();
     const int total = block_scan_excl(nl, [&](int n) { return (seg_cnt[n] + PART_TILE - 1) / PART_TILE; },
@@ -1310,11 +1313,12 @@ k_plan_next(int level, const int *__restrict__ next_begin, const int *__restrict
             const TreeNode *__restrict__ nodes, TreeCtl *__restrict__ ctl, int by_hessian, int *__restrict__ built_right,
             HistWork *__restrict__ work, int *__restrict__ hist_tile_base, int *__restrict__ next_node_tile0, int n_ctas,
             int *__restrict__ cta_off, int4 *__restrict__ seq, int depth, int *__restrict__ next_tile_node, int *__restrict__ part_base,
-            int *__restrict__ child_begin, int *__restrict__ child_cnt) {
+            int *__restrict__ child_begin, int *__restrict__ child_cnt, unsigned long long *__restrict__ group_sum, int n_group_words) {
     // child_begin / child_cnt: segment table of level + 2, the one the partition of level + 1 will fill
     hist_plan(level + 1, next_begin, next_cnt, gcnt, nodes, by_hessian, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(level + 1, next_cnt, next_node_tile0, next_tile_node, ctl, level + 1 < depth - 1, part_base, child_begin, child_cnt);
+    part_plan(level + 1, next_cnt, next_node_tile0, next_tile_node, ctl, level + 1 < depth - 1, part_base, child_begin, child_cnt,
+              group_sum, n_group_words);
 }
 
 // work lists of level 0 (the whole data set in the root)
@@ -1323,10 +1327,10 @@ k_plan_root(const int *__restrict__ seg_begin, const int *__restrict__ seg_cnt, 
             const TreeNode *__restrict__ nodes, int *__restrict__ built_right, HistWork *__restrict__ work,
             int *__restrict__ hist_tile_base, int *__restrict__ node_tile0, TreeCtl *__restrict__ ctl, int n_ctas, int *__restrict__ cta_off,
             int4 *__restrict__ seq, int depth, int *__restrict__ tile_node, int *__restrict__ part_base,
-            int *__restrict__ child_begin, int *__restrict__ child_cnt) {
+            int *__restrict__ child_begin, int *__restrict__ child_cnt, unsigned long long *__restrict__ group_sum, int n_group_words) {
     hist_plan(0, seg_begin, seg_cnt, gcnt, nodes, 0, built_right, work, hist_tile_base, ctl, n_ctas, cta_off, seq);
     __syncthreads();
-    part_plan(0, seg_cnt, node_tile0, tile_node, ctl, depth > 1, part_base, child_begin, child_cnt);
+    part_plan(0, seg_cnt, node_tile0, tile_node, ctl, depth > 1, part_base, child_begin, child_cnt, group_sum, n_group_words);
 }
 
 // Stable scatter of the records into the child segments; records of nodes that stopped splitting are dropped.
@@ -1394,13 +1398,14 @@ k_part_scatter(int level, const TreeNode *__restrict__ nodes, const int *__restr
 // Count, prefix and scatter of a level in ONE kernel.  The output list has two halves: the left children of all nodes
 // go to the first half, the right children to the second, both at offset part_base[n] = records of the nodes before
 // node n.  A record's place then depends only on how many records BEFORE it in its own node go left -- a prefix
-// inside the node, which the tiles of a node pass along by decoupled look-back: every tile publishes its own left
-// count at once ("aggregate") and, as soon as it has summed up its predecessors, its inclusive prefix.  Tiles are
-// handed out in ascending order by a ticket, so a tile only ever waits for tiles that are already running.
+// inside the node.  Every tile publishes its own left count as soon as it has it, per tile and summed per aligned
+// group of 32 tiles; a tile adds up the counts before it from those words (no chain of prefixes: with ~600 tiles in
+// flight a chained look-back walks back over all of them).  Tiles are handed out in ascending order by a ticket, so
+// a tile only ever waits for tiles that are already running.
 // The waits are bounded: a tile that gives up records itself in ctl->error and goes on (the host checks the word
 // after its next sync), so no GPU is ever left spinning.
 // Stable: the rows of either child ascend like those of the node.  Records of nodes that stopped splitting drop out.
-constexpr unsigned long long PART_AGG = 1ull << 32, PART_PREFIX = 2ull << 32;
+constexpr unsigned long long PART_AGG = 1ull << 32, PART_PREFIX = 2ull << 32;  // kind of a status word (bits 32-33)
 constexpr int PART_WAIT_LIMIT = 1 << 22;  // polls of ~50 ns each
 
 __device__ __forceinline__ unsigned long long part_status_wait(const unsigned long long *p, unsigned epoch, TreeCtl *ctl, int tile) {
@@ -1420,8 +1425,8 @@ k_part_one(int level, const TreeNode *__restrict__ nodes, const int *__restrict_
            TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx, const int2 *__restrict__ rec_gh,
            const unsigned char *__restrict__ binsT, size_t Npad, const int *__restrict__ sp_row_ptr,
            const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr, unsigned long long *__restrict__ status,
-           int *__restrict__ next_begin, int *__restrict__ next_cnt, int *__restrict__ out_idx, int2 *__restrict__ out_gh,
-           int half) {
+           unsigned long long *__restrict__ group_sum, int *__restrict__ next_begin, int *__restrict__ next_cnt,
+           int *__restrict__ out_idx, int2 *__restrict__ out_gh, int half) {
     constexpr int WORDS = PART_TILE / 32;        // ballot words of a tile, in record order
     constexpr int WARPS = PART_THREADS / 32;
     __shared__ int s_tile, s_before;
@@ -1490,25 +1495,43 @@ k_part_one(int level, const TreeNode *__restrict__ nodes, const int *__restrict_
             const int total = __shfl_sync(0xffffffffu, v, 31);
             wpre[2 * lane] = v - c0 - c1;
             wpre[2 * lane + 1] = v - c1;
+            // Left records of the node's earlier tiles.  Every tile publishes its own count at once (a status word, and
+            // added into the word of its aligned group of 32 tiles), so nothing here waits on a chain: the tiles between
+            // the node's first tile and this one are covered by at most two windows of 32 status words (the ragged ends)
+            // and the complete groups between them, all read side by side.
             int before = 0;
             const unsigned long long tag = (unsigned long long)epoch << 34;
+            if (lane == 0) {
+                *reinterpret_cast<volatile unsigned long long *>(status + t) = tag | PART_AGG | (unsigned)total;
+                atomicAdd(group_sum + (t >> 5), (1ull << 32) | (unsigned)total);
+            }
             if (k > 0) {
-                if (lane == 0) *reinterpret_cast<volatile unsigned long long *>(status + t) = tag | PART_AGG | (unsigned)total;
-                for (int look = t - 1;; look -= 32) {
-                    const int idx = look - lane;
-                    unsigned long long st = tag | PART_PREFIX;  // before the node's first tile: nothing
-                    if (idx >= t0) st = part_status_wait(status + idx, epoch, ctl, t);
-                    const unsigned stop = __ballot_sync(0xffffffffu, (st & PART_PREFIX) != 0);
-                    const int first = stop ? __ffs(stop) - 1 : 32;
-                    int add = lane <= first ? (int)(unsigned)(st & 0xffffffffull) : 0;
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) add += __shfl_xor_sync(0xffffffffu, add, o);
-                    before += add;
-                    if (stop) break;
+                const int gs = (t0 + 31) >> 5, ge = t >> 5;  // complete groups inside the node before t: [gs, ge)
+                int part = 0;
+                if (gs > ge) {  // the node starts in t's own group
+                    const int idx = t0 + lane;
+                    if (idx < t) part = (int)(unsigned)(part_status_wait(status + idx, epoch, ctl, t) & 0xffffffffull);
+                } else {
+                    const int head = t0 + lane, tail = 32 * ge + lane;
+                    if (head < 32 * gs) part = (int)(unsigned)(part_status_wait(status + head, epoch, ctl, t) & 0xffffffffull);
+                    if (tail < t) part += (int)(unsigned)(part_status_wait(status + tail, epoch, ctl, t) & 0xffffffffull);
+                    for (int g = gs + lane; g < ge; g += 32) {
+                        unsigned long long w = 0;
+                        int it = 0;
+                        for (; it < PART_WAIT_LIMIT; ++it) {
+                            w = *reinterpret_cast<const volatile unsigned long long *>(group_sum + g);
+                            if ((w >> 32) == 32ull) break;  // all 32 tiles of the group have added their count
+                            __nanosleep(40);
+                        }
+                        if (it == PART_WAIT_LIMIT) atomicCAS(&ctl->error, 0, 1 + t);
+                        part += (int)(unsigned)(w & 0xffffffffull);
+                    }
                 }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+                before = part;
             }
             if (lane == 0) {
-                *reinterpret_cast<volatile unsigned long long *>(status + t) = tag | PART_PREFIX | (unsigned)(before + total);
                 s_before = before;
                 if (t == node_tile0[n + 1] - 1) {  // the node's last tile knows the node's left count
                     next_cnt[2 * n] = before + total; next_cnt[2 * n + 1] = cnt - (before + total);
