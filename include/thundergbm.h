@@ -84,6 +84,9 @@ typedef struct {
     int bagging;        /* RowSampler::do_bagging (src/thundergbm/row_sampler.cu:9-35): bootstrap multiplicities on (g,h) */
     float column_sampling_rate; /* Shard::column_sampling (src/thundergbm/builder/shard.cu:8-23); 1 = off */
     unsigned sample_seed;       /* seed of both samplers (the reference draws from std::rand()) */
+    int column_shards;  /* 0: cut points, candidate order and child sums of HistTreeBuilder_single, the reference's builder
+                           for n_device = 1; D >= 1: those of the column-sharded HistTreeBuilder it runs for n_device = D > 1
+                           (src/thundergbm/builder/hist_tree_builder.cu, hist_cut.cu:104-187), whose cut points depend on D */
 } TgbmParam;
 
 typedef struct {

@@ -8,7 +8,9 @@
 //
 // usage: ref_harness <input.tgbin> <out_dir> [key=value ...]
 //   keys: depth n_trees max_num_bin lambda gamma min_child_weight learning_rate
-//         objective tree_method verbose
+//         objective tree_method verbose n_device dump_bins
+//   n_device > 1 (the reference's column-sharded HistTreeBuilder): dump_bins=1, the default, writes the devices' cut
+//   points and bin matrices and stops; dump_bins=0 trains.
 // input.tgbin: i32 n_rows, i32 n_group, i64 nnz, i32 row_ptr[n_rows+1],
 //              i32 col[nnz], f32 val[nnz], f32 y[n_rows], i32 group[n_group]
 #include <cstdio>
@@ -27,6 +29,7 @@
 #define private public
 #define protected public
 #include <thundergbm/builder/hist_tree_builder_single.h>
+#include <thundergbm/builder/hist_tree_builder.h>
 #undef private
 #undef protected
 #include <thundergbm/trainer.h>
@@ -67,6 +70,7 @@ int main(int argc, char **argv) {
         else if (key == "verbose") p.verbose = atoi(v);
         else if (key == "num_class") p.num_class = atoi(v);
         else if (key == "dump_bins") dump_bins = atoi(v);
+        else if (key == "n_device") p.n_device = atoi(v);  // > 1: the reference's column-sharded HistTreeBuilder
     }
     el::Loggers::reconfigureAllLoggers(el::ConfigurationType::Format, "%level : %msg");
     el::Loggers::reconfigureAllLoggers(el::Level::Debug, el::ConfigurationType::Enabled, "false");
@@ -91,7 +95,7 @@ int main(int argc, char **argv) {
     DataSet ds;
     ds.load_from_sparse(n_rows, val.data(), row_ptr.data(), col.data(), y.data(), group.data(), n_group, p);
 
-    if (dump_bins) {
+    if (dump_bins && p.n_device == 1) {
         // what the reference's 1-GPU builder computes at init: cut points and global bin ids
         GBMParam q = p;
         if (q.objective.find("multi:") != std::string::npos || q.objective.find("binary:") != std::string::npos)
@@ -105,6 +109,29 @@ int main(int argc, char **argv) {
         dump(out + "/cut_fid.i32", cut.cut_fid.host_data(), B);
         dump(out + "/csr_bin_id.i32", b.csr_bin_id[0].host_data(), b.csr_bin_id[0].size());
         printf("HARNESS n_bins %d nnz %lld n_features %zu\n", B, nnz, ds.n_features());
+    }
+
+    if (dump_bins && p.n_device > 1) {
+        // what the reference's column-sharded builder computes at init, per device: cut points (descending
+        // within a feature) and the dense matrix of local bin ids (missing = max_num_bin).  A run of its own: a second
+        // multi-device builder in the process disturbs the reference's training (it aborts in SyncMem or loses
+        // histogram updates), and one made after the training computes other cut points for some columns.
+        GBMParam q = p;
+        if (q.objective.find("multi:") != std::string::npos || q.objective.find("binary:") != std::string::npos)
+            q.num_class = ds.label.size();
+        HistTreeBuilder b;
+        b.init(ds, q);
+        for (int d = 0; d < p.n_device; ++d) {
+            auto &cut = b.cut[d];
+            std::string sfx = "_d" + std::to_string(d);
+            dump(out + "/cut_val" + sfx + ".f32", cut.cut_points_val.host_data(), cut.cut_points_val.size());
+            dump(out + "/cut_row_ptr" + sfx + ".i32", cut.cut_row_ptr.host_data(), cut.cut_row_ptr.size());
+            dump(out + "/dense_bin_id" + sfx + ".u8", b.dense_bin_id[d].host_data(), b.dense_bin_id[d].size());
+            printf("HARNESS device %d n_bins %zu n_column %d column_offset %d\n", d, cut.cut_points_val.size(),
+                   b.shards[d].columns.n_column, b.shards[d].columns.column_offset);
+        }
+        printf("HARNESS dump only\n");
+        return 0;
     }
 
     TreeTrainer trainer;

@@ -77,6 +77,7 @@ struct TgoParam {
     int bagging;                // RowSampler::do_bagging
     float column_sampling_rate; // Shard::column_sampling, 1 = off
     unsigned sample_seed;
+    int multi_shards;  // 0: HistTreeBuilder_single; D >= 1: HistTreeBuilder with the columns split over D devices
 };
 }
 
@@ -208,6 +209,99 @@ void bin_ids(Ctx &c) {
             if (c.cut_val[mid] <= v) lo = mid + 1; else hi = mid;
         }
         c.bin[i] = lo;
+    }
+}
+
+// ------------------------------------------------- column-sharded builder (n_device > 1)
+// src/thundergbm/sparse_columns.cu:95-102 csr2csc_gpu: device d owns the columns [d*(F/D), (d+1)*(F/D)), the
+// last device also the remainder.
+inline void shard_columns(int F, int D, int d, int &first, int &count) {
+    const int ave = F / D;
+    first = d * ave;
+    count = d < D - 1 ? ave : F - first;
+}
+
+// src/thundergbm/hist_cut.cu:104-187 get_cut_points3 + unique_by_flag, once per device on its own columns:
+// every stored value v of local column j becomes t = v + j*(m+1) with m the largest value on the device, all t
+// are sorted descending, the column ids are laid over them by COUNT (largest id first), runs of equal t collapse
+// to their first entry, t goes back to t - j*(m+1) and a stable sort by column id groups the result.  The round
+// trip is done in float (each direction one fused multiply-add, checked against the reference's own cut points), so for j > 0 the candidates are the stored values rounded to the spacing of floats near
+// j*(m+1), and columns whose values reach below -1 trade candidates with their neighbours; both effects are part of
+// what the reference computes and are kept.  From the n candidates of a column every (n / max_bin)-th is kept
+// (all when n < max_bin), at most max_bin, in descending order.
+void find_cuts_multi(Ctx &c) {
+    const int F = c.F, mb = c.p.max_num_bin, D = c.p.multi_shards;
+    const int64_t nnz = c.row_ptr[c.N];
+    std::vector<int64_t> cnt(F + 1, 0);
+    for (int64_t i = 0; i < nnz; ++i) cnt[c.col[i] + 1]++;
+    for (int f = 0; f < F; ++f) cnt[f + 1] += cnt[f];
+    std::vector<float> byc(nnz);
+    {
+        std::vector<int64_t> pos(cnt.begin(), cnt.end() - 1);
+        for (int64_t i = 0; i < nnz; ++i) byc[pos[c.col[i]]++] = c.val[i];
+    }
+    std::vector<std::vector<float>> per(F);
+    for (int d = 0; d < D; ++d) {
+        int first, ncol;
+        shard_columns(F, D, d, first, ncol);
+        const int64_t lo = cnt[first], hi = cnt[first + ncol], n = hi - lo;
+        if (n == 0) continue;
+        float m = byc[lo];
+        for (int64_t i = lo; i < hi; ++i) m = std::max(m, byc[i]);
+        const float step = m + 1;
+        std::vector<float> t(n);
+        for (int j = 0; j < ncol; ++j)
+            for (int64_t i = cnt[first + j]; i < cnt[first + j + 1]; ++i) {
+                const float v = byc[i];
+                t[i - lo] = fmaf((float)j, step, v);  // nvcc contracts the functor's `v + j * step` into one fma
+            }
+        std::sort(t.begin(), t.end(), std::greater<float>());
+        std::vector<int> flag(n);
+        {
+            int64_t o = 0;
+            for (int j = ncol - 1; j >= 0; --j)
+                for (int64_t i = cnt[first + j]; i < cnt[first + j + 1]; ++i) flag[o++] = j;
+        }
+        std::vector<std::vector<float>> cand(ncol);
+        for (int64_t i = 0; i < n; ++i) {
+            if (i > 0 && t[i] == t[i - 1]) continue;  // thrust::unique_by_key keeps the first of a run
+            const int j = flag[i];
+            cand[j].push_back(fmaf(-(float)j, step, t[i]));
+        }
+        for (int j = 0; j < ncol; ++j) {
+            const auto &a = cand[j];
+            const int u = (int)a.size(), s = u / mb;
+            auto &o = per[first + j];
+            if (s == 0) o = a;
+            else { o.resize(mb); for (int k = 0; k < mb; ++k) o[k] = a[(int64_t)s * k]; }
+        }
+    }
+    c.cut_ptr.assign(F + 1, 0);
+    for (int f = 0; f < F; ++f) c.cut_ptr[f + 1] = c.cut_ptr[f] + (int)per[f].size();
+    c.cut_val.resize(c.cut_ptr[F]);
+    c.cut_fid.resize(c.cut_ptr[F]);
+    for (int f = 0; f < F; ++f)
+        for (size_t j = 0; j < per[f].size(); ++j) {
+            c.cut_val[c.cut_ptr[f] + j] = per[f][j];
+            c.cut_fid[c.cut_ptr[f] + j] = f;
+        }
+}
+
+// src/thundergbm/builder/hist_tree_builder.cu:15-64 get_bin_ids: over the column's cut points as stored (meant to
+// descend) the search of :31-42 -- first position whose cut is <= v, the last position when there is none.
+void bin_ids_multi(Ctx &c) {
+    const int64_t nnz = c.row_ptr[c.N];
+    c.bin.resize(nnz);
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < nnz; ++i) {
+        const int f = c.col[i];
+        int left = c.cut_ptr[f], right = c.cut_ptr[f + 1] - 1;
+        const float v = c.val[i];
+        while (left != right) {
+            const int mid = left + (right - left) / 2;
+            if (c.cut_val[mid] <= v) right = mid; else left = mid + 1;
+        }
+        c.bin[i] = left;
     }
 }
 
@@ -501,8 +595,83 @@ struct Builder {
         return sp;
     }
 
+    // Column-sharded builder, src/thundergbm/builder/hist_tree_builder.cu:299-433 on every device and
+    // tree_builder.cu:112-147 split_point_all_reduce across them: inclusive prefix sums along the column's bins
+    // (largest values first) are the RIGHT child, the left one is the node minus it; the node's missing values go
+    // right when that gains at least as much; arg abs max with ties to the smaller index inside a device and to
+    // the lower device across them, which together is the smallest global bin index.  Split::l_* carry the right
+    // child's sums here (SplitPoint::rch_sum_gh).
+    Split evaluate_multi(const Hist &H, int node_id) {
+        const TreeNode &nd = nodes[node_id];
+        Split sp;
+        if (!nd.is_valid) return sp;
+        const int B = (int)c.cut_val.size();
+        const float pg = nd.sum_g, ph = nd.sum_h, mcw = c.p.min_child_weight, lam = c.p.lambda;
+        float best = 0, second = 0; int besti = -1; bool have = false;
+        std::vector<float> Pg(B), Ph(B);
+        for (int f = 0; f < c.F; ++f) {
+            const int b0 = c.cut_ptr[f], b1 = c.cut_ptr[f + 1];
+            if (b0 == b1) continue;
+            if (!c.ignored.empty() && c.ignored[f]) continue;
+            if (c.p.hist_mode == 1) {
+                double ag = 0, ah = 0;
+                for (int i = b0; i < b1; ++i) { ag += H.g[i]; ah += H.h[i]; Pg[i] = to_f(ag, q.sg); Ph[i] = to_f(ah, q.sh); }
+            } else {
+                float ag = 0, ah = 0;
+                for (int i = b0; i < b1; ++i) { ag += (float)H.g[i]; ah += (float)H.h[i]; Pg[i] = ag; Ph[i] = ah; }
+            }
+            const float mg = pg - Pg[b1 - 1], mh = ph - Ph[b1 - 1];   // :288-298
+            for (int i = b0; i < b1; ++i) {
+                const float rg = Pg[i], rh = Ph[i];
+                const float gl = fmaxf(0.f, gainf(pg, ph, pg - rg, ph - rh, rg, rh, mcw, lam));
+                const float rg2 = rg + mg, rh2 = rh + mh;
+                const float gr = fmaxf(0.f, gainf(pg, ph, pg - rg2, ph - rh2, rg2, rh2, mcw, lam));
+                const float gn = gl > gr ? gl : -gr;
+                if (!have || fabsf(gn) > fabsf(best)) { if (have) second = fmaxf(second, fabsf(best)); best = gn; besti = i; have = true; }
+                else second = fmaxf(second, fabsf(gn));
+            }
+        }
+        sp.nid = node_id;
+        if (!have) { sp.fea = -1; sp.gain = 0; return sp; }
+        const int f = c.cut_fid[besti], b0 = c.cut_ptr[f];
+        sp.fea = f;
+        sp.gain = fabsf(best);
+        sp.gain2 = second;
+        sp.bid = (unsigned char)(besti - b0);
+        sp.default_right = best < 0;
+        sp.miss_g = pg - Pg[c.cut_ptr[f + 1] - 1];
+        sp.miss_h = ph - Ph[c.cut_ptr[f + 1] - 1];
+        sp.l_g = Pg[besti]; sp.l_h = Ph[besti];
+        sp.fval = c.cut_val[besti];
+        return sp;
+    }
+
+    // src/thundergbm/builder/tree_builder.cu:9-60 update_tree (the column-sharded builder's)
+    void apply_multi(const Split &sp) {
+        if (sp.nid == -1) return;
+        TreeNode &nd = nodes[sp.nid];
+        if (sp.gain > c.p.rt_eps) {
+            nd.gain = sp.gain;
+            TreeNode &l = nodes[nd.lch_index], &r = nodes[nd.rch_index];
+            l.is_valid = true; r.is_valid = true;
+            nd.split_feature_id = sp.fea;
+            nd.split_value = sp.fval;
+            nd.split_bid = sp.bid;
+            r.sum_g = sp.l_g; r.sum_h = sp.l_h;
+            if (sp.default_right) { r.sum_g = r.sum_g + sp.miss_g; r.sum_h = r.sum_h + sp.miss_h; nd.default_right = true; }
+            l.sum_g = nd.sum_g - r.sum_g; l.sum_h = nd.sum_h - r.sum_h;
+            l.base_weight = -l.sum_g / (l.sum_h + c.p.lambda);
+            r.base_weight = -r.sum_g / (r.sum_h + c.p.lambda);
+        } else {
+            nd.is_leaf = true;
+            nodes[nd.lch_index].is_valid = false;
+            nodes[nd.rch_index].is_valid = false;
+        }
+    }
+
     // hist_tree_builder_single.cu:847-902 update_tree
     void apply(const Split &sp) {
+        if (c.p.multi_shards > 0) { apply_multi(sp); return; }
         if (sp.nid == -1) return;
         TreeNode &nd = nodes[sp.nid];
         if (sp.gain > c.p.rt_eps) {
@@ -543,7 +712,9 @@ struct Builder {
                 if (v < b0) lo = mid + 1; else hi = mid;
             }
             bool left = true;
-            if ((bid == -1 && nd.default_right) || (bid >= sb && bid >= 0)) left = false;
+            if (c.p.multi_shards > 0) {  // hist_tree_builder.cu:455-459: bins count down from the largest values
+                if ((bid == -1 && nd.default_right) || (bid >= 0 && bid <= sb)) left = false;
+            } else if ((bid == -1 && nd.default_right) || (bid >= sb && bid >= 0)) left = false;
             nid[i] = left ? nd.lch_index : nd.rch_index;
         }
         return any;
@@ -614,7 +785,10 @@ struct Builder {
                 }
             }
             for (int n = 0; n < n_level; ++n)
-                if (!LH[n].g.empty()) { sps[n] = evaluate(LH[n], off + n); gain2[off + n] = sps[n].gain2; }
+                if (!LH[n].g.empty()) {
+                    sps[n] = c.p.multi_shards > 0 ? evaluate_multi(LH[n], off + n) : evaluate(LH[n], off + n);
+                    gain2[off + n] = sps[n].gain2;
+                }
             if (dump_hist) {
                 const int B = (int)c.cut_val.size();
                 for (int n = 0; n < n_level; ++n)
@@ -758,8 +932,8 @@ void train(Ctx &c) {
         if (c.p.num_class > 2) c.K = c.p.num_class;
     } else if (o == REG_LINEAR || o == REG_LOGISTIC) c.p.num_class = 1;
     if (o == RANK_NDCG) compute_idcg(c);
-    find_cuts(c);
-    bin_ids(c);
+    if (c.p.multi_shards > 0) { find_cuts_multi(c); bin_ids_multi(c); }
+    else { find_cuts(c); bin_ids(c); }
     const int N = c.N, K = c.K;
     c.n_nodes = (1 << (c.p.depth + 1)) - 1;
     c.ypred.assign((size_t)K * N, 0.f);
@@ -877,10 +1051,11 @@ void tgo_predict_raw(int n_rows, const int *row_ptr, const int *col, const float
 
 // stand-alone pieces for kernel-level parity tests ------------------------------------------
 // cut points + global bin ids only
-void *tgo_bin_only(int n_rows, const int *row_ptr, const int *col, const float *val, int max_num_bin) {
+void *tgo_bin_only(int n_rows, const int *row_ptr, const int *col, const float *val, int max_num_bin, int multi_shards) {
     Ctx *c = new Ctx;
     memset(&c->p, 0, sizeof(c->p));
     c->p.max_num_bin = max_num_bin;
+    c->p.multi_shards = multi_shards;
     c->N = n_rows;
     const int64_t nnz = row_ptr[n_rows];
     c->row_ptr.assign(row_ptr, row_ptr + n_rows + 1);
@@ -889,8 +1064,8 @@ void *tgo_bin_only(int n_rows, const int *row_ptr, const int *col, const float *
     int F = 0;
     for (int64_t i = 0; i < nnz; ++i) F = std::max(F, col[i]);
     c->F = F + 1;
-    find_cuts(*c);
-    bin_ids(*c);
+    if (multi_shards > 0) { find_cuts_multi(*c); bin_ids_multi(*c); }
+    else { find_cuts(*c); bin_ids(*c); }
     return c;
 }
 

@@ -28,7 +28,8 @@ class TgoParam(C.Structure):
                 ('num_class', C.c_int), ('lambda_', C.c_float), ('gamma', C.c_float), ('min_child_weight', C.c_float),
                 ('rt_eps', C.c_float), ('learning_rate', C.c_float), ('hist_mode', C.c_int), ('quant_bits', C.c_int),
                 ('n_threads', C.c_int), ('keep_nid', C.c_int), ('portable_exp', C.c_int), ('rank_seed', C.c_uint),
-                ('bagging', C.c_int), ('column_sampling_rate', C.c_float), ('sample_seed', C.c_uint)]
+                ('bagging', C.c_int), ('column_sampling_rate', C.c_float), ('sample_seed', C.c_uint),
+                ('multi_shards', C.c_int)]
 
 
 def build() -> str:
@@ -49,7 +50,7 @@ def lib():
         l.tgo_train.restype = vp
         l.tgo_train.argtypes = [C.c_int, vp, vp, vp, vp, vp, C.c_int, C.POINTER(TgoParam)]
         l.tgo_bin_only.restype = vp
-        l.tgo_bin_only.argtypes = [C.c_int, vp, vp, vp, C.c_int]
+        l.tgo_bin_only.argtypes = [C.c_int, vp, vp, vp, C.c_int, C.c_int]
         l.tgo_free.argtypes = [vp]
         for n in ('n_features', 'n_bins', 'num_class', 'trees_per_round', 'n_nodes', 'n_labels'):
             getattr(l, 'tgo_' + n).argtypes = [vp]
@@ -86,13 +87,14 @@ class Result:
 
 def train(data, objective='reg:linear', depth=6, n_trees=40, max_num_bin=255, learning_rate=1.0, gamma=1.0,
           min_child_weight=1.0, hist_mode=1, quant_bits=18, n_threads=0, keep_nid=0, portable_exp=1, rank_seed=0,
-          num_class=1, rt_eps=1e-6, tree_method='hist', bagging=0, column_sampling_rate=1.0, sample_seed=0, **kw):
+          num_class=1, rt_eps=1e-6, tree_method='hist', bagging=0, column_sampling_rate=1.0, sample_seed=0,
+          multi_shards=0, **kw):
     lam = kw.pop('lambda', kw.pop('lambda_', 1.0))
     assert not kw, kw
     l = lib()
     p = TgoParam(depth, n_trees, max_num_bin, OBJECTIVES[objective], num_class, lam, gamma, min_child_weight, rt_eps,
                  learning_rate, hist_mode, quant_bits, n_threads, keep_nid, portable_exp, rank_seed, int(bagging),
-                 column_sampling_rate, sample_seed)
+                 column_sampling_rate, sample_seed, multi_shards)
     rp = np.ascontiguousarray(data.row_ptr, np.int32); col = np.ascontiguousarray(data.col, np.int32)
     val = np.ascontiguousarray(data.val, np.float32); y = np.ascontiguousarray(data.y, np.float32)
     grp = np.ascontiguousarray(data.group, np.int32)
@@ -122,11 +124,11 @@ def train(data, objective='reg:linear', depth=6, n_trees=40, max_num_bin=255, le
     return r
 
 
-def bin_only(data, max_num_bin=255):
+def bin_only(data, max_num_bin=255, multi_shards=0):
     l = lib()
     rp = np.ascontiguousarray(data.row_ptr, np.int32); col = np.ascontiguousarray(data.col, np.int32)
     val = np.ascontiguousarray(data.val, np.float32)
-    h = l.tgo_bin_only(data.n_rows, _ptr(rp), _ptr(col), _ptr(val), max_num_bin)
+    h = l.tgo_bin_only(data.n_rows, _ptr(rp), _ptr(col), _ptr(val), max_num_bin, multi_shards)
     try:
         F, B = l.tgo_n_features(h), l.tgo_n_bins(h)
         return (_view(l.tgo_cut_val(h), (B,), np.float32), _view(l.tgo_cut_ptr(h), (F + 1,), np.int32),

@@ -15,6 +15,10 @@
 
     python tests/golden/pack_golden.py <run_dir> [--rerun <run_dir2> ...] [--out <dir>] [--shrink]
 
+A run made with n_device=D > 1 (the reference's column-sharded builder; run_reference.sh <out> n_device=2) is packed
+as ref_multi_<case>.npz with the same keys plus n_device: cut points of all features in feature order (they descend
+inside a feature there) and the global bin ids rebuilt from the devices' dense matrices.
+
 --shrink replaces <case>/csr_bin_id.i32 by its digest (bins_digest.npz) so that a large case can be
 carried off the GPU box; packing accepts either form.
 """
@@ -134,6 +138,28 @@ def bins_digest(g):
     return np.frombuffer(hashlib.sha256(bins.tobytes()).digest(), np.uint8), bins[:4096].copy(), bins.size
 
 
+def multi_device_dumps(g, d):
+    """Outputs of the reference's column-sharded builder (ref_harness with n_device = D > 1): per device its cut points
+    and its dense matrix of local bin ids.  Returns the cut points of all features, their offsets, D and the global
+    bin id of every stored value in CSR order -- the same form as the one-device dumps."""
+    vals, ptrs, dense = [], [], []
+    k = 0
+    while os.path.exists(os.path.join(g, f'cut_val_d{k}.f32')):
+        vals.append(np.fromfile(os.path.join(g, f'cut_val_d{k}.f32'), np.float32))
+        ptrs.append(np.fromfile(os.path.join(g, f'cut_row_ptr_d{k}.i32'), np.int32))
+        dense.append(np.fromfile(os.path.join(g, f'dense_bin_id_d{k}.u8'), np.uint8).reshape(d.n_rows, ptrs[-1].size - 1))
+        k += 1
+    cut_val = np.concatenate(vals)
+    sizes = np.concatenate([np.diff(p) for p in ptrs])
+    cut_ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int32)
+    local = np.concatenate(dense, axis=1)
+    rows = np.repeat(np.arange(d.n_rows), np.diff(d.row_ptr))
+    lb = local[rows, d.col]
+    assert lb.max() < 255 or (sizes.max() == 255 and (lb < 255).all()), 'a stored value without a bin'
+    bins = (cut_ptr[d.col] + lb).astype(np.int32)
+    return cut_val, cut_ptr, k, bins
+
+
 def main(argv):
     src, reruns, out, shrink = None, [], HERE, False
     i = 0
@@ -148,7 +174,32 @@ def main(argv):
     os.makedirs(out, exist_ok=True)
     for name in sorted(os.listdir(src)):
         g = os.path.join(src, name)
-        if name not in CASES or not os.path.exists(os.path.join(g, 'tgbm.model')) or not os.path.exists(os.path.join(g, 'cut_val.f32')):
+        if name not in CASES:
+            continue
+        if os.path.exists(os.path.join(g, 'cut_val_d0.f32')):  # a run of the column-sharded builder -> ref_multi_<case>.npz
+            d = CASES[name][0]()
+            cut_val, cut_ptr, n_dev, bins = multi_device_dumps(g, d)
+            keys = dict(cut_val=cut_val, cut_ptr=cut_ptr, n_device=n_dev, n_bin_ids=bins.size, bins_head=bins[:4096].copy(),
+                        bins_sha256=np.frombuffer(hashlib.sha256(bins.tobytes()).digest(), np.uint8))
+            if os.path.exists(os.path.join(g, 'tgbm.model')):
+                run = load_run(g, d.y)
+                m = run['model']
+                others = [load_run(os.path.join(r, name), d.y) for r in reruns if os.path.exists(os.path.join(r, name, 'tgbm.model'))]
+                raw = run['raw']
+                keys.update(spread(run, others) if others else dict(spread_runs=0))
+                keys.update(trees=m['trees'], base_score=np.float32(m['base_score']), label=m['label'], num_class=m['num_class'],
+                            learning_rate=np.float32(m['learning_rate']), metric=np.asarray(run['metric'], np.float32),
+                            raw_pred_sample=raw[::37], raw_pred_sha256=np.frombuffer(hashlib.sha256(raw.tobytes()).digest(), np.uint8),
+                            n_raw=raw.size, logloss=np.float64(run['logloss'] if run['logloss'] is not None else np.nan))
+                print('multi', name, 'devices', n_dev, 'bins', bins.size, 'trees', m['trees'].shape, 'metric', run['metric'][-1],
+                      {k: (float('%.3g' % v) if isinstance(v, float) else v) for k, v in keys.items() if k.startswith('spread')})
+            else:  # the reference's training aborted on this case; its cut points and bin ids were dumped before
+                print('multi', name, 'devices', n_dev, 'bins', bins.size, 'cut points and bin ids only')
+            np.savez_compressed(os.path.join(out, f'ref_multi_{name}.npz'), **keys)
+            continue
+        if not os.path.exists(os.path.join(g, 'tgbm.model')):
+            continue
+        if not os.path.exists(os.path.join(g, 'cut_val.f32')):
             continue
         if shrink and os.path.exists(os.path.join(g, 'csr_bin_id.i32')):
             sha, head, n = bins_digest(g)

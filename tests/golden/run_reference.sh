@@ -5,6 +5,8 @@
 # of further runs, for the reference's own run-to-run spread) into the committed fixtures.
 # usage: run_reference.sh <out_dir> [harness key=value ...]
 #   CASES="a b" restricts the cases; dump_bins=0 skips the cut-point / bin-id dumps (repeat runs).
+#   n_device=2 runs the reference's column-sharded builder on two GPUs: call once with the default dump_bins=1 (writes
+#   the devices' cut points and bin matrices, no training) and once with dump_bins=0 (trains) into the same <out_dir>.
 set -u
 ROOT=$(cd "$(dirname "$0")/../.." && pwd)
 IN=$ROOT/oracle/_ref/inputs

@@ -1,0 +1,151 @@
+"""The reference's column-sharded builder (HistTreeBuilder, what it runs for n_device = D > 1) as a mode of the CUDA
+path: `column_shards = D`.  Its cut points come from a float round trip of every value that depends on D and on the
+column's place on its device, bins count down from the largest values, the candidates' inclusive prefix sums are the
+right child, ties go to the larger value.  Checked through the C ABI
+
+* bit for bit against the CPU oracle's restatement of that builder (cut points, bin ids; trees, partition and scores in
+  the exact arithmetic), for several D and for data whose values reach below -1, where the reference's value shift
+  makes neighbouring columns trade candidates;
+* in the fp32 arithmetic against what the reference itself produced with n_device = 2 (tests/golden/ref_multi_*.npz):
+  cut points and bins bit for bit, trees and scores within float summation noise.
+"""
+import numpy as np
+import pytest
+
+from common import compare_with_noise, load_golden, sum_noise, within_noise
+
+pytestmark = pytest.mark.gpu
+
+CASES = ['fixture_reg', 'fixture_bin', 'c1_dense_reg', 'c2_higgs_small', 'c3_covtype_small', 'c5_mslr_small']
+
+
+def _booster(d, params, **extra):
+    from thundergbm_b200.booster import Booster
+    kw = {k: v for k, v in params.items() if k != 'tree_method'}
+    kw.update(extra)
+    return Booster(d, **kw)
+
+
+def _wide_negative(n=6000, f=11, seed=5):
+    """values in (-6, 6), a few columns much wider than the others, some values repeated many times, gaps"""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((n, f)).astype(np.float32) * rng.uniform(0.2, 2.0, f).astype(np.float32)
+    x[:, 3] = np.round(x[:, 3] * 2) / 2            # few distinct values
+    x[:, 7] = np.abs(x[:, 7]) * 3                   # the widest column sits in the middle of the second device
+    x[rng.random((n, f)) < 0.15] = np.nan           # absent entries
+    y = (np.nan_to_num(x[:, 0]) * 0.5 - np.nan_to_num(x[:, 7]) * 0.1 + rng.standard_normal(n) * 0.1).astype(np.float32)
+    mask = ~np.isnan(x)
+    rp = np.concatenate([[0], np.cumsum(mask.sum(1))]).astype(np.int32)
+    from thundergbm_b200.synth import CsrData
+    return CsrData(n, f, rp, np.nonzero(mask)[1].astype(np.int32), x[mask].astype(np.float32), y, np.zeros(0, np.int32))
+
+
+@pytest.mark.parametrize('name', CASES)
+@pytest.mark.parametrize('shards', [2, 3])
+def test_cuts_and_bins_bit_exact_with_oracle(gpu, orc, cases, name, shards):
+    d, params = cases(name)
+    b = _booster(d, params, column_shards=shards)
+    cut_val, cut_ptr, bins = orc.bin_only(d, params['max_num_bin'], multi_shards=shards)
+    cv, cp = b.cuts()
+    assert np.array_equal(cp, cut_ptr)
+    assert cv.tobytes() == cut_val.tobytes()
+    assert not b.info.csr_layout
+    assert np.array_equal(b.bins(), orc.bins_to_dense(d, bins, cut_ptr, b.info.fpad))
+    b.close()
+
+
+@pytest.mark.parametrize('shards', [1, 2, 4])
+@pytest.mark.parametrize('max_num_bin', [255, 16])
+def test_values_below_minus_one(gpu, orc, shards, max_num_bin):
+    d = _wide_negative()
+    b = _booster(d, dict(objective='reg:linear', depth=5, n_trees=4, max_num_bin=max_num_bin), column_shards=shards, hist_mode='exact',
+                 keep_nid=1)
+    cut_val, cut_ptr, bins = orc.bin_only(d, max_num_bin, multi_shards=shards)
+    cv, cp = b.cuts()
+    assert np.array_equal(cp, cut_ptr) and cv.tobytes() == cut_val.tobytes()
+    assert np.array_equal(b.bins(), orc.bins_to_dense(d, bins, cut_ptr, b.info.fpad))
+    o = orc.train(d, 'reg:linear', depth=5, n_trees=4, max_num_bin=max_num_bin, hist_mode=1, keep_nid=1, multi_shards=shards)
+    b.boost(4)
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid)
+    b.close()
+
+
+@pytest.mark.parametrize('name', CASES)
+def test_training_bit_exact_with_oracle(gpu, orc, cases, name):
+    d, params = cases(name)
+    p = {**params, 'n_trees': min(params['n_trees'], 10)}
+    o = orc.train(d, hist_mode=1, keep_nid=1, multi_shards=2, **p)
+    b = _booster(d, p, keep_nid=1, hist_mode='exact', column_shards=2)
+    b.boost(p['n_trees'])
+    trees = b.trees()
+    for r in range(trees.shape[0]):
+        for k in range(trees.shape[1]):
+            assert trees[r, k].tobytes() == o.trees[r, k].tobytes(), f'tree {r}/{k} differs'
+    assert np.array_equal(b.nid(), o.nid)
+    assert np.array_equal(b.ypred(), o.ypred)
+    assert np.array_equal(b.metrics(), o.metric)
+    b.close()
+
+
+def test_csr_layout(gpu, orc, cases, monkeypatch):
+    monkeypatch.setenv('TGBM_LAYOUT', 'sparse')
+    d, params = cases('c3_covtype_small')
+    o = orc.train(d, hist_mode=1, keep_nid=1, multi_shards=2, **params)
+    b = _booster(d, params, keep_nid=1, hist_mode='exact', column_shards=2)
+    assert b.info.csr_layout == 1
+    b.boost(params['n_trees'])
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid)
+    assert np.array_equal(b.bins_csr(d.nnz), orc.bin_only(d, params['max_num_bin'], multi_shards=2)[2])
+    b.close()
+
+
+GOLDEN = ['fixture_reg', 'fixture_bin', 'c1_dense_reg', 'c2_higgs_small', 'c3_covtype_small']
+
+
+@pytest.mark.parametrize('name', GOLDEN)
+def test_cuts_and_bins_bit_exact_with_the_reference(gpu, cases, name):
+    """Cut points and bin ids against what the reference's two devices computed."""
+    import hashlib
+    g = load_golden('multi_' + name)
+    d, params = cases(name)
+    b = _booster(d, params, column_shards=int(g['n_device']))
+    cv, cp = b.cuts()
+    assert np.array_equal(cp, g['cut_ptr']) and cv.tobytes() == g['cut_val'].tobytes()
+    dense = b.bins()
+    rows = np.repeat(np.arange(d.n_rows), np.diff(d.row_ptr))
+    bins = (cp[d.col] + dense[rows, d.col]).astype(np.int32)
+    assert np.array_equal(bins[:4096], g['bins_head'])
+    assert hashlib.sha256(bins.tobytes()).digest() == g['bins_sha256'].tobytes()
+    b.close()
+
+
+@pytest.mark.parametrize('name', GOLDEN)
+def test_fp32_follows_the_reference_on_two_devices(gpu, orc, cases, name):
+    """fp32 arithmetic + column_shards = 2 against the reference run with n_device = 2 (same tolerances as the
+    one-device comparison in test_gpu_fp32.py)."""
+    from pack_golden import logloss
+    g = load_golden('multi_' + name)
+    d, params = cases(name)
+    b = _booster(d, params, hist_mode='fp32', column_shards=2)
+    assert abs(b.info.base_score - float(g['base_score'])) <= 1e-6 * max(1.0, abs(float(g['base_score'])))
+    b.boost(params['n_trees'])
+    m = b.metrics()
+    tol_m = max(1e-4, 2 * float(g['spread_metric']))
+    assert np.max(np.abs(m - g['metric'])) <= tol_m, (np.max(np.abs(m - g['metric'])), tol_m)
+    ll = logloss(params['objective'], b.ypred(), d.y, g['label'])
+    if ll is not None:
+        assert abs(ll - float(g['logloss'])) <= max(1e-4, 2 * float(g['spread_logloss']))
+    labels = g['label']
+    classes = max(1, labels.size)
+    k = classes if classes > 2 else 1
+    y = np.searchsorted(labels, d.y).astype(np.float32) if labels.size else d.y
+    yp = np.full(k * d.n_rows, float(g['base_score']) if k == 1 else 0.0, np.float32)
+    gh = orc.gradient(y, yp, params['objective'], K=k)
+    bins = orc.bin_only(d, params['max_num_bin'], multi_shards=2)[2]
+    dG, dH = sum_noise(gh[:d.n_rows], int(np.bincount(bins).max()))
+    r = compare_with_noise(g['trees'][0, 0], b.trees()[0, 0], dG, dH, lam=params['lambda'])
+    r.pop('parted')
+    assert r['compared'] >= 1 and within_noise(r), (name, r['worst_gain'], r['worst_weight'], r['bad_gain'], r['bad_weight'])
+    b.close()

@@ -71,7 +71,6 @@ struct BoosterImpl {
     DevBuf<int> bag_count;                 // bagging: multiplicity of every gradient entry in the round's bootstrap sample
     DevBuf<unsigned char> ignored_all;     // column sampling: [round][feature] mask of the features left out
     int f32_stride(int pairs) const {
-        if (comm && comm->active()) return 1;  // the built histograms are all-reduced: keep them compact
         return pairs <= 2 ? 8 : pairs <= 8 ? 4 : pairs <= 16 ? 2 : 1;
     }
     DevBuf<int> built_right, hist_tile_base;
@@ -123,6 +122,7 @@ struct BoosterImpl {
     // ---------------------------------------------------------------- init helpers
     void upload_csr(const DataSet &ds);
     void find_cuts_and_bins(const DataSet &ds);
+    void column_builder_candidates(DevBuf<unsigned long long> &ukeys, DevBuf<long long> &ucopies, long long &nu);
     void init_base_score();
     void gradient(int round);
     void build_tree(int round, int k);
@@ -164,6 +164,100 @@ void BoosterImpl::upload_csr(const DataSet &ds) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Cut-point candidates of the reference's column-sharded builder (HistCut::get_cut_points3 + unique_by_flag,
+// src/thundergbm/hist_cut.cu:104-187, run by each of its `column_shards` devices on the columns
+// SparseColumns::csr2csc_gpu gives it, src/thundergbm/sparse_columns.cu:95-102).  In: the distinct (feature, value)
+// keys in ascending order with their multiplicities.  Out: per feature the candidates, largest first, as keys
+// (feature, complement of the value's ordered image), from which the usual stride selection picks the cut points.
+void BoosterImpl::column_builder_candidates(DevBuf<unsigned long long> &ukeys, DevBuf<long long> &ucopies, long long &nu) {
+    if (nu == 0) return;
+    const int D = p.column_shards;
+    const int grid = std::min(ceil_div(nu, 256), num_sms * 16);
+    // copies before every key, per feature the largest value and the copies before its first key
+    DevBuf<long long> before, ustart, fbefore;
+    DevBuf<float> fmax;
+    before.alloc(nu + 1); ustart.alloc(F + 1); fbefore.alloc(F + 1); fmax.alloc(F);
+    TGBM_CUDA(cudaMemsetAsync(ucopies.p + nu, 0, sizeof(long long), stream));
+    auto scan = [&](const long long *in, long long *out, long long n) {
+        size_t tb = 0;
+        cub::DeviceScan::ExclusiveSum(nullptr, tb, in, out, n, stream);
+        DevBuf<unsigned char> tmp;
+        tmp.alloc(std::max<size_t>(tb, 1));
+        cub::DeviceScan::ExclusiveSum(tmp.p, tb, in, out, n, stream);
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+    };
+    scan(ucopies.p, before.p, nu + 1);
+    long long total = 0;
+    TGBM_CUDA(cudaMemcpyAsync(&total, before.p + nu, sizeof(long long), cudaMemcpyDeviceToHost, stream));
+    k_feature_bounds<<<ceil_div(F + 1, 128), 128, 0, stream>>>(ukeys.p, nu, F, ustart.p);
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+    k_feature_max_before<<<ceil_div(F + 1, 128), 128, 0, stream>>>(ukeys.p, ustart.p, before.p, nu, total, F, fmax.p, fbefore.p);
+    std::vector<float> h_fmax(F);
+    std::vector<long long> h_fbefore(F + 1);
+    TGBM_CUDA(cudaMemcpyAsync(h_fmax.data(), fmax.p, sizeof(float) * F, cudaMemcpyDeviceToHost, stream));
+    TGBM_CUDA(cudaMemcpyAsync(h_fbefore.data(), fbefore.p, sizeof(long long) * (F + 1), cudaMemcpyDeviceToHost, stream));
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+    std::vector<ColumnShift> h_cs(F);
+    std::vector<int> h_first(D), h_cols(D);
+    std::vector<long long> h_sbefore(D);
+    const int ave = F / D;
+    for (int d = 0; d < D; ++d) {
+        const int first = d * ave, ncol = d < D - 1 ? ave : F - first;
+        h_first[d] = first; h_cols[d] = ncol; h_sbefore[d] = h_fbefore[first];
+        float m = -INFINITY;
+        for (int f = first; f < first + ncol; ++f) m = std::max(m, h_fmax[f]);
+        // hist_cut.cu:109: the reference gives up when the shifted values leave the int range
+        TGBM_CHECK(!(ncol > 0 && m > -INFINITY) || (double)m + (double)ncol * ((double)m + 1) < 2147483647.0,
+                   "feature values too large for the column-sharded builder's value shift");
+        for (int f = first; f < first + ncol; ++f)
+            h_cs[f] = ColumnShift{d, first, m + 1.0f, h_fbefore[first + ncol] - h_fbefore[f + 1]};
+    }
+    DevBuf<ColumnShift> cs;
+    DevBuf<int> shard_first, shard_cols;
+    DevBuf<long long> shard_before;
+    cs.alloc(F); shard_first.alloc(D); shard_cols.alloc(D); shard_before.alloc(D);
+    TGBM_CUDA(cudaMemcpyAsync(cs.p, h_cs.data(), sizeof(ColumnShift) * F, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(shard_first.p, h_first.data(), sizeof(int) * D, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(shard_cols.p, h_cols.data(), sizeof(int) * D, cudaMemcpyHostToDevice, stream));
+    TGBM_CUDA(cudaMemcpyAsync(shard_before.p, h_sbefore.data(), sizeof(long long) * D, cudaMemcpyHostToDevice, stream));
+    // shift, sort per device (descending t), copies before every entry of the sorted array
+    DevBuf<unsigned long long> k1, k2;
+    DevBuf<long long> c2;
+    k1.alloc(nu); k2.alloc(nu); c2.alloc(nu + 1);
+    k_shift_keys<<<grid, 256, 0, stream>>>(ukeys.p, nu, cs.p, k1.p);
+    {
+        int end_bit = 32;
+        while ((1ll << (end_bit - 32)) < D && end_bit < 64) ++end_bit;
+        size_t tb = 0;
+        cub::DeviceRadixSort::SortPairs(nullptr, tb, k1.p, k2.p, ucopies.p, c2.p, nu, 0, end_bit, stream);
+        DevBuf<unsigned char> tmp;
+        tmp.alloc(std::max<size_t>(tb, 1));
+        cub::DeviceRadixSort::SortPairs(tmp.p, tb, k1.p, k2.p, ucopies.p, c2.p, nu, 0, end_bit, stream);
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+    }
+    scan(c2.p, before.p, nu);
+    DevBuf<unsigned long long> n_heads;
+    n_heads.alloc(1);
+    n_heads.zero(stream);
+    k_unshift_keys<<<grid, 256, 0, stream>>>(k2.p, before.p, nu, cs.p, shard_first.p, shard_cols.p, shard_before.p,
+                                             k1.p, n_heads.p);
+    unsigned long long h_heads = 0;
+    TGBM_CUDA(cudaMemcpyAsync(&h_heads, n_heads.p, sizeof(h_heads), cudaMemcpyDeviceToHost, stream));
+    {
+        size_t tb = 0;
+        cub::DeviceRadixSort::SortKeys(nullptr, tb, k1.p, k2.p, nu, 0, 64, stream);
+        DevBuf<unsigned char> tmp;
+        tmp.alloc(std::max<size_t>(tb, 1));
+        cub::DeviceRadixSort::SortKeys(tmp.p, tb, k1.p, k2.p, nu, 0, 64, stream);
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+    }
+    nu = (long long)h_heads;
+    ukeys.alloc(std::max<long long>(nu, 1));
+    if (nu) TGBM_CUDA(cudaMemcpyAsync(ukeys.p, k2.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+}
+
+// ------------------------------------------------------------------------------------------------
 // Cut points (HistCut::get_cut_points_single, src/thundergbm/hist_cut.cu:205-286) and the bin matrix.
 // Radix sort of (feature, value) keys and DeviceSelect::Unique come from CUB; this runs once, before
 // the boosting loop.  With several ranks every rank contributes its distinct keys and all ranks
@@ -188,12 +282,16 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         if (multi) comm->agree(local_err, what, stream);
         else if (!local_err.empty()) throw Error(local_err);
     };
+    const bool colb = p.column_shards > 0;   // the column-sharded builder's cut points need the multiplicity of every key
+    DevBuf<long long> ucopies;
     {
         DevBuf<unsigned long long> keys, keys2;
+        DevBuf<long long> copies, copies2;
         DevBuf<long long> d_nu;
         DevBuf<long long> counts, mine;
         try {
             keys.alloc(std::max<size_t>(nnz, 1)); keys2.alloc(std::max<size_t>(nnz, 1)); d_nu.alloc(1);
+            if (colb) { copies.alloc(std::max<size_t>(nnz, 1)); copies2.alloc(std::max<size_t>(nnz, 1)); }
             if (multi) { counts.alloc(comm->world); mine.alloc(1); }
         } catch (const std::exception &e) { local_err = e.what(); }
         auto sort_unique = [&](size_t n) -> long long {  // keys -> keys (sorted distinct), returns the count
@@ -201,6 +299,21 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             size_t tb = 0;
             int end_bit = 32;
             while ((1ll << (end_bit - 32)) < F && end_bit < 64) ++end_bit;
+            if (colb) {  // ... and copies -> copies (summed over equal keys)
+                cub::DeviceRadixSort::SortPairs(nullptr, tb, keys.p, keys2.p, copies.p, copies2.p, (long long)n, 0, end_bit, stream);
+                DevBuf<unsigned char> tmp;
+                tmp.alloc(tb);
+                cub::DeviceRadixSort::SortPairs(tmp.p, tb, keys.p, keys2.p, copies.p, copies2.p, (long long)n, 0, end_bit, stream);
+                size_t tb2 = 0;
+                cub::DeviceReduce::ReduceByKey(nullptr, tb2, keys2.p, keys.p, copies2.p, copies.p, d_nu.p, cub::Sum(), (long long)n, stream);
+                DevBuf<unsigned char> tmp2;
+                tmp2.alloc(tb2);
+                cub::DeviceReduce::ReduceByKey(tmp2.p, tb2, keys2.p, keys.p, copies2.p, copies.p, d_nu.p, cub::Sum(), (long long)n, stream);
+                long long r = 0;
+                TGBM_CUDA(cudaMemcpyAsync(&r, d_nu.p, sizeof(long long), cudaMemcpyDeviceToHost, stream));
+                TGBM_CUDA(cudaStreamSynchronize(stream));
+                return r;
+            }
             cub::DeviceRadixSort::SortKeys(nullptr, tb, keys.p, keys2.p, (long long)n, 0, end_bit, stream);
             DevBuf<unsigned char> tmp;
             tmp.alloc(tb);
@@ -218,6 +331,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         if (local_err.empty()) {
             try {
                 if (nnz) k_make_keys<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_val.p, d_col.p, nnz, keys.p);
+                if (nnz && colb) k_fill_ll<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(copies.p, nnz, 1);
                 nu = sort_unique(nnz);
             } catch (const std::exception &e) { local_err = e.what(); }
         }
@@ -231,25 +345,41 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             comm->wait(stream);
             const long long mx = std::max<long long>(1, *std::max_element(hc.begin(), hc.end()));
             DevBuf<unsigned long long> padded, all;
-            try { padded.alloc(mx); all.alloc((size_t)mx * comm->world); } catch (const std::exception &e) { local_err = e.what(); }
+            DevBuf<long long> padded_c, all_c;
+            try {
+                padded.alloc(mx); all.alloc((size_t)mx * comm->world);
+                if (colb) { padded_c.alloc(mx); all_c.alloc((size_t)mx * comm->world); }
+            } catch (const std::exception &e) { local_err = e.what(); }
             agree("making room for the ranks' feature values");
             TGBM_CUDA(cudaMemsetAsync(padded.p, 0xff, sizeof(unsigned long long) * mx, stream));
             if (nu) TGBM_CUDA(cudaMemcpyAsync(padded.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
             comm->allgather(padded.p, all.p, mx, Comm::I64, stream);
+            if (colb) {
+                TGBM_CUDA(cudaMemsetAsync(padded_c.p, 0, sizeof(long long) * mx, stream));
+                if (nu) TGBM_CUDA(cudaMemcpyAsync(padded_c.p, copies.p, sizeof(long long) * nu, cudaMemcpyDeviceToDevice, stream));
+                comm->allgather(padded_c.p, all_c.p, mx, Comm::I64, stream);
+            }
             long long tot = 0;
             for (long long c : hc) tot += c;
             keys.alloc(std::max<long long>(tot, 1)); keys2.alloc(std::max<long long>(tot, 1));
+            if (colb) { copies.alloc(std::max<long long>(tot, 1)); copies2.alloc(std::max<long long>(tot, 1)); }
             long long o = 0;
             for (int r = 0; r < comm->world; ++r) {
                 if (hc[r]) TGBM_CUDA(cudaMemcpyAsync(keys.p + o, all.p + (size_t)r * mx, sizeof(unsigned long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
+                if (hc[r] && colb) TGBM_CUDA(cudaMemcpyAsync(copies.p + o, all_c.p + (size_t)r * mx, sizeof(long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
                 o += hc[r];
             }
             nu = sort_unique(tot);
         }
         ukeys.alloc(std::max<long long>(nu, 1));
         if (nu) TGBM_CUDA(cudaMemcpyAsync(ukeys.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
+        if (colb) {
+            ucopies.alloc(std::max<long long>(nu, 1) + 1);
+            if (nu) TGBM_CUDA(cudaMemcpyAsync(ucopies.p, copies.p, sizeof(long long) * nu, cudaMemcpyDeviceToDevice, stream));
+        }
         TGBM_CUDA(cudaStreamSynchronize(stream));
     }
+    if (colb) column_builder_candidates(ukeys, ucopies, nu);
     lap("sort + unique of the keys");
     // distinct values per feature -> stride and number of cut points per feature (host, F+1 numbers)
     DevBuf<long long> ustart;
@@ -273,7 +403,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     TGBM_CUDA(cudaMemcpyAsync(d_stride.p, h_stride.data(), sizeof(int) * F, cudaMemcpyHostToDevice, stream));
     TGBM_CUDA(cudaMemcpyAsync(cut_ptr.p, h_cut_ptr.data(), sizeof(int) * (F + 1), cudaMemcpyHostToDevice, stream));
     if (nu) k_select_cuts<<<std::min(ceil_div(nu, 256), num_sms * 16), 256, 0, stream>>>(ukeys.p, nu, ustart.p, d_stride.p, cut_ptr.p,
-                                                                                         p.max_num_bin, cut_val.p, cut_fid.p);
+                                                                                         p.max_num_bin, cut_val.p, cut_fid.p, colb ? 1 : 0);
     h_cut_val.resize(B);
     TGBM_CUDA(cudaMemcpyAsync(h_cut_val.data(), cut_val.p, sizeof(float) * B, cudaMemcpyDeviceToHost, stream));
 
@@ -294,7 +424,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         sp_row_ptr.alloc(N + 1);
         sp_bin.alloc(std::max<size_t>(nnz, 1));
         TGBM_CUDA(cudaMemcpyAsync(sp_row_ptr.p, d_row_ptr.p, sizeof(int) * (N + 1), cudaMemcpyDeviceToDevice, stream));
-        if (nnz) k_bin_csr<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_col.p, d_val.p, nnz, cut_ptr.p, cut_val.p, sp_bin.p);
+        if (nnz) k_bin_csr<<<std::min(ceil_div(nnz, 256), num_sms * 16), 256, 0, stream>>>(d_col.p, d_val.p, nnz, cut_ptr.p, cut_val.p, sp_bin.p, colb ? 1 : 0);
         // rows whose columns arrive unordered are put in ascending bin order (= ascending column order)
         if (nnz) {
             DevBuf<int> unsorted;
@@ -336,7 +466,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         binsT.alloc((size_t)F * Npad);
         TGBM_CUDA(cudaMemsetAsync(bins.p, MISSING_BIN, bins.bytes(), stream));
         TGBM_CUDA(cudaMemsetAsync(binsT.p, MISSING_BIN, binsT.bytes(), stream));
-        if (N) k_bin_dense<<<ceil_div(N, 128), 128, 0, stream>>>(d_row_ptr.p, d_col.p, d_val.p, N, cut_ptr.p, cut_val.p, Fpad, Npad, bins.p, binsT.p);
+        if (N) k_bin_dense<<<ceil_div(N, 128), 128, 0, stream>>>(d_row_ptr.p, d_col.p, d_val.p, N, cut_ptr.p, cut_val.p, Fpad, Npad, bins.p, binsT.p, colb ? 1 : 0);
     }
     TGBM_CUDA(cudaStreamSynchronize(stream));
     TGBM_CUDA(cudaGetLastError());
@@ -645,6 +775,7 @@ void BoosterImpl::build_tree(int round, int k) {
                                         seg_begin[1].p, seg_cnt[1].p, part_group.p, (int)part_group.n);
     launches += 2;
     const int by_hessian = (comm && comm->active()) ? 1 : 0;
+    const int colb = p.column_shards > 0 ? 1 : 0;  // candidates, tie rule and child sums of the column-sharded builder
     const int part_ctas = std::max(1, std::min(max_tiles, num_sms * (2048 / PART_THREADS)));
     for (int level = 0; level < depth; ++level) {
         const int cur = level & 1, nxt = cur ^ 1;
@@ -695,9 +826,18 @@ void BoosterImpl::build_tree(int round, int k) {
             k_hist<true><<<dim3(hist_ctas, G), HIST_THREADS, hist_smem, stream>>>(bins.p, Fpad, F, idx_in, gh_in, hist_cta_off.p, hist_seq.p,
                                                                                   cut_ptr.p, cut_fid.p, built, B, window_rows);
         if (profile_on) { cudaEventRecord(ev.b, stream); events.push_back(ev); }
+        int bs_eval = bs;   // distance of the cells the split search reads
         if (comm && comm->active()) {
-            if (f32) comm->allreduce(built_f, 2 * (size_t)B * pairs, Comm::F32, Comm::SUM, stream);
-            else comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
+            if (f32) {
+                // the ranks' sums meet in a compact buffer: spread cells are gathered first (a pass over B x pairs cells)
+                float2 *compact = reinterpret_cast<float2 *>(built);
+                if (bs != 1) {
+                    const size_t cells = (size_t)B * pairs;
+                    k_compact_cells<<<std::min(ceil_div(cells, 256), num_sms * 8), 256, 0, stream>>>(built_f, compact, cells, bs);
+                    built_f = compact; bs_eval = 1; ++launches;
+                }
+                comm->allreduce(built_f, 2 * (size_t)B * pairs, Comm::F32, Comm::SUM, stream);
+            } else comm->allreduce(built, 2 * (size_t)B * pairs, Comm::I64, Comm::SUM, stream);
         }
         // -- split selection and tree update
         if (f32) {
@@ -706,24 +846,24 @@ void BoosterImpl::build_tree(int round, int k) {
             const float *bf = reinterpret_cast<const float *>(built_f);
             if (sparse) {
                 k_eval_chunk<float><<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
-                                                                              bf, parent_f, full_f, qinfo.p, p.min_child_weight, p.lambda, recs.p, bs, ignored_all.p, rstate.p, F);
-                k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
+                                                                              bf, parent_f, full_f, qinfo.p, p.min_child_weight, p.lambda, recs.p, bs_eval, ignored_all.p, rstate.p, F, colb);
+                k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1, colb);
             } else {
                 k_eval<float><<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, bf, parent_f, full_f, qinfo.p,
-                                                                 p.min_child_weight, p.lambda, recs.p, cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, bs,
-                                                                 ignored_all.p, rstate.p);
+                                                                 p.min_child_weight, p.lambda, recs.p, cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, bs_eval,
+                                                                 ignored_all.p, rstate.p, colb);
             }
         } else {
         const long long *parent_hist = level == 0 ? nullptr : hist_full.p + full_offset(level - 1);
         if (sparse) {
             k_eval_chunk<long long><<<dim3(n_chunks, pairs), 64, 0, stream>>>(level, n_chunks, B, chunk_bin0.p, cut_ptr.p, cut_fid.p, nodes.p, built_right.p,
                                                                    built, parent_hist, hist_full.p + full_offset(level), qinfo.p,
-                                                                   p.min_child_weight, p.lambda, recs.p, 1, ignored_all.p, rstate.p, F);
-            k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1);
+                                                                   p.min_child_weight, p.lambda, recs.p, 1, ignored_all.p, rstate.p, F, colb);
+            k_best_apply<<<nl, 32, 0, stream>>>(level, n_chunks, cut_ptr.p, cut_val.p, recs.p, nodes.p, p.rt_eps, p.lambda, cut_fid.p, 1, colb);
         } else {
             k_eval<long long><<<dim3(F, pairs), 64, 0, stream>>>(level, F, B, cut_ptr.p, nodes.p, built_right.p, built, parent_hist,
                                                       hist_full.p + full_offset(level), qinfo.p, p.min_child_weight, p.lambda, recs.p,
-                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, 1, ignored_all.p, rstate.p);
+                                                      cut_val.p, p.rt_eps, cut_fid.p, eval_ticket.p, 1, ignored_all.p, rstate.p, colb);
         }
         }
         // -- move the rows (not after the last level: the finished tree is applied by walking it, see k_predict_walk)
@@ -737,11 +877,11 @@ void BoosterImpl::build_tree(int round, int k) {
             if (sparse)
                 k_part_one<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, tile_node[cur].p,
                                                                          part_base.p, ctl.p, idx_in, gh_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p,
-                                                                         part_status.p, part_group.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
+                                                                         part_status.p, part_group.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1, colb);
             else
                 k_part_one<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, tile_node[cur].p,
                                                                           part_base.p, ctl.p, idx_in, gh_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p,
-                                                                          part_status.p, part_group.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1);
+                                                                          part_status.p, part_group.p, seg_begin[nxt].p, seg_cnt[nxt].p, rec_idx[nxt].p, rec_gh[nxt].p, n1, colb);
             k_plan_next<<<1, 1024, 0, stream>>>(level, seg_begin[nxt].p, seg_cnt[nxt].p, seg_cnt[nxt].p, nodes.p, ctl.p, by_hessian, built_right.p,
                                                 hist_work.p, hist_tile_base.p, node_tile0[nxt].p, hist_ctas, hist_cta_off.p, hist_seq.p, depth, tile_node[nxt].p,
                                                 part_base.p, seg_begin[cur].p, seg_cnt[cur].p, part_group.p, (int)part_group.n);
@@ -751,10 +891,10 @@ void BoosterImpl::build_tree(int round, int k) {
         }
         if (sparse)
             k_part_count<true><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                                       idx_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p);
+                                                                       idx_in, nullptr, Npad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p, colb);
         else
             k_part_count<false><<<part_ctas, PART_THREADS, 0, stream>>>(level, nodes.p, seg_begin[cur].p, seg_cnt[cur].p, node_tile0[cur].p, ctl.p,
-                                                                        idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p);
+                                                                        idx_in, binsT.p, Npad, nullptr, nullptr, cut_ptr.p, bits.p, tile_left.p, tile_node[cur].p, colb);
         k_part_scan<<<1, 1024, 0, stream>>>(level, nodes.p, seg_cnt[cur].p, node_tile0[cur].p, tile_left.p,
                                             seg_begin[nxt].p, seg_cnt[nxt].p, gcnt.p, ctl.p);
         // the next level's plan runs beside the scatter: launched first so that it gets its SM slot, while the
@@ -787,13 +927,13 @@ void BoosterImpl::build_tree(int round, int k) {
         if (fuse) maxbits.zero(stream);
         if (sparse)
             k_predict_walk<2><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, nullptr, Fpad, sp_row_ptr.p, sp_bin.p, cut_ptr.p, N,
-                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p);
+                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p, colb);
         else if (Fpad == 32)
             k_predict_walk<0><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
-                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p);
+                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p, colb);
         else
             k_predict_walk<1><<<walk_ctas, 256, walk_smem, stream>>>(nodes.p, n_nodes, in_smem, bins.p, Fpad, nullptr, nullptr, cut_ptr.p, N,
-                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p);
+                                                                     p.learning_rate, yp, nid_out, y.p, fo, metric_partial.p, maxbits.p, colb);
         grad_max_ready = metric_partial_ready = fuse;
     }
     launches += 2;

@@ -214,6 +214,7 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
     p.quant_bits = cp->quant_bits; p.keep_nid = cp->keep_nid; p.verbose = cp->verbose; p.rank_seed = cp->rank_seed;
     p.hist_mode = cp->hist_mode;
     p.bagging = cp->bagging != 0; p.column_sampling_rate = cp->column_sampling_rate; p.sample_seed = cp->sample_seed;
+    p.column_shards = cp->column_shards;
     p.tree_method = "hist";
     return p;
 }
@@ -222,6 +223,9 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
 namespace tgbm {
 std::vector<std::vector<Tree>> train_model(GBMParam &p, const DataSet &ds) {
     TGBM_CHECK(p.n_device >= 1, "n_device must be at least 1");
+    // TGBM_COLUMN_BUILDER=1: n_device = D > 1 also selects what the reference's D-device builder computes
+    if (const char *e = getenv("TGBM_COLUMN_BUILDER"))
+        if (*e && strcmp(e, "0") && p.n_device > 1 && p.column_shards == 0) p.column_shards = p.n_device;
     return p.n_device > 1 ? train_in_process(p, ds, p.n_device) : train(p, ds, nullptr);
 }
 void set_last_error(const std::string &msg) { g_err = msg; }
@@ -400,7 +404,7 @@ void tgbm_default_param(TgbmParam *p) {
     p->min_child_weight = d.min_child_weight; p->lambda = d.lambda; p->gamma = d.gamma; p->learning_rate = d.learning_rate;
     p->objective = "reg:linear"; p->quant_bits = d.quant_bits; p->keep_nid = 0; p->verbose = 0; p->profile = 0; p->rank_seed = 0;
     p->hist_mode = tgbm::default_hist_mode();
-    p->bagging = 0; p->column_sampling_rate = 1.f; p->sample_seed = 0;
+    p->bagging = 0; p->column_sampling_rate = 1.f; p->sample_seed = 0; p->column_shards = 0;
 }
 
 int tgbm_comm_unique_id(unsigned char id[128]) { return guard([&] { tgbm::comm_get_unique_id(id); }); }

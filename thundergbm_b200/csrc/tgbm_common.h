@@ -82,6 +82,11 @@ struct GBMParam {
     // the additions in the last bits.  1 "exact": gradients on a power-of-two grid, integer sums -- the deterministic
     // mode: bit-identical from run to run and for any number of GPUs.
     int hist_mode = 0;
+    // 0: cut points, candidate order and child sums of the one-device builder (HistTreeBuilder_single, what the
+    // reference runs for n_device = 1).  D >= 1: those of the column-sharded HistTreeBuilder the reference runs for
+    // n_device = D > 1 -- its cut points depend on D (each device shifts and re-rounds the values of its own block
+    // of columns, hist_cut.cu:104-134).  The rows are still sharded over this implementation's own GPUs.
+    int column_shards = 0;
     int quant_bits = 18;        // exact mode: value bits of the fixed-point gradient grid
     unsigned sample_seed = 0;   // bagging and column sampling (the reference draws from std::rand())
     unsigned rank_seed = 0;     // LambdaRank partner sampling

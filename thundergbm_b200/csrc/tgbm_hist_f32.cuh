@@ -192,6 +192,12 @@ k_sum_gh(const float2 *__restrict__ gh, int n, double *__restrict__ partial) {
         partial[((size_t)k * gridDim.x + blockIdx.x) * 2 + 1] = th;
     }
 }
+// spread cells (`stride` float2 apart) -> consecutive cells: what the ranks all-reduce
+static __global__ void k_compact_cells(const float2 *__restrict__ spread, float2 *__restrict__ compact, size_t cells, int stride) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < cells; i += (size_t)gridDim.x * blockDim.x)
+        compact[i] = spread[i * (size_t)stride];
+}
+
 static __global__ void k_sum_gh_final(const double *__restrict__ partial, int nb, double *__restrict__ out) {
     const int k = blockIdx.x;
     double tg = 0, th = 0;

@@ -293,6 +293,7 @@ void parse_param(GBMParam &mp, int argc, char **argv) {
         else if (k == "tree_method") mp.tree_method = val;
         else if (k == "quant_bits") mp.quant_bits = atoi(val);
         else if (k == "hist_mode") mp.hist_mode = hist_mode_from_name(val);
+        else if (k == "column_shards") mp.column_shards = atoi(val);
         else if (k == "seed" || k == "sample_seed") mp.sample_seed = (unsigned)strtoul(val, nullptr, 10);
         else log_info("\"%s\" is unknown option!", name);
     };

@@ -94,7 +94,9 @@ static __global__ void k_feature_bounds(const unsigned long long *__restrict__ u
 // s == 0 keeps every distinct value, else positions 0, s, ..., (max_bin-1) s
 static __global__ void k_select_cuts(const unsigned long long *__restrict__ ukeys, long long nu, const long long *__restrict__ ustart,
                               const int *__restrict__ stride, const int *__restrict__ cut_ptr, int max_bin,
-                              float *__restrict__ cut_val, int *__restrict__ cut_fid) {
+                              float *__restrict__ cut_val, int *__restrict__ cut_fid, int down) {
+    // down: the keys carry the complement of the float's ordered image (candidates of the column-sharded builder,
+    // largest value first)
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nu; i += (long long)gridDim.x * blockDim.x) {
         const unsigned long long k = ukeys[i];
         const int f = (int)(k >> 32);
@@ -104,16 +106,95 @@ static __global__ void k_select_cuts(const unsigned long long *__restrict__ ukey
         if (s == 0) pos = t;
         else if (t % s == 0 && t / s < max_bin) pos = t / s;
         else continue;
-        cut_val[cut_ptr[f] + pos] = key_to_float(k);
+        cut_val[cut_ptr[f] + pos] = key_to_float(down ? (k ^ 0xffffffffull) : k);
         cut_fid[cut_ptr[f] + pos] = f;
     }
+}
+
+// ------------------------------------------------------------------ cut points of the column-sharded builder
+// HistCut::get_cut_points3 + unique_by_flag (src/thundergbm/hist_cut.cu:104-187), which every device of the
+// reference runs on its own block of columns: each stored value v of local column j becomes t = v + j*(m+1), m the
+// largest value on the device; all t of the device are sorted descending; the column ids are laid over the sorted
+// array by COUNT, largest id first; runs of equal t keep their first entry; t goes back to t - j*(m+1) with the id
+// found there.  Done here on the distinct (feature, value) keys with their multiplicities: the position of a key's
+// first copy in the reference's sorted array is the number of copies before it.
+struct ColumnShift {            // per feature
+    int shard, first;           // device that owns it in the reference, first column of that device
+    float step;                 // m + 1 of that device
+    long long below;            // copies in the device's columns with a LARGER id: where this column's ids start
+};
+__device__ __forceinline__ unsigned float_order(float v) {
+    unsigned u = __float_as_uint(v);
+    if (u == 0x80000000u) u = 0;
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float order_float(unsigned u) {
+    u = (u & 0x80000000u) ? (u & 0x7fffffffu) : ~u;
+    return __uint_as_float(u);
+}
+// key (feature, value) -> (device, complement of the ordered image of t): ascending keys = descending t per device
+static __global__ void k_shift_keys(const unsigned long long *__restrict__ ukeys, long long nu, const ColumnShift *__restrict__ cs,
+                                    unsigned long long *__restrict__ out) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nu; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long k = ukeys[i];
+        const int f = (int)(k >> 32);
+        const ColumnShift c = cs[f];
+        const float v = key_to_float(k), j = (float)(f - c.first);
+        const float t = __fmaf_rn(j, c.step, v);  // one rounding: what nvcc makes of the reference's `v + j * step`
+        out[i] = ((unsigned long long)(unsigned)c.shard << 32) | (unsigned)~float_order(t);
+    }
+}
+// sorted shifted keys + the number of copies before each -> candidate keys (feature, complement of the ordered image of
+// the value shifted back), all-ones for the entries that unique_by_key drops
+static __global__ void k_unshift_keys(const unsigned long long *__restrict__ skeys, const long long *__restrict__ before, long long nu,
+                                      const ColumnShift *__restrict__ cs, const int *__restrict__ shard_first,
+                                      const int *__restrict__ shard_cols, const long long *__restrict__ shard_before,
+                                      unsigned long long *__restrict__ out, unsigned long long *__restrict__ n_heads) {
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nu; i += (long long)gridDim.x * blockDim.x) {
+        const unsigned long long k = skeys[i];
+        if (i > 0 && skeys[i - 1] == k) { out[i] = ~0ull; continue; }
+        const int d = (int)(k >> 32), first = shard_first[d];
+        const long long pos = before[i] - shard_before[d];
+        int lo = 0, hi = shard_cols[d] - 1;  // smallest local id whose ids start at or before pos (`below` falls as the id grows)
+        while (lo < hi) {
+            const int mid = (lo + hi) / 2;
+            if (cs[first + mid].below <= pos) hi = mid; else lo = mid + 1;
+        }
+        const float t = order_float(~(unsigned)(k & 0xffffffffull)), j = (float)lo, step = cs[first + lo].step;
+        const float v = __fmaf_rn(-j, step, t);
+        out[i] = ((unsigned long long)(unsigned)(first + lo) << 32) | (unsigned)~float_order(v);
+        atomicAdd(n_heads, 1ull);
+    }
+}
+static __global__ void k_fill_ll(long long *p, size_t n, long long v) {
+    for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) p[i] = v;
+}
+// per feature: largest stored value (the last of its ascending keys) and the number of copies before its first key
+static __global__ void k_feature_max_before(const unsigned long long *__restrict__ ukeys, const long long *__restrict__ ustart,
+                                            const long long *__restrict__ before, long long nu, long long total, int F,
+                                            float *__restrict__ fmax, long long *__restrict__ fbefore) {
+    const int f = blockIdx.x * blockDim.x + threadIdx.x;
+    if (f > F) return;
+    const long long a = ustart[f];
+    fbefore[f] = a < nu ? before[a] : total;
+    if (f < F) fmax[f] = ustart[f + 1] > a ? key_to_float(ukeys[ustart[f + 1] - 1]) : -INFINITY;
+}
+
+// HistTreeBuilder::get_bin_ids of the column-sharded builder (hist_tree_builder.cu:31-49): the cut points of a
+// feature descend there; first position in [lo, hi] whose cut is <= v, hi when there is none
+__device__ __forceinline__ int bin_search_down(const float *__restrict__ cut_val, int lo, int hi, float v) {
+    while (lo != hi) {
+        const int mid = lo + (hi - lo) / 2;
+        if (cut_val[mid] <= v) hi = mid; else lo = mid + 1;
+    }
+    return lo;
 }
 
 // HistTreeBuilder_single::get_bin_ids (hist_tree_builder_single.cu:81-119): clamped upper bound,
 // bin = min(#cuts <= v, n_cuts - 1); stored as the feature-local id in both layouts
 static __global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val,
                             int n_rows, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val, int Fpad,
-                            size_t Npad, unsigned char *__restrict__ bins, unsigned char *__restrict__ binsT) {
+                            size_t Npad, unsigned char *__restrict__ bins, unsigned char *__restrict__ binsT, int multi) {
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     if (r >= n_rows) return;
     for (int j = row_ptr[r]; j < row_ptr[r + 1]; ++j) {
@@ -122,6 +203,8 @@ static __global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *_
         const int b0 = cut_ptr[f];
         int lo = b0, hi = cut_ptr[f + 1] - 1;
         if (hi < lo) continue;
+        if (multi) lo = bin_search_down(cut_val, lo, hi, v);
+        else
         while (lo < hi) {
             const int mid = lo + (hi - lo) / 2;
             if (cut_val[mid] <= v) lo = mid + 1; else hi = mid;
@@ -135,11 +218,13 @@ static __global__ void k_bin_dense(const int *__restrict__ row_ptr, const int *_
 // Wide sparse data: the reference's own layout, one global bin id per stored value
 // (hist_tree_builder_single.cu:113-119), sharing the CSR row pointers.
 static __global__ void k_bin_csr(const int *__restrict__ col, const float *__restrict__ val, size_t nnz,
-                                 const int *__restrict__ cut_ptr, const float *__restrict__ cut_val, int *__restrict__ out) {
+                                 const int *__restrict__ cut_ptr, const float *__restrict__ cut_val, int *__restrict__ out, int multi) {
     for (size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x; i < nnz; i += (size_t)gridDim.x * blockDim.x) {
         const int f = col[i];
         const float v = val[i];
         int lo = cut_ptr[f], hi = cut_ptr[f + 1] - 1;
+        if (multi) lo = bin_search_down(cut_val, lo, hi, v);
+        else
         while (lo < hi) {
             const int mid = lo + (hi - lo) / 2;
             if (cut_val[mid] <= v) lo = mid + 1; else hi = mid;
@@ -821,7 +906,10 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
                                              const int *__restrict__ built_right, const T *__restrict__ built,
                                              const T *__restrict__ parent, T *__restrict__ full,
                                              const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, int bs,
-                                             const unsigned char *__restrict__ ignored) {
+                                             const unsigned char *__restrict__ ignored, int multi) {
+    // multi: the column-sharded builder's candidates (hist_tree_builder.cu:299-352): the INCLUSIVE prefix along the
+    // bins (they count down from the largest values there) is the right child, the left one is the node minus it,
+    // missing values join the right child when that gains at least as much; the record then carries the right sums
     // bs: distance of two cells of `built` in cells (1 unless the fp32 histogram kernel spread them out)
     // ignored: the round's column-sampling mask (Shard::column_sampling, src/thundergbm/builder/shard.cu:8-23; the
     // masked features take no part in the split search, hist_tree_builder_single.cu:304,663), or null
@@ -892,7 +980,14 @@ __device__ __forceinline__ void eval_feature(int level, int F, int B, const int 
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
         const int b = lane * 8 + i;
-        if (b < nb) {
+        if (b < nb && multi) {
+            const float rg = cell_f(base_g + lg8[i] + sg[warp][b], inv_sg), rh = cell_f(base_h + lh8[i] + sh[warp][b], inv_sh);
+            const float gl = fmaxf(0.f, split_gain(pg, ph, __fsub_rn(pg, rg), __fsub_rn(ph, rh), rg, rh, mcw, lam));
+            const float rg2 = __fadd_rn(rg, mg), rh2 = __fadd_rn(rh, mh);
+            const float gr = fmaxf(0.f, split_gain(pg, ph, __fsub_rn(pg, rg2), __fsub_rn(ph, rh2), rg2, rh2, mcw, lam));
+            const float gn = gl > gr ? gl : -gr;
+            if (best_bin < 0 || fabsf(gn) > fabsf(best)) { best = gn; best_bin = b; best_lg = rg; best_lh = rh; }
+        } else if (b < nb) {
             const float lg = cell_f(base_g + lg8[i], inv_sg), lh = cell_f(base_h + lh8[i], inv_sh);
             const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
             const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
@@ -929,7 +1024,7 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
              const int *__restrict__ cut_fid, const TreeNode *__restrict__ nodes, const int *__restrict__ built_right,
              const T *__restrict__ built, const T *__restrict__ parent, T *__restrict__ full,
              const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *__restrict__ recs, int bs,
-             const unsigned char *__restrict__ ignored_all, const RoundState *__restrict__ rs, int F) {
+             const unsigned char *__restrict__ ignored_all, const RoundState *__restrict__ rs, int F, int multi) {
     __shared__ T sg[2][256], sh[2][256];
     const unsigned char *ignored = ignored_all ? ignored_all + (size_t)rs->round * F : nullptr;
     const int c = blockIdx.x, j = blockIdx.y;
@@ -1021,12 +1116,21 @@ k_eval_chunk(int level, int n_chunks, int B, const int *__restrict__ chunk_bin0,
             const int f = cut_fid[b0 + b];
             const int lastb = cut_ptr[f + 1] - 1 - b0;
             const float mg = __fsub_rn(pg, cell_f(sg[warp][lastb], inv_sg)), mh = __fsub_rn(ph, cell_f(sh[warp][lastb], inv_sh));
-            const float lg = cell_f(eg[i], inv_sg), lh = cell_f(eh[i], inv_sh);
-            const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
-            const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
-            const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
-            const float gn = gl > gr ? gl : -gr;
-            if (best_bin < 0 || fabsf(gn) > fabsf(best)) { best = gn; best_bin = b0 + b; best_lg = lg; best_lh = lh; best_mg = mg; best_mh = mh; }
+            float gn, keep_g, keep_h;
+            if (multi) {  // inclusive prefix = right child, see eval_feature
+                const float rg = cell_f(sg[warp][b], inv_sg), rh = cell_f(sh[warp][b], inv_sh);
+                const float gl = fmaxf(0.f, split_gain(pg, ph, __fsub_rn(pg, rg), __fsub_rn(ph, rh), rg, rh, mcw, lam));
+                const float rg2 = __fadd_rn(rg, mg), rh2 = __fadd_rn(rh, mh);
+                const float gr = fmaxf(0.f, split_gain(pg, ph, __fsub_rn(pg, rg2), __fsub_rn(ph, rh2), rg2, rh2, mcw, lam));
+                gn = gl > gr ? gl : -gr; keep_g = rg; keep_h = rh;
+            } else {
+                const float lg = cell_f(eg[i], inv_sg), lh = cell_f(eh[i], inv_sh);
+                const float gr = fmaxf(0.f, split_gain(pg, ph, lg, lh, __fsub_rn(pg, lg), __fsub_rn(ph, lh), mcw, lam));
+                const float lg2 = __fadd_rn(lg, mg), lh2 = __fadd_rn(lh, mh);
+                const float gl = fmaxf(0.f, split_gain(pg, ph, lg2, lh2, __fsub_rn(pg, lg2), __fsub_rn(ph, lh2), mcw, lam));
+                gn = gl > gr ? gl : -gr; keep_g = lg; keep_h = lh;
+            }
+            if (best_bin < 0 || fabsf(gn) > fabsf(best)) { best = gn; best_bin = b0 + b; best_lg = keep_g; best_lh = keep_h; best_mg = mg; best_mh = mh; }
         }
     }
     unsigned long long key = best_bin < 0 ? 0ull
@@ -1059,7 +1163,7 @@ __device__ __forceinline__ SplitRec load_rec(const SplitRec *p) {
 }
 __device__ __forceinline__ void best_apply_node(int level, int n, int F, const int *__restrict__ cut_ptr,
                                                 const float *__restrict__ cut_val, const SplitRec *recs, TreeNode *nodes,
-                                                float rt_eps, float lam, const int *__restrict__ cut_fid, int chunked) {
+                                                float rt_eps, float lam, const int *__restrict__ cut_fid, int chunked, int multi) {
     // chunked: F is the number of chunks and a record's bin is a global bin index (k_eval_chunk);
     // otherwise one record per feature with a feature-local bin (k_eval).  Ties go to the smaller global bin either way.
     const int lane = threadIdx.x & 31;
@@ -1108,6 +1212,21 @@ __device__ __forceinline__ void best_apply_node(int level, int n, int F, const i
         nd.gain = gain;
         nd.split_feature_id = f;
         nd.split_bid = (unsigned char)r.bin;
+        if (multi) {
+            // TreeBuilder::update_tree of the column-sharded builder (tree_builder.cu:9-60): the split value is the
+            // cut point itself, the record's sums are the right child's, the left child is the node minus it
+            nd.split_value = cut_val[b0 + r.bin];
+            TreeNode &l = nodes[nd.lch_index], &rc = nodes[nd.rch_index];
+            l.is_valid = 1; rc.is_valid = 1;
+            float rgs = r.lg, rhs = r.lh;
+            if (default_right) { rgs = __fadd_rn(rgs, r.mg); rhs = __fadd_rn(rhs, r.mh); nd.default_right = 1; }
+            else nd.default_right = 0;
+            rc.sum_g = rgs; rc.sum_h = rhs;
+            l.sum_g = __fsub_rn(nd.sum_g, rgs); l.sum_h = __fsub_rn(nd.sum_h, rhs);
+            l.base_weight = __fdiv_rn(-l.sum_g, __fadd_rn(l.sum_h, lam));
+            rc.base_weight = __fdiv_rn(-rc.sum_g, __fadd_rn(rc.sum_h, lam));
+            return;
+        }
         if (r.bin == 0) {
             const float c = cut_val[b0];
             nd.split_value = (float)((double)__fsub_rn(c, fabsf(c)) - 1e-5);
@@ -1134,8 +1253,8 @@ __device__ __forceinline__ void best_apply_node(int level, int n, int F, const i
 static __global__ void __launch_bounds__(32)
 k_best_apply(int level, int F, const int *__restrict__ cut_ptr, const float *__restrict__ cut_val,
              const SplitRec *__restrict__ recs, TreeNode *__restrict__ nodes, float rt_eps, float lam,
-             const int *__restrict__ cut_fid, int chunked) {
-    best_apply_node(level, blockIdx.x, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, chunked);
+             const int *__restrict__ cut_fid, int chunked, int multi) {
+    best_apply_node(level, blockIdx.x, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, chunked, multi);
 }
 
 // Dense layout: evaluation of every (pair, feature) and, by the block that finishes a pair last, the choice among the
@@ -1147,9 +1266,9 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
        const T *__restrict__ built, const T *__restrict__ parent, T *__restrict__ full,
        const QuantInfo *__restrict__ q, float mcw, float lam, SplitRec *recs, const float *__restrict__ cut_val,
        float rt_eps, const int *__restrict__ cut_fid, int *__restrict__ ticket, int built_stride,
-       const unsigned char *__restrict__ ignored_all, const RoundState *__restrict__ rs) {
+       const unsigned char *__restrict__ ignored_all, const RoundState *__restrict__ rs, int multi) {
     const unsigned char *ignored = ignored_all ? ignored_all + (size_t)rs->round * F : nullptr;
-    eval_feature<T>(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs, built_stride, ignored);
+    eval_feature<T>(level, F, B, cut_ptr, nodes, built_right, built, parent, full, q, mcw, lam, recs, built_stride, ignored, multi);
     __shared__ int last;
     __threadfence();  // the block's records are visible before its ticket is
     __syncthreads();
@@ -1161,8 +1280,8 @@ k_eval(int level, int F, int B, const int *__restrict__ cut_ptr, TreeNode *nodes
     if (!last) return;
     __threadfence();
     const int warp = threadIdx.x >> 5;
-    if (level == 0) { if (warp == 0) best_apply_node(0, 0, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, 0); }
-    else best_apply_node(level, 2 * blockIdx.y + warp, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, 0);
+    if (level == 0) { if (warp == 0) best_apply_node(0, 0, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, 0, multi); }
+    else best_apply_node(level, 2 * blockIdx.y + warp, F, cut_ptr, cut_val, recs, nodes, rt_eps, lam, cut_fid, 0, multi);
 }
 
 // ------------------------------------------------------------------ instance partition
@@ -1225,7 +1344,7 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
              const int *__restrict__ node_tile0, const TreeCtl *__restrict__ ctl, const int *__restrict__ rec_idx,
              const unsigned char *__restrict__ binsT, size_t Npad, const int *__restrict__ sp_row_ptr,
              const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr, unsigned *__restrict__ bits,
-             int *__restrict__ tile_left, const int *__restrict__ tile_node) {
+             int *__restrict__ tile_left, const int *__restrict__ tile_node, int rev) {
     __shared__ int wsum[32];
     const int nt = ctl->n_part_tiles[level & 1], nl = 1 << level;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1264,7 +1383,7 @@ k_part_count(int level, const TreeNode *__restrict__ nodes, const int *__restric
         int cnt = 0;
 #pragma unroll
         for (int j = 0; j < PART_RPT; ++j) {
-            const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (b[j] < nd.split_bid));
+            const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (rev ? b[j] > nd.split_bid : b[j] < nd.split_bid));
             const unsigned m = __ballot_sync(0xffffffffu, left);
             if (lane == 0) { bits[(size_t)t * (PART_TILE / 32) + j * (PART_THREADS / 32) + warp] = m; cnt += __popc(m); }
         }
@@ -1426,7 +1545,7 @@ k_part_one(int level, const TreeNode *__restrict__ nodes, const int *__restrict_
            const unsigned char *__restrict__ binsT, size_t Npad, const int *__restrict__ sp_row_ptr,
            const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr, unsigned long long *__restrict__ status,
            unsigned long long *__restrict__ group_sum, int *__restrict__ next_begin, int *__restrict__ next_cnt,
-           int *__restrict__ out_idx, int2 *__restrict__ out_gh, int half) {
+           int *__restrict__ out_idx, int2 *__restrict__ out_gh, int half, int rev) {
     constexpr int WORDS = PART_TILE / 32;        // ballot words of a tile, in record order
     constexpr int WARPS = PART_THREADS / 32;
     __shared__ int s_tile, s_before;
@@ -1480,7 +1599,7 @@ k_part_one(int level, const TreeNode *__restrict__ nodes, const int *__restrict_
         unsigned m[PART_RPT];
 #pragma unroll
         for (int j = 0; j < PART_RPT; ++j) {
-            const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (b[j] < nd.split_bid));
+            const bool left = r[j] >= 0 && ((b[j] == MISSING_BIN) ? !nd.default_right : (rev ? b[j] > nd.split_bid : b[j] < nd.split_bid));
             m[j] = __ballot_sync(0xffffffffu, left);
             if (lane == 0) wpre[j * WARPS + warp] = __popc(m[j]);
         }
@@ -1595,15 +1714,16 @@ k_prune(TreeNode *__restrict__ nodes, int n_nodes, int depth, float gamma, int t
 // A node was split iff its children are valid; pruning only marks nodes, so the walk goes on below a pruned
 // parent to find the node the reference's table would hold (`nid_out`) while the score takes the weight of the
 // deepest node on the path that survived pruning.
-// Walk table entry: flags = split bin (bits 0-7) | default right (8) | was split (9) | pruned (10) | feature << 16
+// Walk table entry: flags = split bin (bits 0-7) | default right (8) | was split (9) | pruned (10) |
+// bins count down, i.e. left means bin > split bin (11; the column-sharded builder's rule, hist_tree_builder.cu:455-459) | feature << 16
 struct WalkNode { int flags; float weight; };
 struct WalkSpan { int c0, c1; };  // CSR layout: global bins [c0, c1) of the split feature
 
-__device__ __forceinline__ WalkNode walk_node(const TreeNode *__restrict__ nodes, int i) {
+__device__ __forceinline__ WalkNode walk_node(const TreeNode *__restrict__ nodes, int i, int rev) {
     const TreeNode nd = nodes[i];
     const bool split = nd.is_valid && nd.lch_index >= 0 && nodes[nd.lch_index].is_valid;
     WalkNode w;
-    w.flags = (int)nd.split_bid | (nd.default_right ? 0x100 : 0) | (split ? 0x200 : 0) | (nd.is_pruned ? 0x400 : 0) |
+    w.flags = (int)nd.split_bid | (nd.default_right ? 0x100 : 0) | (split ? 0x200 : 0) | (nd.is_pruned ? 0x400 : 0) | (rev ? 0x800 : 0) |
               (split ? (int)((unsigned)nd.split_feature_id << 16) : 0);
     w.weight = nd.base_weight;
     return w;
@@ -1626,7 +1746,7 @@ k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_sme
                const int *__restrict__ sp_row_ptr, const int *__restrict__ sp_bin, const int *__restrict__ cut_ptr,
                int n, float lr, float *__restrict__ yp, int *__restrict__ nid_out,
                const float *__restrict__ y, int fuse_objective, double *__restrict__ metric_partial,
-               unsigned *__restrict__ maxbits) {
+               unsigned *__restrict__ maxbits, int rev) {
     // fuse_objective >= 0 (a pointwise objective, one tree per round): the same pass adds up the round's training
     // metric (same grid, same order of additions as k_metric_partial) and finds the maxima of the next round's
     // gradients, so that neither needs a pass of its own over y and the scores.
@@ -1639,7 +1759,7 @@ k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_sme
     WalkSpan *ws = reinterpret_cast<WalkSpan *>(walk_sm + sizeof(WalkNode) * n_nodes);
     if (table_in_smem) {
         for (int i = threadIdx.x; i < n_nodes; i += blockDim.x) {
-            wn[i] = walk_node(nodes, i);
+            wn[i] = walk_node(nodes, i, rev);
             if (LAYOUT == 2) ws[i] = walk_span(nodes, cut_ptr, i);
         }
         __syncthreads();
@@ -1657,7 +1777,7 @@ k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_sme
         float weight = 0.f;
 #pragma unroll 1
         for (;;) {
-            const WalkNode wk = table_in_smem ? wn[nid] : walk_node(nodes, nid);
+            const WalkNode wk = table_in_smem ? wn[nid] : walk_node(nodes, nid, rev);
             if (!(wk.flags & 0x400)) weight = wk.weight;
             if (!(wk.flags & 0x200)) break;
             int b = MISSING_BIN;
@@ -1678,7 +1798,7 @@ k_predict_walk(const TreeNode *__restrict__ nodes, int n_nodes, int table_in_sme
                 const uint32_t b0 = (f & 8) ? a2 : a0, b1 = (f & 8) ? a3 : a1;
                 b = (((f & 4) ? b1 : b0) >> (8 * (f & 3))) & 0xffu;
             }
-            const bool left = (b == MISSING_BIN) ? !(wk.flags & 0x100) : (b < (wk.flags & 0xff));
+            const bool left = (b == MISSING_BIN) ? !(wk.flags & 0x100) : ((wk.flags & 0x800) ? b > (wk.flags & 0xff) : b < (wk.flags & 0xff));
             nid = 2 * nid + (left ? 1 : 2);
         }
         if (nid_out) nid_out[r] = nid;
