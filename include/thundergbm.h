@@ -87,6 +87,8 @@ typedef struct {
     int column_shards;  /* 0: cut points, candidate order and child sums of HistTreeBuilder_single, the reference's builder
                            for n_device = 1; D >= 1: those of the column-sharded HistTreeBuilder it runs for n_device = D > 1
                            (src/thundergbm/builder/hist_tree_builder.cu, hist_cut.cu:104-187), whose cut points depend on D */
+    int exact_builder;  /* 1: tree_method = exact, the reference's ExactTreeBuilder (src/thundergbm/builder/exact_tree_builder.cu):
+                           every distinct stored value of a node is a split candidate; one GPU */
 } TgbmParam;
 
 typedef struct {

@@ -78,6 +78,7 @@ struct TgoParam {
     float column_sampling_rate; // Shard::column_sampling, 1 = off
     unsigned sample_seed;
     int multi_shards;  // 0: HistTreeBuilder_single; D >= 1: HistTreeBuilder with the columns split over D devices
+    int exact_builder; // 1: ExactTreeBuilder (tree_method = exact): every distinct value of a node is a candidate
 };
 }
 
@@ -136,6 +137,10 @@ struct Ctx {
     std::vector<double> round_seconds;
     std::vector<float> gain2;  // [tree][n_nodes]: runner-up |gain| at every evaluated node (how decisive the split was)
     std::vector<unsigned char> ignored;  // column-sampling mask of the running round (empty = no sampling)
+    // exact builder: the stored values by column, largest first (SparseColumns::csr2csc_gpu, sparse_columns.cu:20-93,127)
+    std::vector<int64_t> csc_ptr;
+    std::vector<int> csc_row;
+    std::vector<float> csc_val;
     double train_seconds = 0, init_seconds = 0;
     float expf_(float x) const { return p.portable_exp ? portable_expf(x) : expf(x); }
 };
@@ -302,6 +307,34 @@ void bin_ids_multi(Ctx &c) {
             if (c.cut_val[mid] <= v) right = mid; else left = mid + 1;
         }
         c.bin[i] = left;
+    }
+}
+
+// src/thundergbm/sparse_columns.cu:20-93 csr2csc_gpu + :127 the per-column sort by value, descending and stable
+// (rows of equal value stay in ascending order)
+void build_csc(Ctx &c) {
+    const int F = c.F;
+    const int64_t nnz = c.row_ptr[c.N];
+    c.csc_ptr.assign(F + 1, 0);
+    for (int64_t i = 0; i < nnz; ++i) c.csc_ptr[c.col[i] + 1]++;
+    for (int f = 0; f < F; ++f) c.csc_ptr[f + 1] += c.csc_ptr[f];
+    c.csc_row.resize(nnz); c.csc_val.resize(nnz);
+    std::vector<int64_t> pos(c.csc_ptr.begin(), c.csc_ptr.end() - 1);
+    for (int r = 0; r < c.N; ++r)
+        for (int j = c.row_ptr[r]; j < c.row_ptr[r + 1]; ++j) {
+            const int64_t o = pos[c.col[j]]++;
+            c.csc_row[o] = r; c.csc_val[o] = c.val[j];
+        }
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int f = 0; f < F; ++f) {
+        const int64_t a = c.csc_ptr[f], b = c.csc_ptr[f + 1];
+        std::vector<int64_t> idx(b - a);
+        for (int64_t i = 0; i < b - a; ++i) idx[i] = a + i;
+        std::stable_sort(idx.begin(), idx.end(), [&](int64_t x, int64_t y) { return c.csc_val[x] > c.csc_val[y]; });
+        std::vector<int> rr(b - a); std::vector<float> vv(b - a);
+        for (int64_t i = 0; i < b - a; ++i) { rr[i] = c.csc_row[idx[i]]; vv[i] = c.csc_val[idx[i]]; }
+        std::copy(rr.begin(), rr.end(), c.csc_row.begin() + a);
+        std::copy(vv.begin(), vv.end(), c.csc_val.begin() + a);
     }
 }
 
@@ -669,6 +702,121 @@ struct Builder {
         }
     }
 
+    // ExactTreeBuilder::find_split (src/thundergbm/builder/exact_tree_builder.cu:15-300) for every node of the level:
+    // the stored values of a (feature, node) in descending order; runs of equal value are one candidate with the run's
+    // summed (g,h) (:94-111); the inclusive prefix over the runs is the RIGHT child (:114-118); missing = node sum minus
+    // the last prefix (:160-167); a candidate's split value is the midpoint to the next smaller distinct value, for
+    // the smallest one `v - |largest value| - rt_eps` (:137-151); gains, default direction and ties as in the
+    // column-sharded histogram builder (:186-209, :218-258: smaller index, i.e. smaller feature, then larger value).
+    std::vector<Split> evaluate_exact(int level) {
+        const int n_level = 1 << level, off = n_level - 1;
+        std::vector<Split> sps(n_level);
+        struct Best { float gain = 0, second = 0; bool have = false; int fea = -1; float fval = 0, rg = 0, rh = 0, mg = 0, mh = 0; };
+        std::vector<Best> best(n_level);
+        const float mcw = c.p.min_child_weight, lam = c.p.lambda;
+        std::vector<std::vector<int64_t>> ent(n_level);   // entries of the running feature by node, column order kept
+        for (int f = 0; f < c.F; ++f) {
+            const bool left_out = !c.ignored.empty() && c.ignored[f];   // :195: its candidates stay, with gain 0
+            for (auto &e : ent) e.clear();
+            for (int64_t i = c.csc_ptr[f]; i < c.csc_ptr[f + 1]; ++i) {
+                const int n = nid[c.csc_row[i]] - off;
+                if (n >= 0 && n < n_level) ent[n].push_back(i);
+            }
+            for (int n = 0; n < n_level; ++n) {
+                const auto &e = ent[n];
+                if (e.empty()) continue;
+                const TreeNode &nd = nodes[off + n];
+                const float pg = nd.sum_g, ph = nd.sum_h;
+                // runs of equal value and their prefix sums
+                std::vector<float> rv, Pg, Ph;
+                if (c.p.hist_mode == 1) {
+                    double ag = 0, ah = 0;
+                    for (size_t t = 0; t < e.size(); ++t) {
+                        double g, h; qrow(c.csc_row[e[t]], g, h);
+                        ag += g; ah += h;
+                        if (t + 1 == e.size() || c.csc_val[e[t + 1]] != c.csc_val[e[t]]) { rv.push_back(c.csc_val[e[t]]); Pg.push_back(to_f(ag, q.sg)); Ph.push_back(to_f(ah, q.sh)); }
+                    }
+                } else {
+                    // run sum first (:94-111; thrust's reduce_by_key adds a run as a tree of partial sums, which stays within
+                    // an ulp or two of the rounded exact sum: restated as a double sum rounded once), then the float scan
+                    // over the runs (:114-118)
+                    float ag = 0, ah = 0;
+                    double sg = 0, sh = 0;
+                    for (size_t t = 0; t < e.size(); ++t) {
+                        sg += gh[c.csc_row[e[t]]].g; sh += gh[c.csc_row[e[t]]].h;
+                        if (t + 1 == e.size() || c.csc_val[e[t + 1]] != c.csc_val[e[t]]) {
+                            ag += (float)sg; ah += (float)sh; sg = 0; sh = 0;
+                            rv.push_back(c.csc_val[e[t]]); Pg.push_back(ag); Ph.push_back(ah);
+                        }
+                    }
+                }
+                const size_t R = rv.size();
+                const float mg = pg - Pg[R - 1], mh = ph - Ph[R - 1];
+                Best &b = best[n];
+                for (size_t t = 0; t < R; ++t) {
+                    const float rg = Pg[t], rh = Ph[t];
+                    const float gl = fmaxf(0.f, gainf(pg, ph, pg - rg, ph - rh, rg, rh, mcw, lam));
+                    const float rg2 = rg + mg, rh2 = rh + mh;
+                    const float gr = fmaxf(0.f, gainf(pg, ph, pg - rg2, ph - rh2, rg2, rh2, mcw, lam));
+                    const float gn = left_out ? 0.f : (gl > gr ? gl : -gr);
+                    if (!b.have || fabsf(gn) > fabsf(b.gain)) {
+                        if (b.have) b.second = fmaxf(b.second, fabsf(b.gain));
+                        b.have = true; b.gain = gn; b.fea = f; b.rg = rg; b.rh = rh; b.mg = mg; b.mh = mh;
+                        b.fval = t + 1 == R ? (rv[t] - fabsf(rv[0])) - c.p.rt_eps : (rv[t] + rv[t + 1]) * 0.5f;
+                    } else b.second = fmaxf(b.second, fabsf(gn));
+                }
+            }
+        }
+        for (int n = 0; n < n_level; ++n) {
+            if (!best[n].have) continue;   // no stored value in the node: SplitPoint::nid stays -1 (:273-275)
+            Split &sp = sps[n];
+            const Best &b = best[n];
+            sp.nid = off + n; sp.fea = b.fea; sp.gain = fabsf(b.gain); sp.gain2 = b.second; sp.bid = 0;
+            sp.default_right = b.gain < 0; sp.miss_g = b.mg; sp.miss_h = b.mh; sp.l_g = b.rg; sp.l_h = b.rh; sp.fval = b.fval;
+        }
+        return sps;
+    }
+
+    // ExactTreeBuilder::update_ins2node_id + ins2node_id_all_reduce (exact_tree_builder.cu:303-340, :394-409): rows that
+    // store the split feature compare the value with the split value, the others follow the default direction
+    bool move_rows_exact() {
+        bool any = false;
+        std::vector<int> next(nid);
+        std::vector<unsigned char> moved(c.N, 0);
+        for (int f = 0; f < c.F; ++f)
+            for (int64_t i = c.csc_ptr[f]; i < c.csc_ptr[f + 1]; ++i) {
+                const int r = c.csc_row[i];
+                const TreeNode &nd = nodes[nid[r]];
+                if (nd.is_leaf || !nd.is_valid || nd.split_feature_id != f) continue;
+                any = true;
+                next[r] = c.csc_val[i] < nd.split_value ? nd.lch_index : nd.rch_index;
+                moved[r] = 1;
+            }
+        if (!any) return false;   // tree_builder.cu:174-181 leaves the level loop before the default directions are applied
+        for (int r = 0; r < c.N; ++r) {
+            const TreeNode &nd = nodes[nid[r]];
+            if (moved[r] || nd.is_leaf || !nd.is_valid) continue;
+            next[r] = nd.default_right ? nd.rch_index : nd.lch_index;
+        }
+        nid.swap(next);
+        return any;
+    }
+
+    // src/thundergbm/builder/tree_builder.cu:147-194 with ExactTreeBuilder's find_split / update_ins2node_id
+    void build_exact() {
+        const int d = c.p.depth;
+        nid.assign(c.N, 0);
+        init_tree();
+        gain2.assign(nodes.size(), 0.f);
+        for (int level = 0; level < d; ++level) {
+            const int n_level = 1 << level, off = n_level - 1;
+            std::vector<Split> sps = evaluate_exact(level);
+            for (int n = 0; n < n_level; ++n) { gain2[off + n] = sps[n].gain2; apply_multi(sps[n]); }
+            if (!move_rows_exact()) break;
+        }
+        prune();
+    }
+
     // hist_tree_builder_single.cu:847-902 update_tree
     void apply(const Split &sp) {
         if (c.p.multi_shards > 0) { apply_multi(sp); return; }
@@ -932,13 +1080,14 @@ void train(Ctx &c) {
         if (c.p.num_class > 2) c.K = c.p.num_class;
     } else if (o == REG_LINEAR || o == REG_LOGISTIC) c.p.num_class = 1;
     if (o == RANK_NDCG) compute_idcg(c);
-    if (c.p.multi_shards > 0) { find_cuts_multi(c); bin_ids_multi(c); }
+    if (c.p.exact_builder) { build_csc(c); c.cut_ptr.assign(c.F + 1, 0); }
+    else if (c.p.multi_shards > 0) { find_cuts_multi(c); bin_ids_multi(c); }
     else { find_cuts(c); bin_ids(c); }
     const int N = c.N, K = c.K;
     c.n_nodes = (1 << (c.p.depth + 1)) - 1;
     c.ypred.assign((size_t)K * N, 0.f);
     std::vector<GH> gh((size_t)K * N);
-    init_base_score(c, gh);
+    if (!c.p.exact_builder) init_base_score(c, gh);   // include/thundergbm/booster.h:66-73: only for tree_method = hist
     c.init_seconds = now_s() - t_init;
     const double t0 = now_s();
     for (int r = 0; r < c.p.n_trees; ++r) {  // src/thundergbm/trainer.cu:44-47, include/thundergbm/booster.h:76-93
@@ -952,7 +1101,8 @@ void train(Ctx &c) {
         for (int k = 0; k < K; ++k) {
             q.round = (uint32_t)r; q.k = (uint32_t)k;
             Builder b(c, gh.data() + (size_t)k * N, q);
-            b.build(r == 0 && k == 0 && c.p.keep_nid);
+            if (c.p.exact_builder) b.build_exact();
+            else b.build(r == 0 && k == 0 && c.p.keep_nid);
             predict_in_training(c, b, c.ypred.data() + (size_t)k * N);
             c.trees.insert(c.trees.end(), b.nodes.begin(), b.nodes.end());
             c.gain2.insert(c.gain2.end(), b.gain2.begin(), b.gain2.end());

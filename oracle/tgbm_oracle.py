@@ -29,7 +29,7 @@ class TgoParam(C.Structure):
                 ('rt_eps', C.c_float), ('learning_rate', C.c_float), ('hist_mode', C.c_int), ('quant_bits', C.c_int),
                 ('n_threads', C.c_int), ('keep_nid', C.c_int), ('portable_exp', C.c_int), ('rank_seed', C.c_uint),
                 ('bagging', C.c_int), ('column_sampling_rate', C.c_float), ('sample_seed', C.c_uint),
-                ('multi_shards', C.c_int)]
+                ('multi_shards', C.c_int), ('exact_builder', C.c_int)]
 
 
 def build() -> str:
@@ -94,7 +94,7 @@ def train(data, objective='reg:linear', depth=6, n_trees=40, max_num_bin=255, le
     l = lib()
     p = TgoParam(depth, n_trees, max_num_bin, OBJECTIVES[objective], num_class, lam, gamma, min_child_weight, rt_eps,
                  learning_rate, hist_mode, quant_bits, n_threads, keep_nid, portable_exp, rank_seed, int(bagging),
-                 column_sampling_rate, sample_seed, multi_shards)
+                 column_sampling_rate, sample_seed, multi_shards, 1 if tree_method == 'exact' else 0)
     rp = np.ascontiguousarray(data.row_ptr, np.int32); col = np.ascontiguousarray(data.col, np.int32)
     val = np.ascontiguousarray(data.val, np.float32); y = np.ascontiguousarray(data.y, np.float32)
     grp = np.ascontiguousarray(data.group, np.int32)
@@ -108,7 +108,7 @@ def train(data, objective='reg:linear', depth=6, n_trees=40, max_num_bin=255, le
         r.train_seconds, r.init_seconds = l.tgo_train_seconds(h), l.tgo_init_seconds(h)
         r.cut_val = _view(l.tgo_cut_val(h), (B,), np.float32)
         r.cut_ptr = _view(l.tgo_cut_ptr(h), (F + 1,), np.int32)
-        r.bins = _view(l.tgo_bins(h), (int(rp[-1]),), np.int32)
+        r.bins = _view(l.tgo_bins(h), (int(rp[-1]),), np.int32) if tree_method != 'exact' else np.zeros(0, np.int32)
         r.trees = _view(l.tgo_trees(h), (n_trees, K, nn), NODE_DTYPE)
         r.metric = _view(l.tgo_metric(h), (n_trees,), np.float32)
         r.ypred = _view(l.tgo_ypred(h), (K, data.n_rows), np.float32)

@@ -19,10 +19,13 @@ def load_golden(name):
     return g
 
 
-def compare_tree_decisive(ref, mine, gain2, rel_margin=1e-4):
+def compare_tree_decisive(ref, mine, gain2, rel_margin=1e-4, min_child_weight=None):
     """Walks two trees of the same shape from the root.  Where both split on the same (feature, bin) the walk
     continues into both children; where they differ, the node must be a near-tie in `mine` (runner-up gain within
-    rel_margin of the best), otherwise it is reported.  Returns (#nodes compared equal, list of real mismatches)."""
+    rel_margin of the best), otherwise it is reported.  With `min_child_weight`: also excused is a node where `ref` took
+    `mine`'s runner-up while a child of `mine`'s own choice sits within 16 ulps of the node's sum of the hessian threshold -- the candidate
+    passes `h >= min_child_weight` on one side and fails it on the other by the last bits of a float sum.
+    Returns (#nodes compared equal, list of real mismatches)."""
     bad, same = [], 0
     stack = [0]
     while stack:
@@ -35,9 +38,15 @@ def compare_tree_decisive(ref, mine, gain2, rel_margin=1e-4):
         # a parent pruned back to a leaf keeps its split fields: compare the unpruned decision
         a_split = a['split_feature_id'] >= 0 and a['gain'] > 0
         b_split = b['split_feature_id'] >= 0 and b['gain'] > 0
-        if a_split != b_split or (a_split and (a['split_feature_id'] != b['split_feature_id'] or a['split_bid'] != b['split_bid'])):
+        if a_split != b_split or (a_split and (a['split_feature_id'] != b['split_feature_id'] or a['split_bid'] != b['split_bid'] or
+                                               a['split_value'] != b['split_value'])):   # (the exact builder has no bins)
             g = max(float(b['gain']), float(a['gain']), 1e-30)
             tie = abs(float(b['gain']) - float(gain2[i])) <= rel_margin * g or g < 1e-3
+            if not tie and min_child_weight is not None and b_split and b['lch_index'] > 0:
+                h_min = min(float(mine[b['lch_index']]['sum_h']), float(mine[b['rch_index']]['sum_h']))
+                # a child's sum is the node's minus the sibling's: its error is a few ulps of the NODE's sum
+                edge = max(2e-3 * min_child_weight, 16 * float(np.spacing(np.float32(abs(float(b['sum_h']))))))
+                tie = abs(h_min - min_child_weight) <= edge and abs(float(a['gain']) - float(gain2[i])) <= rel_margin * g
             if not tie:
                 bad.append(i)
             continue

@@ -15,6 +15,8 @@
 
     python tests/golden/pack_golden.py <run_dir> [--rerun <run_dir2> ...] [--out <dir>] [--shrink]
 
+--prefix exact packs runs made with tree_method=exact dump_bins=0 (no cut points exist there) as ref_exact_<case>.npz.
+
 A run made with n_device=D > 1 (the reference's column-sharded builder; run_reference.sh <out> n_device=2) is packed
 as ref_multi_<case>.npz with the same keys plus n_device: cut points of all features in feature order (they descend
 inside a feature there) and the global bin ids rebuilt from the devices' dense matrices.
@@ -161,12 +163,13 @@ def multi_device_dumps(g, d):
 
 
 def main(argv):
-    src, reruns, out, shrink = None, [], HERE, False
+    src, reruns, out, shrink, prefix = None, [], HERE, False, None
     i = 0
     while i < len(argv):
         if argv[i] == '--rerun': reruns.append(argv[i + 1]); i += 2
         elif argv[i] == '--out': out = argv[i + 1]; i += 2
         elif argv[i] == '--shrink': shrink = True; i += 1
+        elif argv[i] == '--prefix': prefix = argv[i + 1]; i += 2
         else: src = argv[i]; i += 1
     if src is None:
         raise SystemExit(__doc__)
@@ -198,6 +201,24 @@ def main(argv):
             np.savez_compressed(os.path.join(out, f'ref_multi_{name}.npz'), **keys)
             continue
         if not os.path.exists(os.path.join(g, 'tgbm.model')):
+            continue
+        if not os.path.exists(os.path.join(g, 'cut_val.f32')):  # a run without cut points (tree_method=exact) -> ref_<prefix>_<case>.npz
+            if not prefix:
+                continue
+            y = CASES[name][0]().y
+            run = load_run(g, y)
+            m = run['model']
+            others = [load_run(os.path.join(r, name), y) for r in reruns if os.path.exists(os.path.join(r, name, 'tgbm.model'))]
+            raw = run['raw']
+            extra = spread(run, others) if others else dict(spread_runs=0)
+            np.savez_compressed(
+                os.path.join(out, f'ref_{prefix}_{name}.npz'), trees=m['trees'], base_score=np.float32(m['base_score']),
+                label=m['label'], num_class=m['num_class'], learning_rate=np.float32(m['learning_rate']),
+                metric=np.asarray(run['metric'], np.float32), raw_pred_sample=raw[::37],
+                raw_pred_sha256=np.frombuffer(hashlib.sha256(raw.tobytes()).digest(), np.uint8), n_raw=raw.size,
+                logloss=np.float64(run['logloss'] if run['logloss'] is not None else np.nan), **extra)
+            print(prefix, name, 'trees', m['trees'].shape, 'metric', run['metric'][-1] if run['metric'] else None,
+                  {k: (float('%.3g' % v) if isinstance(v, float) else v) for k, v in extra.items()})
             continue
         if not os.path.exists(os.path.join(g, 'cut_val.f32')):
             continue

@@ -16,7 +16,7 @@ class TgbmParam(C.Structure):
                 ('min_child_weight', C.c_float), ('lambda_', C.c_float), ('gamma', C.c_float),
                 ('learning_rate', C.c_float), ('objective', C.c_char_p), ('quant_bits', C.c_int),
                 ('keep_nid', C.c_int), ('verbose', C.c_int), ('profile', C.c_int), ('rank_seed', C.c_uint),
-                ('hist_mode', C.c_int), ('bagging', C.c_int), ('column_sampling_rate', C.c_float), ('sample_seed', C.c_uint), ('column_shards', C.c_int)]
+                ('hist_mode', C.c_int), ('bagging', C.c_int), ('column_sampling_rate', C.c_float), ('sample_seed', C.c_uint), ('column_shards', C.c_int), ('exact_builder', C.c_int)]
 
 
 class TgbmInfo(C.Structure):

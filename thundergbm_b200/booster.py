@@ -53,6 +53,7 @@ def make_param(**kw) -> TgbmParam:
         if k == 'objective':
             v = v.encode()
         if k == 'tree_method':
+            p.exact_builder = 1 if v == 'exact' else 0
             continue
         if k == 'hist_mode' and isinstance(v, str):
             v = {'fp32': 0, 'exact': 1}[v]

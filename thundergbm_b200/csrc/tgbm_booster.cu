@@ -14,6 +14,7 @@
 
 #include "tgbm_kernels.cuh"
 #include "tgbm_hist_f32.cuh"
+#include "tgbm_exact.cuh"
 #include "tgbm_rank.cuh"
 
 namespace tgbm {
@@ -122,6 +123,20 @@ struct BoosterImpl {
     // ---------------------------------------------------------------- init helpers
     void upload_csr(const DataSet &ds);
     void find_cuts_and_bins(const DataSet &ds);
+    // tree_method = exact (tgbm_exact.cuh)
+    bool exact = false;
+    long long ex_nnz = 0;
+    DevBuf<int> ex_row;                 // stored values by column, largest first: row ...
+    DevBuf<float> ex_val;               // ... and value
+    DevBuf<long long> ex_csc_ptr;
+    DevBuf<unsigned> ex_key[2], ex_idx[2];  // per level: partition id of every entry / sorted, entry of every sorted position
+    DevBuf<unsigned char> ex_sums;      // ExPair<T> per sorted position: (g,h) of its partition up to itself
+    DevBuf<int> ex_pid_ptr, ex_nid, ex_any;
+    DevBuf<unsigned long long> ex_best;
+    DevBuf<unsigned char> ex_tmp;       // scratch of the radix sort and the scan by key
+    void init_exact(const DataSet &ds);
+    template <typename T> void exact_levels(int k, const void *gh_rows);
+    void build_tree_exact(int round, int k);
     void column_builder_candidates(DevBuf<unsigned long long> &ukeys, DevBuf<long long> &ucopies, long long &nu);
     void init_base_score();
     void gradient(int round);
@@ -475,6 +490,129 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Exact builder, set-up: the stored values by column, largest first (SparseColumns::csr2csc_gpu,
+// src/thundergbm/sparse_columns.cu:20-93 and :127) -- one stable radix sort of (column, complement of the value's ordered
+// image) keys with the row ids as payload -- and the buffers of the level loop, sized once.
+void BoosterImpl::init_exact(const DataSet &ds) {
+    const size_t nnz = (size_t)ds.rp[N];
+    ex_nnz = (long long)nnz;
+    TGBM_CHECK(nnz < (1ull << 31), "the exact builder indexes stored values with 32 bits");
+    TGBM_CHECK((double)F * (double)(1 << std::max(0, depth - 1)) < 4294967295.0, "columns x nodes of the last level must fit 32 bits");
+    const size_t n1 = std::max<size_t>(nnz, 1);
+    const int grid = std::max(1, std::min(ceil_div((long long)n1, 256), num_sms * 16));
+    {
+        DevBuf<unsigned long long> keys, keys2;
+        DevBuf<int> rows;
+        keys.alloc(n1); keys2.alloc(n1); rows.alloc(n1); ex_row.alloc(n1); ex_val.alloc(n1); ex_csc_ptr.alloc(F + 1);
+        if (N) k_exact_rows<<<std::min(ceil_div(N, 256), num_sms * 16), 256, 0, stream>>>(d_row_ptr.p, N, rows.p);
+        if (nnz) k_exact_csc_keys<<<grid, 256, 0, stream>>>(d_val.p, d_col.p, nnz, keys.p);
+        int end_bit = 32;
+        while ((1ll << (end_bit - 32)) < F && end_bit < 64) ++end_bit;
+        if (nnz) {
+            size_t tb = 0;
+            cub::DeviceRadixSort::SortPairs(nullptr, tb, keys.p, keys2.p, rows.p, ex_row.p, (long long)nnz, 0, end_bit, stream);
+            DevBuf<unsigned char> tmp;
+            tmp.alloc(std::max<size_t>(tb, 1));
+            TGBM_CUDA(cub::DeviceRadixSort::SortPairs(tmp.p, tb, keys.p, keys2.p, rows.p, ex_row.p, (long long)nnz, 0, end_bit, stream));
+            k_exact_csc_vals<<<grid, 256, 0, stream>>>(keys2.p, nnz, ex_val.p);
+            TGBM_CUDA(cudaStreamSynchronize(stream));
+        }
+        k_feature_bounds<<<ceil_div(F + 1, 128), 128, 0, stream>>>(keys2.p, (long long)nnz, F, ex_csc_ptr.p);
+        TGBM_CUDA(cudaStreamSynchronize(stream));
+    }
+    d_row_ptr.release(); d_col.release(); d_val.release();
+    // no cut points, no bin matrix
+    B = 0; sparse = false;
+    h_cut_ptr.assign(F + 1, 0);
+    cut_ptr.alloc(F + 1); cut_val.alloc(1); cut_fid.alloc(1);
+    cut_ptr.zero(stream);
+    const size_t max_nl = (size_t)1 << std::max(0, depth - 1);
+    for (int i = 0; i < 2; ++i) { ex_key[i].alloc(n1); ex_idx[i].alloc(n1); }
+    k_exact_iota<<<grid, 256, 0, stream>>>(ex_idx[0].p, n1);
+    ex_sums.alloc(n1 * (f32 ? sizeof(ExPair<float>) : sizeof(ExPair<long long>)));
+    ex_pid_ptr.alloc((size_t)F * max_nl + 2);
+    ex_nid.alloc(std::max(N, 1));
+    ex_best.alloc(max_nl);
+    ex_best.zero(stream);
+    ex_any.alloc(1);
+    ex_any.zero(stream);
+    size_t tb_sort = 0, tb_scan = 0;
+    cub::DeviceRadixSort::SortPairs(nullptr, tb_sort, ex_key[0].p, ex_key[1].p, ex_idx[0].p, ex_idx[1].p, (long long)n1, 0, 32, stream);
+    if (f32) {
+        cub::TransformInputIterator<ExPair<float>, ExGather<float>, cub::CountingInputIterator<long long>> in(
+            cub::CountingInputIterator<long long>(0), ExGather<float>{ex_idx[1].p, ex_row.p, nullptr});
+        cub::DeviceScan::InclusiveScanByKey(nullptr, tb_scan, ex_key[1].p, in, reinterpret_cast<ExPair<float> *>(ex_sums.p), ExAdd<float>(),
+                                            (long long)n1, cub::Equality(), stream);
+    } else {
+        cub::TransformInputIterator<ExPair<long long>, ExGather<long long>, cub::CountingInputIterator<long long>> in(
+            cub::CountingInputIterator<long long>(0), ExGather<long long>{ex_idx[1].p, ex_row.p, nullptr});
+        cub::DeviceScan::InclusiveScanByKey(nullptr, tb_scan, ex_key[1].p, in, reinterpret_cast<ExPair<long long> *>(ex_sums.p), ExAdd<long long>(),
+                                            (long long)n1, cub::Equality(), stream);
+    }
+    ex_tmp.alloc(std::max<size_t>(std::max(tb_sort, tb_scan), 1));
+    TGBM_CUDA(cudaFuncSetAttribute(k_exact_gain<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    TGBM_CUDA(cudaFuncSetAttribute(k_exact_gain<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+    TGBM_CUDA(cudaStreamSynchronize(stream));
+    TGBM_CUDA(cudaGetLastError());
+}
+
+// The level loop of one tree with the exact split search (TreeBuilder::build_approximate, tree_builder.cu:147-194, with
+// ExactTreeBuilder::find_split / update_ins2node_id).  T = float: the reference's arithmetic; T = long long: sums of the
+// quantised gradients, exact in any order.
+template <typename T>
+void BoosterImpl::exact_levels(int k, const void *gh_rows) {
+    const long long nnz = ex_nnz;
+    const int grid = std::max(1, std::min(ceil_div(std::max<long long>(nnz, 1), 256), num_sms * 16));
+    const int row_grid = std::max(1, std::min(ceil_div(std::max(N, 1), 256), num_sms * 8));
+    ExPair<T> *sums = reinterpret_cast<ExPair<T> *>(ex_sums.p);
+    TGBM_CUDA(cudaMemsetAsync(ex_nid.p, 0, sizeof(int) * (size_t)std::max(N, 1), stream));
+    for (int level = 0; level < depth; ++level) {
+        const int nl = 1 << level;
+        const long long n_pid = (long long)F * nl;
+        if (nnz) {
+            k_exact_keys<<<grid, 256, 0, stream>>>(ex_row.p, nnz, ex_csc_ptr.p, F, ex_nid.p, level, ex_key[0].p);
+            int end_bit = 1;
+            while ((1ll << end_bit) <= n_pid && end_bit < 32) ++end_bit;   // the largest key, EX_NONE, has every bit set
+            size_t tb = ex_tmp.n;
+            TGBM_CUDA(cub::DeviceRadixSort::SortPairs(ex_tmp.p, tb, ex_key[0].p, ex_key[1].p, ex_idx[0].p, ex_idx[1].p, nnz, 0, end_bit, stream));
+            using Gather = ExGather<T>;
+            cub::TransformInputIterator<ExPair<T>, Gather, cub::CountingInputIterator<long long>> in(
+                cub::CountingInputIterator<long long>(0),
+                Gather{ex_idx[1].p, ex_row.p, reinterpret_cast<decltype(Gather::gh)>(gh_rows)});
+            tb = ex_tmp.n;
+            TGBM_CUDA(cub::DeviceScan::InclusiveScanByKey(ex_tmp.p, tb, ex_key[1].p, in, sums, ExAdd<T>(), nnz, cub::Equality(), stream));
+            k_exact_pid_ptr<<<std::max(1, std::min(ceil_div(n_pid + 1, 256), num_sms * 16)), 256, 0, stream>>>(ex_key[1].p, nnz, n_pid, ex_pid_ptr.p);
+            k_exact_gain<T><<<num_sms * 2, EX_THREADS, sizeof(unsigned long long) * (size_t)nl, stream>>>(
+                ex_key[1].p, ex_idx[1].p, ex_val.p, sums, ex_pid_ptr.p, nnz, level, nodes.p, qinfo.p, p.min_child_weight, p.lambda,
+                ignored_all.p, rstate.p, F, ex_best.p);
+            launches += 5;
+        }
+        k_exact_apply<T><<<ceil_div(nl, 128), 128, 0, stream>>>(ex_key[1].p, ex_idx[1].p, ex_val.p, sums, ex_pid_ptr.p, level, nodes.p, qinfo.p,
+                                                                 p.min_child_weight, p.lambda, p.rt_eps, ex_best.p, ex_any.p);
+        if (nnz) k_exact_move<<<grid, 256, 0, stream>>>(ex_row.p, ex_val.p, nnz, ex_csc_ptr.p, F, ex_nid.p, nodes.p, ex_any.p);
+        k_exact_move_missing<<<row_grid, 256, 0, stream>>>(ex_nid.p, N, level, nodes.p, ex_any.p);
+        launches += 3;
+    }
+    (void)k;
+}
+
+void BoosterImpl::build_tree_exact(int round, int k) {
+    const int tree_index = round * K + k;
+    k_tree_init<<<ceil_div(n_nodes, 256), 256, 0, stream>>>(nodes.p, n_nodes, root_sum.p + 2 * k, qinfo.p, p.lambda, N,
+                                                            seg_begin[0].p, seg_cnt[0].p, gcnt.p, ctl.p, f32 ? 1 : 0);
+    if (f32) exact_levels<float>(k, gh.p + (size_t)k * N);
+    else exact_levels<long long>(k, ghq.p + (size_t)k * N);
+    k_prune<<<1, 1024, prune_in_smem ? sizeof(TreeNode) * (size_t)n_nodes : 0, stream>>>(nodes.p, n_nodes, depth, p.gamma, prune_in_smem ? 1 : 0);
+    if (N) {
+        int *nid_out = p.keep_nid ? nid_keep.p + (size_t)tree_index * N : nullptr;
+        k_exact_predict<<<std::min(ceil_div(N, 256), num_sms * 8), 256, 0, stream>>>(ex_nid.p, N, nodes.p, p.learning_rate, ypred.p + (size_t)k * N, nid_out);
+    }
+    grad_max_ready = metric_partial_ready = false;
+    k_store_tree<<<std::min(ceil_div(n_nodes, 256), 64), 256, 0, stream>>>(nodes.p, model.p, n_nodes, K, k, rstate.p);
+    launches += 4;
+}
+
+// ------------------------------------------------------------------------------------------------
 Booster::Booster(const GBMParam &param, const Comm *comm) : impl_(new BoosterImpl) {
     impl_->p = param;
     impl_->comm = comm;
@@ -574,7 +712,16 @@ void Booster::init(const DataSet &ds) {
         fprintf(stderr, "[tgbm init] %-28s %8.1f ms\n", what, std::chrono::duration<double, std::milli>(t - t_mark).count());
         t_mark = t;
     };
-    m.find_cuts_and_bins(ds);
+    if (p.tree_method == "auto") p.tree_method = m.F > 20000 ? "exact" : "hist";   // src/thundergbm/trainer.cu:19-23
+    TGBM_CHECK(p.tree_method == "hist" || p.tree_method == "exact", "unknown tree_method " + p.tree_method);
+    m.exact = p.tree_method == "exact";
+    if (m.exact) {
+        TGBM_CHECK(!multi, "the exact builder runs on one GPU");
+        locally([&] { m.init_exact(ds); });
+        agree("sorting its columns");
+    } else {
+        m.find_cuts_and_bins(ds);
+    }
     lap("= cuts and bins, with frees");
 
     locally([&] {
@@ -647,7 +794,7 @@ void Booster::init(const DataSet &ds) {
     m.graphs_allowed = getenv("TGBM_NO_GRAPH") == nullptr;
     m.eval_ticket.zero(m.stream);
     m.hist_seq.alloc((size_t)ceil_div(std::max(N, 1), HIST_THREADS) + max_pairs + 16);
-    m.recs.alloc(((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
+    m.recs.alloc(m.exact ? 1 : ((size_t)1 << (depth - 1)) * (m.sparse ? std::max(m.n_chunks, 1) : m.F));
     m.max_tiles = ceil_div(N, PART_TILE) + (1 << depth) + 2;
     m.tile_left.alloc(m.max_tiles);
     m.tile_node[0].alloc(m.max_tiles); m.tile_node[1].alloc(m.max_tiles);
@@ -738,6 +885,7 @@ void BoosterImpl::gradient(int round) {
 // with the host's libm, as the reference does.
 void BoosterImpl::init_base_score() {
     base_score = 0;
+    if (exact) return;   // include/thundergbm/booster.h:66-73: the reference computes a base score for tree_method = hist only
     if (!(objective == REG_LINEAR || objective == REG_LOGISTIC || objective == BINARY_LOGISTIC)) return;
     gradient(-1);
     unsigned long long hs[2];
@@ -969,7 +1117,10 @@ void BoosterImpl::round_metric(int round) {
 void BoosterImpl::run_round(int round) {
     auto direct = [&]() {
         gradient(round);
-        for (int k = 0; k < K; ++k) build_tree(round, k);
+        for (int k = 0; k < K; ++k) {
+            if (exact) build_tree_exact(round, k);
+            else build_tree(round, k);
+        }
         round_metric(round);
     };
     static const bool graph_with_comm = getenv("TGBM_NO_GRAPH_COMM") == nullptr;  // the round's collectives are captured with it
@@ -1034,6 +1185,7 @@ int Booster::num_class() const { return impl_->num_class; }
 float Booster::base_score() const { return impl_->base_score; }
 int Booster::n_bins() const { return impl_->B; }
 int Booster::n_features() const { return impl_->F; }
+std::string Booster::tree_method() const { return impl_->p.tree_method; }
 int Booster::fpad() const { return impl_->Fpad; }
 cudaStream_t Booster::stream() const { return impl_->stream; }
 void Booster::set_profile(bool on) {

@@ -49,6 +49,7 @@ public:
     float base_score() const;
     int n_bins() const;
     int n_features() const;
+    std::string tree_method() const;   // after init(): "hist" or "exact" (auto resolved)
     int fpad() const;
     cudaStream_t stream() const;
     void set_profile(bool on);

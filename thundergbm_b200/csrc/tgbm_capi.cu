@@ -4,6 +4,7 @@
 #include <climits>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <thread>
 
@@ -56,8 +57,7 @@ std::vector<std::vector<tgbm::Tree>> wrap_model(::Tree *model, int n_trees, int 
 
 // TreeTrainer::train (src/thundergbm/trainer.cu:18-57) for the histogram path
 std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSet &ds, const tgbm::Comm *comm) {
-    TGBM_CHECK(p.tree_method == "hist" || p.tree_method == "auto", "tree_method=" + p.tree_method +
-               " is outside this library: only the histogram builder (tree_method=hist) is implemented");
+    TGBM_CHECK(p.tree_method == "hist" || p.tree_method == "auto" || p.tree_method == "exact", "unknown tree_method " + p.tree_method);
     const bool timing = getenv("TGBM_TIMING") != nullptr;  // phase times on stderr
     auto t_mark = std::chrono::steady_clock::now();
     auto lap = [&](const char *what) {
@@ -69,11 +69,9 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
     std::vector<std::vector<tgbm::Tree>> result;
     {
     tgbm::Booster booster(p, comm);
-    booster.init(ds);  // counts the features when the data set has not
+    booster.init(ds);  // counts the features when the data set has not, and resolves tree_method=auto (trainer.cu:19-23)
+    p.tree_method = booster.tree_method();
     lap("init");
-    if (p.tree_method == "auto") p.tree_method = booster.n_features() > 20000 ? "exact" : "hist";  // trainer.cu:19-23
-    TGBM_CHECK(p.tree_method == "hist", "tree_method=auto resolves to exact above 20000 features"
-               " (src/thundergbm/trainer.cu:19-23), which is outside this library: ask for tree_method=hist");
     const auto t0 = std::chrono::high_resolution_clock::now();
     booster.boost(p.n_trees);
     booster.sync();
@@ -100,7 +98,21 @@ std::vector<std::vector<tgbm::Tree>> train(tgbm::GBMParam &p, const tgbm::DataSe
 // of the rows (query groups stay whole), an NCCL communicator between them and a host-side meeting point
 // (tgbm::HostGroup) so that a rank that fails takes the others with it instead of leaving them in a collective.
 // The rows are sharded, not the columns, and every rank builds the same trees; rank 0's copy is returned.
+// The communicators of an in-process group outlive the call: setting one up costs a few hundred milliseconds, a
+// 100-round training on eight GPUs little more.  One set per device count, used by one call at a time, dropped when a
+// call fails (its communicators may have been aborted), never torn down at process exit.  TGBM_NO_COMM_CACHE=1 makes
+// every call build and destroy its own.
+std::mutex g_group_mutex;
+std::map<int, std::vector<tgbm::Comm *>> g_group_comms;
+
 std::vector<std::vector<tgbm::Tree>> train_in_process(tgbm::GBMParam &p, const tgbm::DataSet &ds, int n_dev) {
+    std::lock_guard<std::mutex> one_call_at_a_time(g_group_mutex);
+    const bool keep_comms = getenv("TGBM_NO_COMM_CACHE") == nullptr;
+    std::vector<tgbm::Comm *> comms(n_dev, nullptr);
+    {
+        auto it = g_group_comms.find(n_dev);
+        if (it != g_group_comms.end()) { comms = it->second; g_group_comms.erase(it); }
+    }
     int avail = 0;
     TGBM_CUDA(cudaGetDeviceCount(&avail));
     TGBM_CHECK(n_dev <= avail, "n_device = " + std::to_string(n_dev) + " but only " + std::to_string(avail) + " GPU(s) are visible");
@@ -135,10 +147,10 @@ std::vector<std::vector<tgbm::Tree>> train_in_process(tgbm::GBMParam &p, const t
     std::vector<std::thread> threads;
     for (int r = 0; r < n_dev; ++r)
         threads.emplace_back([&, r] {
-            tgbm::Comm *c = nullptr;
+            tgbm::Comm *&c = comms[r];
             try {
                 TGBM_CUDA(cudaSetDevice(r));
-                c = tgbm::comm_create(id, r, n_dev);
+                if (!c) c = tgbm::comm_create(id, r, n_dev);
                 c->host = group;
                 const int lo = row_lo[r], hi = row_lo[r + 1];
                 tgbm::DataSet shard;
@@ -161,9 +173,24 @@ std::vector<std::vector<tgbm::Tree>> train_in_process(tgbm::GBMParam &p, const t
                 errors[r] = e.what();
                 group->abandon();
             }
-            if (c) tgbm::comm_destroy(c);
         });
     for (auto &t : threads) t.join();
+    bool failed = false;
+    for (const auto &e : errors) failed = failed || !e.empty();
+    if (failed || !keep_comms) {
+        std::vector<std::thread> closers;   // every rank leaves its communicator on a thread of its own, as it joined it
+        for (int r = 0; r < n_dev; ++r)
+            closers.emplace_back([&, r] {
+                if (!comms[r]) return;
+                cudaSetDevice(r);
+                comms[r]->host.reset();
+                tgbm::comm_destroy(comms[r]);
+            });
+        for (auto &t : closers) t.join();
+    } else {
+        for (auto *c : comms) c->host.reset();
+        g_group_comms[n_dev] = comms;
+    }
     cudaSetDevice(caller_dev);
     // a rank's own failure explains more than the "another rank failed" of its peers
     std::string first, own;
@@ -215,7 +242,7 @@ tgbm::GBMParam param_from_c(const TgbmParam *cp) {
     p.hist_mode = cp->hist_mode;
     p.bagging = cp->bagging != 0; p.column_sampling_rate = cp->column_sampling_rate; p.sample_seed = cp->sample_seed;
     p.column_shards = cp->column_shards;
-    p.tree_method = "hist";
+    p.tree_method = cp->exact_builder ? "exact" : "hist";
     return p;
 }
 }  // namespace
@@ -404,7 +431,7 @@ void tgbm_default_param(TgbmParam *p) {
     p->min_child_weight = d.min_child_weight; p->lambda = d.lambda; p->gamma = d.gamma; p->learning_rate = d.learning_rate;
     p->objective = "reg:linear"; p->quant_bits = d.quant_bits; p->keep_nid = 0; p->verbose = 0; p->profile = 0; p->rank_seed = 0;
     p->hist_mode = tgbm::default_hist_mode();
-    p->bagging = 0; p->column_sampling_rate = 1.f; p->sample_seed = 0; p->column_shards = 0;
+    p->bagging = 0; p->column_sampling_rate = 1.f; p->sample_seed = 0; p->column_shards = 0; p->exact_builder = 0;
 }
 
 int tgbm_comm_unique_id(unsigned char id[128]) { return guard([&] { tgbm::comm_get_unique_id(id); }); }
