@@ -13,10 +13,11 @@
 #   2. src/thundergbm/builder/*.cu: bare `cuda::par` is ambiguous with libcu++'s
 #      ::cuda namespace under CUDA 12.x -> `thrust::cuda::par`.
 #
-# Usage: oracle/build_ref.sh [reference_dir]     (default: where the reference checkout is mounted)
+# Usage: oracle/build_ref.sh [reference_dir]     (default: $TGBM_REFERENCE_DIR, else a checkout named `reference`
+#                                                 beside this repository)
 set -euo pipefail
-REF=${1:-/root/reference}
 HERE=$(cd "$(dirname "$0")" && pwd)
+REF=${1:-${TGBM_REFERENCE_DIR:-$HERE/../../reference}}
 OUT=$HERE/_ref
 if [ ! -d "$REF/src/thundergbm" ]; then
   echo "reference tree not found at $REF; keeping prebuilt $OUT if any" >&2
