@@ -452,10 +452,16 @@ def main():
     predict = None
     if rank == 0 and not args.no_e2e:
         from thundergbm_b200.booster import predict_raw
-        trees = head['trees']
-        _, pms = predict_raw(data, trees, PARAMS['learning_rate'], float(info.base_score), timing=True)
+        trees = head['trees'][:45]   # at most 45 rounds: the size the predict figures in the design notes are quoted on
+        runs = []
+        for i in range(4):            # one untimed call (the first launch of a kernel loads it), then three timed ones
+            _, pms = predict_raw(data, trees, PARAMS['learning_rate'], float(info.base_score), timing=True)
+            if i:
+                runs.append(pms)
+        pms = float(np.median(runs))
         pbytes = data.nnz * 8.0 + data.n_rows * 8.0
-        predict = {'kernel_ms': pms, 'rows': data.n_rows, 'rounds': int(trees.shape[0]), 'gbs': pbytes / (pms * 1e-3) / 1e9 if pms > 0 else None,
+        predict = {'kernel_ms': pms, 'calls_ms': runs, 'rows': data.n_rows, 'rounds': int(trees.shape[0]),
+                   'gbs': pbytes / (pms * 1e-3) / 1e9 if pms > 0 else None,
                    'frac_of_hbm_peak': pbytes / (pms * 1e-3) / 1e9 / peak if pms > 0 else None}
 
     # ---- end to end through the reference's C entry point with host buffers ----------------------

@@ -106,8 +106,13 @@ def test_errors_leave_model_null(gpu, cases):
     model = C.c_void_p(123)
     nc = C.c_int(1); per = C.c_int(0); gl = (C.c_float * 4)()
     lib.sparse_train_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(y), 5, 2, 1, 1.0, 1.0, 1.0, 64, 0, 1.0, 0, 1, 0.3,
-                            b'reg:linear', C.byref(nc), b'exact', C.byref(model), C.byref(per), gl, None, 0)
-    assert model.value is None and b'hist' in lib.tgbm_last_error()
+                            b'reg:linear', C.byref(nc), b'approx', C.byref(model), C.byref(per), gl, None, 0)
+    assert model.value is None and b'tree_method' in lib.tgbm_last_error()
+    # the exact builder runs on one GPU only
+    model = C.c_void_p(123)
+    lib.sparse_train_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(y), 5, 2, 1, 1.0, 1.0, 1.0, 64, 0, 1.0, 0, 1, 0.3,
+                            b'reg:nonsense', C.byref(nc), b'exact', C.byref(model), C.byref(per), gl, None, 0)
+    assert model.value is None and b'objective' in lib.tgbm_last_error()
 
 
 def test_python_mirror_classes(gpu, cases):

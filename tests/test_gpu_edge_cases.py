@@ -191,3 +191,37 @@ def test_predict_raw_special_values(gpu, orc, n_features):
     got = predict_raw(dt, trees, 0.3, base)
     want = orc.predict_raw(dt, trees, 0.3, base, n_features=n_features + 3)
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize('shuffle', [False, True])
+def test_predict_raw_dense_rows(gpu, orc, shuffle):
+    """A dense matrix handed over as CSR (every row stores all 28 features) takes the one-thread-per-row conversion to
+    threshold ranks; a row whose columns are not 0 .. F-1 in order sends the whole call back to the general kernel.
+    Values on thresholds, their float neighbours, zeros of both signs, +-inf and NaN included.  Bit-identical to the
+    oracle either way."""
+    from thundergbm_b200.booster import Booster, predict_raw
+    from thundergbm_b200.synth import CsrData, higgs_like
+    d = higgs_like(20_000, seed=5)
+    b = Booster(d, objective='binary:logistic', depth=8, n_trees=10, learning_rate=0.3, max_num_bin=255)
+    b.boost(10)
+    trees, base = b.trees(), b.info.base_score
+    b.close()
+    F = d.n_cols
+    rng = np.random.default_rng(17)
+    thr = trees['split_value'][(trees['is_valid'] != 0) & (trees['is_leaf'] == 0)]
+    pool = np.concatenate([thr, np.nextafter(thr, np.float32(np.inf)), np.nextafter(thr, np.float32(-np.inf)),
+                           np.array([0.0, -0.0, np.inf, -np.inf, np.nan, 1e30, -1e30], np.float32)]).astype(np.float32)
+    m = 6001
+    x = d.val[:m * F].reshape(m, F).copy()
+    special = rng.random(x.shape) < 0.2
+    x[special] = pool[rng.integers(0, pool.size, int(special.sum()))]
+    cols = np.tile(np.arange(F, dtype=np.int32), m).reshape(m, F)
+    rp = (np.arange(m + 1) * F).astype(np.int32)
+    ordered = CsrData(m, F, rp, cols.reshape(-1).copy(), x.reshape(-1).astype(np.float32), np.zeros(m, np.float32))
+    want = orc.predict_raw(ordered, trees, 0.3, base, n_features=F)   # (the oracle looks columns up by binary search)
+    if shuffle:                                   # the same data with two entries of one row stored the other way round
+        cols[m // 2, [3, 11]] = cols[m // 2, [11, 3]]
+        x[m // 2, [3, 11]] = x[m // 2, [11, 3]]
+    dt = CsrData(m, F, rp, cols.reshape(-1), x.reshape(-1).astype(np.float32), np.zeros(m, np.float32))
+    got = predict_raw(dt, trees, 0.3, base)
+    assert np.array_equal(got, want)

@@ -26,10 +26,13 @@ def _worker(rank, world, port, case, q):
     uid = [Comm.unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
     comm = Comm(uid[0], rank, world)
+    case, _, extra = case.partition('@')
     make, params = CASES[case]
     d = make()
     kw = {k: v for k, v in params.items() if k != 'tree_method'}
     kw['n_trees'] = min(kw['n_trees'], 4)
+    if extra.startswith('column_shards='):
+        kw['column_shards'] = int(extra.split('=')[1])
     lo, hi = d.n_rows * rank // world, d.n_rows * (rank + 1) // world
     if d.group.size:  # cut at query-group boundaries
         ends = np.cumsum(d.group)
@@ -53,16 +56,22 @@ def _worker(rank, world, port, case, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize('case', ['c2_higgs_small', 'c3_covtype_small', 'fixture_bin', 'fixture_rank', 'c5_mslr_small'])
+@pytest.mark.parametrize('case', ['c2_higgs_small', 'c3_covtype_small', 'fixture_bin', 'fixture_rank', 'c5_mslr_small',
+                                  'c2_higgs_small@column_shards=3'])
 def test_two_gpus_equal_one_gpu(gpu, cases, case):
+    """(`@column_shards=3`: the reference's column-sharded builder as it would run on three devices, computed on two
+    row-sharded GPUs: its cut points need the multiplicity of every value over all ranks.)"""
     import torch
     import torch.multiprocessing as mp
     if torch.cuda.device_count() < 2:
         pytest.skip('needs 2 GPUs')
     from thundergbm_b200.booster import Booster
-    d, params = cases(case)
+    name, _, extra = case.partition('@')
+    d, params = cases(name)
     kw = {k: v for k, v in params.items() if k != 'tree_method'}
     kw['n_trees'] = min(kw['n_trees'], 4)
+    if extra.startswith('column_shards='):
+        kw['column_shards'] = int(extra.split('=')[1])
     b = Booster(d, **kw)
     b.boost(kw['n_trees'])
     want, want_m = b.trees().tobytes(), b.metrics().tolist()

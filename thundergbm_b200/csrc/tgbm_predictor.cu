@@ -298,15 +298,27 @@ constexpr int RK_THREADS = 256;
 // CSR values -> ranks.  A block owns RK_ROWS consecutive rows = one contiguous piece of the CSR arrays; its warps read
 // that piece 32 values at a time (coalesced) and find the row of every value in the block's row pointers: a 32-ary
 // search for the warp's first value, then a walk over the few row boundaries inside the warp's 32 values.
-template <bool DENSE_PATH>
+// SMEM_THR: the thresholds sit in shared memory, 256 per feature padded with +inf at a stride of 257 floats (lanes on
+// different features then hit different banks at every step), and the search is eight branch-free steps.
+constexpr int RK_THR_STRIDE = 257;
+template <bool DENSE_PATH, bool SMEM_THR>
 __global__ void __launch_bounds__(RK_THREADS)
 k_rank_rows(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F, int Fpad,
             const int *__restrict__ thr_ptr, const float *__restrict__ thr, unsigned char *__restrict__ bins) {
     __shared__ int s_rp[RK_ROWS + 1];
-    const int row0 = blockIdx.x * RK_ROWS;
+    extern __shared__ float s_thr[];   // SMEM_THR: [F][RK_THR_STRIDE]
+    if (SMEM_THR)   // once per block; the blocks are persistent
+        for (int i = threadIdx.x; i < F * 256; i += RK_THREADS) {
+            const int f = i >> 8, k = i & 255, a = thr_ptr[f];
+            s_thr[f * RK_THR_STRIDE + k] = a + k < thr_ptr[f + 1] ? thr[a + k] : INFINITY;
+        }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_tiles = (n_rows + RK_ROWS - 1) / RK_ROWS;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int row0 = tile * RK_ROWS;
+    __syncthreads();   // the previous tile's row pointers have been read (and the thresholds are in place)
     for (int i = threadIdx.x; i <= RK_ROWS; i += RK_THREADS) s_rp[i] = row_ptr[min(row0 + i, n_rows)];
     __syncthreads();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e0 = s_rp[0], e1 = s_rp[RK_ROWS];
     constexpr int UNROLL = 4;  // pieces of 32 values per warp and iteration: their loads are issued together
     for (int base0 = e0 + warp * 32 * UNROLL; base0 < e1; base0 += RK_THREADS * UNROLL) {
@@ -338,6 +350,13 @@ k_rank_rows(const int *__restrict__ row_ptr, const int *__restrict__ col, const 
                 const int first = lo;
                 int hi = thr_ptr[c + 1];
                 const int n_thr = hi - first;
+                if (SMEM_THR) {
+                    const float *t = s_thr + c * RK_THR_STRIDE;
+                    int pos = 0;
+#pragma unroll
+                    for (int step = 128; step >= 1; step >>= 1) pos += t[pos + step - 1] <= v ? step : 0;
+                    lo = first + min(pos, n_thr);   // a stored +inf passes the padding too
+                } else
                 while (lo < hi) {
                     const int mid = (lo + hi) >> 1;
                     if (thr[mid] <= v) lo = mid + 1; else hi = mid;
@@ -349,6 +368,60 @@ k_rank_rows(const int *__restrict__ row_ptr, const int *__restrict__ col, const 
             }
         }
     }
+    }
+}
+
+// Rows that store every feature, columns in order (a dense matrix handed over as CSR): one thread per row reads its F
+// values with 16-byte loads, checks its row pointer and the column ids against 0 .. F-1 as it goes (any other row raises `not_dense` and
+// the caller falls back to the kernel above) and ranks each value by an eight-step descent through the feature's
+// thresholds laid out as an implicit search tree (level by level: the lanes of a warp, all on the same feature, touch
+// consecutive words).  No row search, no address arithmetic per value: ncu counted 130 warp instructions per value in the
+// kernel above.
+constexpr int RD_THREADS = 256;
+template <bool DENSE_PATH>
+__global__ void __launch_bounds__(RD_THREADS)
+k_rank_dense_rows(const int *__restrict__ row_ptr, const int *__restrict__ col, const float *__restrict__ val, int n_rows, int F, const float *__restrict__ tree_thr,
+                  const int *__restrict__ thr_ptr, unsigned char *__restrict__ bins, int *__restrict__ not_dense) {
+    extern __shared__ float s_tree[];   // [F][256]: 255 thresholds of the feature in level order, padded with +inf
+    __shared__ int s_n[32];
+    for (int i = threadIdx.x; i < F * 256; i += RD_THREADS) s_tree[i] = tree_thr[i];
+    if (threadIdx.x < F) s_n[threadIdx.x] = thr_ptr[threadIdx.x + 1] - thr_ptr[threadIdx.x];
+    __syncthreads();
+    const int F4 = F / 4;   // F is a multiple of 4 here
+    bool bad = false;
+    for (int r = blockIdx.x * RD_THREADS + threadIdx.x; r < n_rows; r += gridDim.x * RD_THREADS) {
+        const float4 *vp = reinterpret_cast<const float4 *>(val + (size_t)r * F);
+        const int4 *cp = reinterpret_cast<const int4 *>(col + (size_t)r * F);
+        bad |= row_ptr[r] != r * F;
+        uint32_t out[8] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+            if (q < F4) {
+                const float4 v4 = vp[q];
+                const int4 c4 = cp[q];
+                bad |= c4.x != 4 * q || c4.y != 4 * q + 1 || c4.z != 4 * q + 2 || c4.w != 4 * q + 3;
+                const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+                uint32_t word = 0;
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const int f = 4 * q + k;
+                    const float *t = s_tree + f * 256;
+                    int pos = 0;
+#pragma unroll
+                    for (int step = 0; step < 8; ++step) pos = 2 * pos + (t[pos] <= v[k] ? 2 : 1);
+                    int rank = min(pos - 255, s_n[f]);   // a stored +inf passes the padding too
+                    if (DENSE_PATH) { if (!(v[k] < INFINITY)) rank = 255; }
+                    else if (v[k] != v[k]) rank = s_n[f];
+                    word |= (uint32_t)rank << (8 * k);
+                }
+                out[q] = word;
+            }
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(bins + (size_t)r * 32);
+        dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+        dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) *not_dense = 1;
 }
 
 constexpr int PR_THREADS = 512;
@@ -437,6 +510,115 @@ k_predict_ranks(const unsigned char *__restrict__ bins, int Fpad, int F, int n_r
 #pragma unroll
                 for (int j = 0; j < RPT; ++j) {
                     const int i = tile * ROWS + j * PR_THREADS + (int)threadIdx.x;
+                    if (i >= n_rows) continue;
+                    if (last) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
+                    else partial[(size_t)t * n_rows + i] = DENSE_PATH ? dsum[j] : (double)fsum[j];
+                }
+            }
+        }
+    }
+}
+
+// ---- traversal on two planes of ranks (rows of at most 32 features) --------------------------------------------------
+// The walk above is bound by instruction issue; this one strips the step down to: node (8 bytes), word, byte, compare,
+// index.  Three things make that possible.  (1) Every tree is completed to its full depth on the host: below a leaf
+// that sits above the last level the nodes pass to the left and the leftmost leaf of the subtree carries the weight,
+// so a walk always takes `depth` steps and no step tests for a leaf.  (2) A tile keeps TWO planes of rank words in
+// shared memory, the ranks b and the ranks rotated by one, (b + 1) & 255: a node whose missing values go right
+// compares b <= t on the first plane (missing = 255 fails), a node whose missing values go left compares
+// (b + 1) & 255 <= t + 1 on the second (missing = 0 passes) -- the default direction costs no instruction.
+// (3) A node is ONE 32-bit word: the byte-permute selector that moves the feature's byte into the TOP byte of a zero
+// word (bits 0-15, used as they are), the index of (plane, word) (16-20) and the threshold in the top byte (24-31):
+// `permuted <= node` as unsigned words then IS `byte <= threshold` (the lower 24 bits can only help the right-hand
+// side of a tie it already wins), so no field is extracted for the comparison.  ncu: 17.6 warp instructions per row
+// and level with fields to extract, issue slots 71 % busy, 1.4 shared-memory wavefronts per read.
+typedef unsigned PlaneNode;
+__host__ __device__ inline PlaneNode plane_node(unsigned byte, unsigned threshold, unsigned plane_word) {
+    return ((byte << 12) | 0x0444u) | (plane_word << 16) | (threshold << 24);
+}
+constexpr int PL_THREADS = 1024;   // ncu, 512 threads x 4 rows: 4 warps per scheduler, issue slots 60 % busy, stalls on shared-memory
+constexpr int PL_RPT = 2;          // reads and on dependent arithmetic: the same tile with twice the warps and half the rows each
+constexpr int PL_ROWS = PL_THREADS * PL_RPT;
+constexpr int PL_WORDS = 9;  // eight words of a 32-byte row + one word of absent marks per plane
+
+template <bool DENSE_PATH>
+__global__ void __launch_bounds__(PL_THREADS)
+k_predict_planes(const unsigned char *__restrict__ bins, int Fpad, int n_rows, const PlaneNode *__restrict__ model_nodes,
+                 const float *__restrict__ model_leaves, int n_rounds, int K, int depth, int chunk_trees, float lr, float base_score,
+                 float *__restrict__ out, double *__restrict__ partial) {
+    extern __shared__ __align__(16) unsigned char pl_sm[];
+    constexpr int RPT = PL_RPT, ROWS = PL_ROWS;
+    uint32_t *words = reinterpret_cast<uint32_t *>(pl_sm);                       // [2][9][ROWS]
+    const int n_inner = (1 << depth) - 1, n_leaf = 1 << depth;
+    PlaneNode *tnodes = reinterpret_cast<PlaneNode *>(words + 2 * PL_WORDS * ROWS);   // [chunk_trees][n_inner]
+    float *tleaves = reinterpret_cast<float *>(tnodes + (size_t)chunk_trees * n_inner);  // [chunk_trees][n_leaf]
+    const int n_tiles = (n_rows + ROWS - 1) / ROWS;
+    for (int i = threadIdx.x; i < ROWS; i += PL_THREADS) {
+        words[(PL_WORDS - 1) * ROWS + i] = 0xffffffffu;         // absent feature: rank 255 ...
+        words[(2 * PL_WORDS - 1) * ROWS + i] = 0u;              // ... and its rotation
+    }
+    for (int t = 0; t < K; ++t) {
+        for (int r0 = 0; r0 < n_rounds; r0 += chunk_trees) {
+            const int nc = min(chunk_trees, n_rounds - r0);
+            const bool first = r0 == 0, last = r0 + nc >= n_rounds;
+            __syncthreads();  // the previous chunk's walks are over
+            for (int i = threadIdx.x; i < nc * n_inner; i += PL_THREADS)
+                tnodes[i] = model_nodes[((size_t)(r0 + i / n_inner) * K + t) * n_inner + i % n_inner];
+            for (int i = threadIdx.x; i < nc * n_leaf; i += PL_THREADS)
+                tleaves[i] = model_leaves[((size_t)(r0 + i / n_leaf) * K + t) * n_leaf + i % n_leaf];
+            __syncthreads();
+            for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+                double dsum[RPT];
+                float fsum[RPT];
+#pragma unroll
+                for (int j = 0; j < RPT; ++j) {
+                    const int slot = j * PL_THREADS + threadIdx.x;
+                    const int i = min(tile * ROWS + slot, n_rows - 1);
+                    const uint4 a = reinterpret_cast<const uint4 *>(bins + (size_t)i * Fpad)[0], b = reinterpret_cast<const uint4 *>(bins + (size_t)i * Fpad)[1];
+                    const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {  // a thread spreads out its own rows and reads only them back: no barrier needed
+                        words[k * ROWS + slot] = w[k];
+                        words[(PL_WORDS + k) * ROWS + slot] = __vadd4(w[k], 0x01010101u);
+                    }
+                    dsum[j] = base_score; fsum[j] = base_score;
+                    if (!first) { const double p = partial[(size_t)t * n_rows + i]; dsum[j] = p; fsum[j] = (float)p; }
+                }
+                for (int c = 0; c < nc; ++c) {
+                    const PlaneNode *nd = tnodes + (size_t)c * n_inner;
+                    unsigned cur[RPT];
+#pragma unroll
+                    for (int j = 0; j < RPT; ++j) cur[j] = 0;
+                    auto level = [&]() {
+                        PlaneNode n[RPT];
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j) n[j] = nd[cur[j]];
+                        uint32_t w[RPT];
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j)   // [(plane, word)][row slot]
+                            w[j] = words[((n[j] >> 16) & 0xffu) * (unsigned)ROWS + (unsigned)(j * PL_THREADS) + threadIdx.x];
+#pragma unroll
+                        for (int j = 0; j < RPT; ++j)
+                            cur[j] = 2 * cur[j] + (__byte_perm(w[j], 0u, n[j]) <= n[j] ? 1 : 2);
+                    };
+                    if (depth == 8) {   // the usual depth, unrolled
+#pragma unroll
+                        for (int lvl = 0; lvl < 8; ++lvl) level();
+                    } else {
+#pragma unroll 1
+                        for (int lvl = 0; lvl < depth; ++lvl) level();
+                    }
+                    const float *lw = tleaves + (size_t)c * n_leaf - n_inner;
+#pragma unroll
+                    for (int j = 0; j < RPT; ++j) {
+                        const float wt = lw[cur[j]];
+                        if (DENSE_PATH) dsum[j] += (double)__fmul_rn(lr, wt);
+                        else fsum[j] = __fmaf_rn(lr, wt, fsum[j]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < RPT; ++j) {
+                    const int i = tile * ROWS + j * PL_THREADS + (int)threadIdx.x;
                     if (i >= n_rows) continue;
                     if (last) out[(size_t)t * n_rows + i] = DENSE_PATH ? (float)(0.0 + dsum[j]) : fsum[j];
                     else partial[(size_t)t * n_rows + i] = DENSE_PATH ? dsum[j] : (double)fsum[j];
@@ -561,6 +743,42 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
             }
         }
     }
+    // complete trees for the two-plane walk (rows of at most 32 features; TGBM_PREDICT_RANKS=1 keeps the walk above)
+    const bool planes = ranks && F <= 32 && depth >= 1 && depth <= 12 && getenv("TGBM_PREDICT_RANKS") == nullptr;
+    std::vector<PlaneNode> pl_nodes;
+    std::vector<float> pl_leaves;
+    const int n_inner = (1 << depth) - 1, n_leaf = 1 << depth;
+    if (planes) {
+        pl_nodes.resize((size_t)n_rounds * K * n_inner);
+        pl_leaves.assign((size_t)n_rounds * K * n_leaf, 0.f);
+        const PlaneNode pass = plane_node(0, 255, PL_WORDS - 1);   // absent word of plane 0: 255 <= 255, left
+        for (int tr = 0; tr < n_rounds * K; ++tr) {
+            const RNode *src = rflat.data() + (size_t)tr * n_nodes;
+            PlaneNode *dn = pl_nodes.data() + (size_t)tr * n_inner;
+            float *dl = pl_leaves.data() + (size_t)tr * n_leaf;
+            // carry[i]: the node inherits a leaf from above (1) with weight w[i], or lies off every path (2)
+            std::vector<unsigned char> carry(n_nodes, 0);
+            std::vector<float> w(n_nodes, 0.f);
+            for (int i = 0; i < n_nodes; ++i) {
+                const bool leaf = carry[i] != 0 || (src[i].flags & 0x200);
+                const float wt = carry[i] == 1 ? w[i] : carry[i] == 2 ? 0.f : src[i].weight;
+                if (i >= n_inner) { dl[i - n_inner] = leaf ? wt : 0.f; continue; }
+                if (leaf) {
+                    dn[i] = pass;
+                    carry[2 * i + 1] = carry[i] == 2 ? 2 : 1; w[2 * i + 1] = wt;
+                    carry[2 * i + 2] = 2;
+                    continue;
+                }
+                const int fl = src[i].flags;
+                const unsigned word = (unsigned)fl >> 16, byte = (((unsigned)fl >> 10) & 31u) / 8u, t = (unsigned)fl & 0xffu;
+                const bool default_right = fl & 0x100;
+                // missing goes right: plane 0, rank <= t; missing goes left: plane 1 (ranks rotated by one), <= t + 1
+                dn[i] = plane_node(byte, default_right ? t : t + 1, word + (default_right ? 0u : (unsigned)PL_WORDS));
+            }
+        }
+    }
+    DevBuf<PlaneNode> d_pl_nodes;
+    DevBuf<float> d_pl_leaves;
     DevBuf<int> d_thr_ptr;
     DevBuf<float> d_thr;
     DevBuf<RNode> d_rmodel;
@@ -574,6 +792,15 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
         TGBM_CUDA(cudaMemcpyAsync(d_rmodel.p, rflat.data(), sizeof(RNode) * rflat.size(), cudaMemcpyHostToDevice, st));
         const size_t rk_rows_bytes = F <= 32 ? sizeof(uint32_t) * 9 * PR_ROWS : 0;
         rk_chunk = (int)std::min<size_t>((size_t)n_rounds, ((size_t)(216 * 1024) - rk_rows_bytes) / (sizeof(RNode) * (size_t)n_nodes));
+        if (planes) {
+            d_pl_nodes.alloc(pl_nodes.size()); d_pl_leaves.alloc(pl_leaves.size());
+            TGBM_CUDA(cudaMemcpyAsync(d_pl_nodes.p, pl_nodes.data(), sizeof(PlaneNode) * pl_nodes.size(), cudaMemcpyHostToDevice, st));
+            TGBM_CUDA(cudaMemcpyAsync(d_pl_leaves.p, pl_leaves.data(), sizeof(float) * pl_leaves.size(), cudaMemcpyHostToDevice, st));
+            const size_t per_tree = sizeof(PlaneNode) * (size_t)n_inner + sizeof(float) * (size_t)n_leaf;
+            const size_t row_bytes = sizeof(uint32_t) * 2 * PL_WORDS * PL_ROWS;
+            rk_chunk = (int)std::min<size_t>((size_t)n_rounds, ((size_t)(224 * 1024) - row_bytes) / per_tree);
+            TGBM_CHECK(rk_chunk >= 1, "a tree of this depth does not fit beside a tile of rows");
+        }
         if (rk_chunk < n_rounds) d_partial.alloc((size_t)N * K);
     }
     const bool tiled = heap_ok && !ranks;
@@ -586,11 +813,59 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     if (tiled) tiles(true);  // scratch for the running sums is allocated here, outside the timed kernel
     if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
     if (tiled) done = tiles(false);
+    // dense fast path of the conversion: every row stores F values (checked here on the host copy of the row pointers;
+    // the kernel checks the column ids), F a multiple of 4 up to 32
+    bool dense_rows = ranks && planes && F % 4 == 0 && (size_t)N * F == nnz && getenv("TGBM_PREDICT_RANKS") == nullptr;
+    // (whether row i really starts at i * F and holds the columns 0 .. F-1 is checked by the kernel, row by row)
+    DevBuf<float> d_tree_thr;
+    DevBuf<int> d_not_dense;
+    if (dense_rows) {
+        std::vector<float> tree((size_t)F * 256, INFINITY);
+        for (int f = 0; f < F; ++f) {
+            std::vector<float> sorted(255, INFINITY);
+            std::copy(thr.begin() + thr_ptr[f], thr.begin() + thr_ptr[f + 1], sorted.begin());
+            // node k of the implicit tree holds the middle of its range; children 2k+1 (left half), 2k+2 (right half)
+            struct Range { int k, lo, hi; };
+            std::vector<Range> todo{{0, 0, 255}};
+            while (!todo.empty()) {
+                const Range g = todo.back();
+                todo.pop_back();
+                if (g.lo >= g.hi) continue;
+                const int mid = (g.lo + g.hi) / 2;
+                tree[(size_t)f * 256 + g.k] = sorted[mid];
+                todo.push_back({2 * g.k + 1, g.lo, mid});
+                todo.push_back({2 * g.k + 2, mid + 1, g.hi});
+            }
+        }
+        d_tree_thr.alloc(tree.size()); d_not_dense.alloc(1);
+        TGBM_CUDA(cudaMemcpyAsync(d_tree_thr.p, tree.data(), sizeof(float) * tree.size(), cudaMemcpyHostToDevice, st));
+        d_not_dense.zero(st);
+    }
     if (ranks) {
+        bool converted = false;
+        if (dense_rows) {
+            const size_t tree_smem = sizeof(float) * (size_t)F * 256;
+            auto kern = dense_path ? k_rank_dense_rows<true> : k_rank_dense_rows<false>;
+            kern<<<std::min((N + RD_THREADS - 1) / RD_THREADS, num_sms * 8), RD_THREADS, tree_smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, d_tree_thr.p,
+                                                                                                      d_thr_ptr.p, d_bins.p, d_not_dense.p);
+            int h_not_dense = 0;
+            TGBM_CUDA(cudaMemcpyAsync(&h_not_dense, d_not_dense.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+            TGBM_CUDA(cudaStreamSynchronize(st));
+            converted = h_not_dense == 0;
+        }
+        if (!converted) {
         TGBM_CUDA(cudaMemsetAsync(d_bins.p, MISSING_BIN, d_bins.bytes(), st));
-        const int rk_blocks = (N + RK_ROWS - 1) / RK_ROWS;
-        if (dense_path) k_rank_rows<true><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
-        else k_rank_rows<false><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+        const int rk_blocks = std::min((N + RK_ROWS - 1) / RK_ROWS, num_sms * 8);   // persistent: a block walks several tiles of rows
+        const size_t thr_smem = sizeof(float) * (size_t)F * RK_THR_STRIDE;
+        const bool smem_thr = thr_smem <= 40 * 1024 && getenv("TGBM_PREDICT_RANKS") == nullptr;
+        if (smem_thr) {
+            if (dense_path) k_rank_rows<true, true><<<rk_blocks, RK_THREADS, thr_smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+            else k_rank_rows<false, true><<<rk_blocks, RK_THREADS, thr_smem, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+        } else {
+            if (dense_path) k_rank_rows<true, false><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+            else k_rank_rows<false, false><<<rk_blocks, RK_THREADS, 0, st>>>(d_rp.p, d_col.p, d_val.p, N, F, Fpad, d_thr_ptr.p, d_thr.p, d_bins.p);
+        }
+        }
         const size_t rk_smem = sizeof(RNode) * (size_t)n_nodes * rk_chunk + (F <= 32 ? sizeof(uint32_t) * 9 * PR_ROWS : 0);
         const int grid = std::max(1, std::min((N + PR_ROWS - 1) / PR_ROWS, num_sms));
         if (getenv("TGBM_TIMING")) {  // how the time splits between the conversion and the walk
@@ -605,7 +880,18 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
             kern<<<grid, PR_THREADS, rk_smem, st>>>(d_bins.p, Fpad, F, N, d_rmodel.p, n_rounds, K, n_nodes, depth, rk_chunk, learning_rate, base_score,
                                              d_out.p, d_partial.p);
         };
-        if (dense_path) { if (F <= 32) go(k_predict_ranks<true, true>); else go(k_predict_ranks<true, false>); }
+        if (planes) {
+            const size_t pl_smem = sizeof(uint32_t) * 2 * PL_WORDS * PL_ROWS +
+                                   (sizeof(PlaneNode) * (size_t)n_inner + sizeof(float) * (size_t)n_leaf) * rk_chunk;
+            const int pl_grid = std::max(1, std::min((N + PL_ROWS - 1) / PL_ROWS, num_sms));
+            auto go_planes = [&](auto kern) {
+                TGBM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pl_smem));
+                kern<<<pl_grid, PL_THREADS, pl_smem, st>>>(d_bins.p, Fpad, N, d_pl_nodes.p, d_pl_leaves.p, n_rounds, K, depth, rk_chunk, learning_rate,
+                                                          base_score, d_out.p, d_partial.p);
+            };
+            if (dense_path) go_planes(k_predict_planes<true>); else go_planes(k_predict_planes<false>);
+        }
+        else if (dense_path) { if (F <= 32) go(k_predict_ranks<true, true>); else go(k_predict_ranks<true, false>); }
         else { if (F <= 32) go(k_predict_ranks<false, true>); else go(k_predict_ranks<false, false>); }
         done = true;
     }
