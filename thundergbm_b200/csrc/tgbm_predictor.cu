@@ -707,7 +707,10 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     std::vector<int> thr_ptr;
     std::vector<float> thr;
     std::vector<RNode> rflat;
-    bool ranks = heap_ok && getenv("TGBM_PREDICT_FLOAT") == nullptr && sizeof(RNode) * (size_t)n_nodes * std::min(8, n_rounds) <= 140 * 1024 && F < 65536;
+    // (the rank bytes are a dense N x Fpad matrix: not for wide sparse data, where it would dwarf the CSR itself)
+    const size_t rank_bytes = (size_t)N * (size_t)((F + 31) / 32 * 32);
+    bool ranks = heap_ok && getenv("TGBM_PREDICT_FLOAT") == nullptr && sizeof(RNode) * (size_t)n_nodes * std::min(8, n_rounds) <= 140 * 1024 && F < 65536 &&
+                 rank_bytes <= std::max<size_t>((size_t)64 << 20, 8 * nnz);
     if (ranks) {
         std::vector<std::vector<float>> per(F);
         for (size_t i = 0; i < flat.size(); ++i) {
