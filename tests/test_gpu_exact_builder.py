@@ -117,3 +117,61 @@ def test_fp32_follows_the_reference(gpu, orc, cases, name):
     r.pop('parted')
     assert r['compared'] >= 1 and within_noise(r, hard=8.0), (name, r['worst_gain'], r['worst_weight'], r['bad_gain'], r['bad_weight'])
     b.close()
+
+
+@pytest.mark.parametrize('n,f,density', [(1, 3, 1.0), (2, 1, 1.0), (33, 5, 0.5), (1000, 40, 0.3), (1025, 31, 1.0)])
+def test_ragged_shapes(gpu, orc, n, f, density):
+    """One row, one feature, rows without any stored value, features nobody stores."""
+    from thundergbm_b200 import synth
+    rng = np.random.default_rng(n + f)
+    x = np.round(rng.standard_normal((n, f)) * 3).astype(np.float32) / 2      # few distinct values: long runs of equal values
+    x[rng.random((n, f)) > density] = 0
+    if not x.any():
+        x[0, 0] = 1.0
+    y = (x[:, 0] - x[:, 1 % f] + 0.3 * rng.standard_normal(n)).astype(np.float32)
+    d = synth.dense_to_csr(x, y)
+    p = dict(objective='reg:linear', depth=4, n_trees=3, max_num_bin=255, learning_rate=0.5, tree_method='exact')
+    o = orc.train(d, hist_mode=1, keep_nid=1, **p)
+    b = _booster(d, p, keep_nid=1, hist_mode='exact')
+    b.boost(3)
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid) and np.array_equal(b.ypred(), o.ypred)
+    b.close()
+
+
+@pytest.mark.parametrize('depth', [1, 10])
+def test_depth_extremes(gpu, orc, cases, depth):
+    d, params = cases('fixture_bin')
+    p = {**params, 'depth': depth, 'n_trees': 2, 'tree_method': 'exact'}
+    o = orc.train(d, hist_mode=1, keep_nid=1, **p)
+    b = _booster(d, p, keep_nid=1, hist_mode='exact')
+    b.boost(2)
+    assert b.trees().tobytes() == o.trees.tobytes()
+    assert np.array_equal(b.nid(), o.nid)
+    b.close()
+
+
+def test_cli_with_tree_method_exact(gpu, tmp_path):
+    """thundergbm-train with tree_method=exact in the conf: split values are midpoints of stored values."""
+    import os
+    import subprocess
+    from thundergbm_b200 import synth
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d = synth.dense_regression(1500, 6, seed=9)
+    data = tmp_path / 'train.txt'
+    with open(data, 'w') as fh:
+        for i in range(d.n_rows):
+            a, b = d.row_ptr[i], d.row_ptr[i + 1]
+            fh.write(f'{d.y[i]:.9g} ' + ' '.join(f'{c + 1}:{v:.9g}' for c, v in zip(d.col[a:b], d.val[a:b])) + '\n')
+    conf = tmp_path / 'run.conf'
+    conf.write_text(f'data={data}\ndepth=3\nn_trees=4\nlearning_rate=0.5\nobjective=reg:linear\ntree_method=exact\n')
+    out = subprocess.run([os.path.join(root, 'thundergbm_b200', 'bin', 'thundergbm-train'), str(conf)], cwd=tmp_path,
+                         capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert '[4/4] RMSE = ' in out.stdout and os.path.exists(tmp_path / 'tgbm.model')
+    from pack_golden import read_model, tree_view
+    t = tree_view(read_model(str(tmp_path / 'tgbm.model'))['trees'])
+    root_node = t[0, 0][0]
+    col = np.sort(d.val[d.col == root_node['split_feature_id']])
+    mids = ((col[1:] + col[:-1]) * np.float32(0.5)).astype(np.float32)
+    assert root_node['split_bid'] == 0 and np.any(mids == root_node['split_value'])
