@@ -138,6 +138,32 @@ def reg_base(d):
     return float(np.mean(d.y))
 
 
+def test_python_mirror_cv_and_tree_arrays(gpu, cases):
+    """cv() and the tree arrays behind get_shap_trees() of the reference's wrapper (python/thundergbm/thundergbm.py:223-351)."""
+    from thundergbm_b200.thundergbm import TGBMClassifier, TGBMRanker, TGBMRegressor
+    import scipy.sparse as sp
+    d, _ = cases('fixture_bin')
+    X = sp.csr_matrix((d.val, d.col, d.row_ptr), shape=(d.n_rows, d.n_cols))
+    clf = TGBMClassifier(depth=4, n_trees=5, learning_rate=0.5, verbose=0, objective='binary:logistic')
+    res = clf.cv(X, d.y, nfold=3, seed=1)
+    assert set(res) == {'train-accuracy-mean', 'train-accuracy-std', 'test-accuracy-mean', 'test-accuracy-std'}
+    assert 0.7 < res['test-accuracy-mean'] <= res['train-accuracy-mean'] + 0.05 <= 1.05
+    trees = clf.get_trees()
+    assert len(trees) == 5 and all(t['children_left'].shape == (31,) for t in trees)
+    root = trees[0]
+    assert root['children_left'][0] == 1 and root['children_right'][0] == 2 and root['children_default'][0] in (1, 2)
+    leaves = root['children_left'] == -1
+    assert leaves.any() and np.all(root['value'][~leaves] == 0)
+    d1, _ = cases('c1_dense_reg')
+    X1 = sp.csr_matrix((d1.val, d1.col, d1.row_ptr), shape=(d1.n_rows, d1.n_cols))
+    reg = TGBMRegressor(depth=4, n_trees=5, learning_rate=0.5, verbose=0)
+    # caller-made folds; predict() leaves the base score out, so the "RMSE" (a mean squared error) is large but finite
+    folds = [(np.arange(0, 8000), np.arange(8000, 10000)), (np.arange(2000, 10000), np.arange(0, 2000))]
+    res = reg.cv(X1, d1.y, folds=folds)
+    assert np.isfinite(res['test-RMSE-mean']) and res['train-RMSE-std'] >= 0
+    assert TGBMRanker(verbose=0).cv(X1, d1.y) is None
+
+
 def test_cli_train_and_predict(gpu, tmp_path):
     """thundergbm-train <conf> writes ./tgbm.model; thundergbm-predict <conf> reads it and logs the metric."""
     import subprocess

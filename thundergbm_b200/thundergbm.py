@@ -142,6 +142,57 @@ class TGBMModel:
         return trees
 
 
+    def cv(self, X, y, folds=None, nfold=5, shuffle=True, seed=0):
+        """k-fold cross validation as the reference's wrapper does it (python/thundergbm/thundergbm.py:223-282): rows
+        permuted with RandomState(seed), folds of int(n / nfold) consecutive entries of the permutation (or the
+        caller's (train_ids, test_ids) pairs), fit + predict per fold; accuracy for classifiers, mean squared error for
+        regressors (which the reference reports under the key 'RMSE'); not for rankers.  Returns, and keeps in
+        `eval_res`, mean and sample standard deviation of the train and test scores."""
+        if self._impl == 'ranker':
+            print('Cross-validation for ## Ranker ## have not been supported yep..')
+            return None
+        import statistics
+        X = X.tocsr() if sp.issparse(X) else sp.csr_matrix(X)
+        y = np.asarray(y, np.float32)
+        n = X.shape[0]
+        if folds is not None:
+            train_ids, test_ids = [f[0] for f in folds], [f[1] for f in folds]
+            nfold = len(train_ids)
+        else:
+            order = np.random.RandomState(seed).permutation(n) if shuffle else np.arange(n)
+            step = int(n / nfold)
+            test_ids = [order[i:i + step] for i in range(0, n, step)]
+            train_ids = [np.concatenate([test_ids[i] for i in range(nfold) if i != k]) for k in range(nfold)]
+        train_scores, test_scores = [], []
+        for k in range(nfold):
+            self.fit(X[train_ids[k], :], y[train_ids[k]])
+            pairs = ((self.predict(X[train_ids[k], :]), y[train_ids[k]]), (self.predict(X[test_ids[k], :]), y[test_ids[k]]))
+            for (pred, truth), scores in zip(pairs, (train_scores, test_scores)):
+                if self._impl == 'classifier':
+                    scores.append(float(np.mean(np.asarray(pred) == truth)))
+                else:
+                    scores.append(float(np.mean((np.asarray(pred, np.float64) - truth) ** 2)))
+        name = 'accuracy' if self._impl == 'classifier' else 'RMSE'
+        self.eval_res = {f'train-{name}-mean': statistics.mean(train_scores), f'train-{name}-std': statistics.stdev(train_scores),
+                         f'test-{name}-mean': statistics.mean(test_scores), f'test-{name}-std': statistics.stdev(test_scores)}
+        print('mean train %s:%.6f+%.6f' % (name, self.eval_res[f'train-{name}-mean'], self.eval_res[f'train-{name}-std']))
+        print('mean test %s:%.6f+%.6f' % (name, self.eval_res[f'test-{name}-mean'], self.eval_res[f'test-{name}-std']))
+        return self.eval_res
+
+    def get_shap_trees(self):
+        """The trees as `shap.explainers.tree.Tree` objects (python/thundergbm/thundergbm.py:284-351): one tree per
+        round, leaf values as a column.  Needs the `shap` package; `get_trees()` gives the same arrays without it."""
+        if self.objective != 'binary:logistic' and self.tree_per_iter != 1:
+            raise RuntimeError('not supported yet!')
+        import shap.explainers.tree as shap_tree
+        out = []
+        for t in self.get_trees()[::self.tree_per_iter]:
+            t = dict(t)
+            t['value'] = t['value'].reshape(-1, 1)
+            out.append(shap_tree.Tree(t))
+        return out
+
+
 class TGBMClassifier(TGBMModel):
     _impl = 'classifier'
 
