@@ -92,7 +92,7 @@ def test_two_gpus_equal_one_gpu(gpu, cases, case):
             assert all(0.0 < v <= 1.0 for v in metrics)
 
 
-def _scikit_train(d, n_device, depth, n_trees, objective, lr):
+def _scikit_train(d, n_device, depth, n_trees, objective, lr, tree_method=b'hist'):
     import ctypes as C
     from thundergbm_b200 import _lib
     from thundergbm_b200.booster import NODE_DTYPE
@@ -105,7 +105,7 @@ def _scikit_train(d, n_device, depth, n_trees, objective, lr):
     num_class = C.c_int(1); per_iter = C.c_int(0)
     group_label = (C.c_float * 64)()
     lib.sparse_train_scikit(d.n_rows, vp(val), vp(rp), vp(col), vp(y), depth, n_trees, n_device, 1.0, 1.0, 1.0, 255, 0, 1.0, 0, 1, lr,
-                            objective.encode(), C.byref(num_class), b'hist', C.byref(model), C.byref(per_iter), group_label,
+                            objective.encode(), C.byref(num_class), tree_method, C.byref(model), C.byref(per_iter), group_label,
                             vp(grp) if grp.size else None, int(grp.size))
     if not model.value:
         return None, lib.tgbm_last_error().decode()
@@ -132,6 +132,20 @@ def test_n_device_two_through_the_reference_entry_point(gpu, cases, case):
     two, err2 = _scikit_train(d, 2, params['depth'], 3, params['objective'], params['learning_rate'])
     assert one is not None and two is not None, (err1, err2)
     assert one == two
+
+
+def test_exact_builder_on_two_devices_is_refused_by_every_rank(gpu, cases):
+    """tree_method=exact runs on one GPU: with n_device=2 both host threads raise the same error before any collective
+    that only one of them would join, and the call returns it."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    d, params = cases('fixture_reg')
+    out, err = _scikit_train(d, 2, 3, 1, 'reg:linear', 1.0, tree_method=b'exact')
+    assert out is None and 'one GPU' in err
+    # and the next call on the same devices works (the failed call's communicators were dropped)
+    out, err = _scikit_train(d, 2, 3, 1, 'reg:linear', 1.0)
+    assert out is not None, err
 
 
 def test_n_device_beyond_the_visible_gpus_is_refused(gpu, cases):
