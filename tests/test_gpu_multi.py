@@ -134,6 +134,33 @@ def test_n_device_two_through_the_reference_entry_point(gpu, cases, case):
     assert one == two
 
 
+def test_column_builder_through_the_reference_entry_point(gpu, cases, monkeypatch):
+    """TGBM_COLUMN_BUILDER=1: sparse_train_scikit(n_device=2) gives what the reference's two-device builder computes
+    (cut points shifted and re-rounded per device, bins counting down, ...), i.e. the trees of column_shards=2 on one GPU."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs 2 GPUs')
+    from thundergbm_b200.booster import Booster
+    d, params = cases('c2_higgs_small')
+    monkeypatch.setenv('TGBM_COLUMN_BUILDER', '1')
+    two, err = _scikit_train(d, 2, params['depth'], 3, params['objective'], params['learning_rate'])
+    assert two is not None, err
+    monkeypatch.delenv('TGBM_COLUMN_BUILDER')
+    plain, err = _scikit_train(d, 2, params['depth'], 3, params['objective'], params['learning_rate'])
+    assert plain is not None and plain != two
+    b = Booster(d, objective=params['objective'], depth=params['depth'], n_trees=3, learning_rate=params['learning_rate'], column_shards=2)
+    b.boost(3)
+    t = b.trees()
+    b.close()
+    # get_a_tree's view of the first tree: children, default child, feature, threshold, value, hessian sum
+    first = np.frombuffer(two[0], np.uint8)
+    n = t.shape[2]
+    feature = first[3 * 4 * n:4 * 4 * n].view(np.int32)
+    threshold = first[4 * 4 * n:5 * 4 * n].view(np.float32)
+    assert np.array_equal(feature, t[0, 0]['split_feature_id'])
+    assert threshold.tobytes() == t[0, 0]['split_value'].tobytes()
+
+
 def test_exact_builder_on_two_devices_is_refused_by_every_rank(gpu, cases):
     """tree_method=exact runs on one GPU: with n_device=2 both host threads raise the same error before any collective
     that only one of them would join, and the call returns it."""
