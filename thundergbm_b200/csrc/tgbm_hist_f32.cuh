@@ -10,10 +10,11 @@
 // one accumulator per (node, bin) for the whole GPU, every (row, feature) pair issues one vector reduction
 // `red.global.add.v2.f32` that the L2 performs in arrival order.
 //
-// The L2 spreads addresses over its slices in chunks much larger than a cell, so the 57 KB of a single node's cells
-// keep only a few slices busy (measured: 86 G reductions/s into 8-byte cells of one node, 163 G/s with the cells
-// 64 bytes apart, 181 G/s into the compact cells of 64 nodes).  Levels with few histograms therefore write their
-// cells `cell_stride` float2 apart; the evaluation kernels read them with the same stride.
+// The L2 performs the reductions that aim at one line one after the other, so cells packed 16 to a line are its
+// worst case (measured with the bare reductions of 10.5 M rows x 28: 87 G/s into 8-byte cells of one node, 165 G/s
+// with the cells 64 bytes apart, 176 G/s at 128 bytes, 190 G/s at 256 bytes, 165 G/s at 512 bytes; the same order with
+// 8 or 64 nodes).  The histograms are therefore built with their cells `cell_stride` float2 apart (32 = 256 bytes
+// wherever the spread buffer has room); the evaluation kernels read them with the same stride.
 //
 // The fixed-point kernels (k_hist, k_hist_sparse) remain the deterministic mode.
 #pragma once
@@ -101,22 +102,27 @@ k_hist_f32(const unsigned char *__restrict__ bins, int Fpad, int F, const int *_
         }
     }
     __syncthreads();
-    if (stage && threadIdx.x == 0 && (int)blockIdx.x < units) issue(blockIdx.x, 0);
+    // A CTA takes a contiguous run of the unit sequence, so that at any moment the CTAs of the grid work on different
+    // nodes: with all of them on the same node (units dealt out round-robin) every reduction in flight aims at that one
+    // node's 57 KB of cells, the regime the L2 handles worst (86 G reductions/s against 181 G/s over 64 nodes).
+    const int run = (units + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int u_begin = min((int)blockIdx.x * run, units), u_end = min(u_begin + run, units);
+    if (stage && threadIdx.x == 0 && u_begin < u_end) issue(u_begin, 0);
     int n_done = 0;  // units this CTA has consumed: buffer = n_done & 1, parity = (n_done >> 1) & 1
-    for (int u = blockIdx.x; u < units; u += gridDim.x, ++n_done) {
+    for (int u = u_begin; u < u_end; ++u, ++n_done) {
         const int4 e = seq[u / PER_TILE];  // first record, records, histogram slot
         const int q = (u % PER_TILE) * F32_THREADS + threadIdx.x;
         int r = -1;
         float2 v = make_float2(0.f, 0.f);
         if (stage) {
             const int buf = n_done & 1;
-            if (threadIdx.x == 0 && u + (int)gridDim.x < units) issue(u + gridDim.x, buf ^ 1);  // one unit ahead
+            if (threadIdx.x == 0 && u + 1 < u_end) issue(u + 1, buf ^ 1);  // one unit ahead
             if (!mbar_wait(&s_bar[buf], (n_done >> 1) & 1)) { s_fail = 1; atomicCAS(&ctl->error, 0, 0x40000000 | u); }
             const int p0 = e.x + (u % PER_TILE) * F32_THREADS;
             if (q < e.y) { r = s_idx[buf][(p0 & 3) + threadIdx.x]; v = s_gh[buf][(p0 & 1) + threadIdx.x]; }
             __syncthreads();  // every thread holds its record: the buffer may be refilled two units from now
             if (s_fail) {  // leave only when the copy that is still on its way has landed (bounded as well)
-                if (threadIdx.x == 0 && u + (int)gridDim.x < units) mbar_wait(&s_bar[buf ^ 1], ((n_done + 1) >> 1) & 1);
+                if (threadIdx.x == 0 && u + 1 < u_end) mbar_wait(&s_bar[buf ^ 1], ((n_done + 1) >> 1) & 1);
                 return;
             }
             if (threadIdx.x == 0) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
