@@ -140,6 +140,10 @@ int tgbm_booster_get_labels(TgbmBooster *b, float *out);             /* n_labels
 /* hands the trained trees over as the opaque model of part 1 */
 int tgbm_booster_to_model(TgbmBooster *b, Tree **model);
 void tgbm_booster_free(TgbmBooster *b);
+/* The library's device buffers come from one memory pool per GPU that keeps what a call releases (up to
+ * TGBM_POOL_KEEP_MB megabytes, default 16384; TGBM_NO_POOL=1: plain cudaMalloc / cudaFree), so that the next call finds
+ * its memory mapped.  This gives every unused block back to the driver now. */
+void tgbm_release_device_memory(void);
 
 /* Predictor::predict_raw (src/thundergbm/predictor.cu:32-189) on node records as returned by
  * tgbm_booster_get_trees: out[t * n_rows + i] */

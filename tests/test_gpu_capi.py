@@ -254,3 +254,33 @@ def test_metric_score_entry_point(gpu, orc, cases):
         assert rc == 0, lib.tgbm_last_error()
         assert out.value == b.metrics()[-1], name
         b.close()
+
+
+def test_released_buffers_are_kept_and_given_back_on_request(gpu, cases):
+    """The library keeps the device buffers a call releases for the next call (a second training of the same shape
+    allocates nothing) and tgbm_release_device_memory returns them to the driver; the trees do not depend on it."""
+    import torch
+    from thundergbm_b200 import _lib
+    lib = _lib.lib()
+    d, _ = cases('c2_higgs_small')
+    m0 = _train(lib, d, 'binary:logistic', depth=6, n_trees=3)[0]   # loads the kernels and whatever the driver keeps per context
+    lib.model_free(C.byref(m0))
+    lib.tgbm_release_device_memory()
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    m1, _, per, _ = _train(lib, d, 'binary:logistic', depth=6, n_trees=3)
+    free1, _ = torch.cuda.mem_get_info()
+    m2, _, _, _ = _train(lib, d, 'binary:logistic', depth=6, n_trees=3)
+    free2, _ = torch.cuda.mem_get_info()
+    if not os.environ.get('TGBM_NO_POOL'):
+        assert free1 < free0            # the first call's buffers stay with the library
+        assert free2 == free1           # the second call found all of its buffers there
+    lib.tgbm_release_device_memory()
+    free3, _ = torch.cuda.mem_get_info()
+    assert free3 > free1 or os.environ.get('TGBM_NO_POOL')
+    assert free3 >= free0 - (8 << 20)   # everything is back
+    n1, n2 = C.c_int(0), C.c_int(0)
+    lib.get_n_nodes(C.byref(m1), C.byref(n1), 3, per)
+    lib.get_n_nodes(C.byref(m2), C.byref(n2), 3, per)
+    assert n1.value == n2.value
+    lib.model_free(C.byref(m1)); lib.model_free(C.byref(m2))

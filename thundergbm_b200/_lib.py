@@ -56,6 +56,8 @@ def load() -> C.CDLL:
         getattr(lib, 'tgbm_booster_' + name).argtypes = [vp, vp]
     lib.tgbm_booster_get_cuts.argtypes = [vp, vp, vp]
     lib.tgbm_booster_free.argtypes = [vp]
+    lib.tgbm_release_device_memory.argtypes = []
+    lib.tgbm_release_device_memory.restype = None
     lib.tgbm_predict_raw.argtypes = [C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, vp]
     lib.tgbm_predict_raw_timed.argtypes = [C.c_int, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_float, C.c_float, vp, vp]
     lib.tgbm_metric_score.argtypes = [C.c_char_p, C.c_int, C.c_int, vp, vp, vp, C.c_int, fp]

@@ -19,7 +19,7 @@ BIN = os.path.join(HERE, 'bin')
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
 FLAGS = ['-std=c++17', '-O3', '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-fmad=false',
          '-Xcompiler', '-fPIC,-O3', '-ccbin', '/usr/bin/g++']
-SOURCES = ['tgbm_booster.cu', 'tgbm_predictor.cu', 'tgbm_capi.cu', 'tgbm_host.cpp', 'tgbm_comm.cpp', 'tgbm_noalloc.cu']
+SOURCES = ['tgbm_booster.cu', 'tgbm_predictor.cu', 'tgbm_capi.cu', 'tgbm_host.cpp', 'tgbm_comm.cpp', 'tgbm_noalloc.cu', 'tgbm_devmem.cu']
 
 
 def _newer(target: str, deps: list[str]) -> bool:

@@ -358,6 +358,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             } catch (const std::exception &e) { local_err = e.what(); }
         }
         agree("sorting its feature values");
+        lap("  local sort + unique");
         if (multi) {
             // union of the ranks' distinct keys: all-gather (padded to the largest rank), then sort + unique again
             TGBM_CUDA(cudaMemcpyAsync(mine.p, &nu, sizeof(long long), cudaMemcpyHostToDevice, stream));
@@ -376,6 +377,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             TGBM_CUDA(cudaMemsetAsync(padded.p, 0xff, sizeof(unsigned long long) * mx, stream));
             if (nu) TGBM_CUDA(cudaMemcpyAsync(padded.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
             comm->allgather(padded.p, all.p, mx, Comm::I64, stream);
+            lap("  all-gather of the distinct keys");
             if (colb) {
                 TGBM_CUDA(cudaMemsetAsync(padded_c.p, 0, sizeof(long long) * mx, stream));
                 if (nu) TGBM_CUDA(cudaMemcpyAsync(padded_c.p, copies.p, sizeof(long long) * nu, cudaMemcpyDeviceToDevice, stream));
@@ -392,6 +394,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
                 o += hc[r];
             }
             nu = sort_unique(tot);
+            lap("  sort + unique of the union");
         }
         ukeys.alloc(std::max<long long>(nu, 1));
         if (nu) TGBM_CUDA(cudaMemcpyAsync(ukeys.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));

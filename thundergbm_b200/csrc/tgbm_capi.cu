@@ -28,15 +28,17 @@ thread_local std::string g_err;
 
 template <typename F>
 int guard(F &&f) {
+    int rc = 0;
     try {
         g_err.clear();
         f();
-        return 0;
     } catch (const std::exception &e) {
         g_err = e.what();
         if (tgbm::verbosity() >= 1) fprintf(stderr, "thundergbm: %s\n", g_err.c_str());
-        return 1;
+        rc = 1;
     }
+    tgbm::dev_trim();   // what the call released stays mapped for the next one, up to the pools' limit
+    return rc;
 }
 
 std::vector<std::vector<tgbm::Tree>> wrap_model(::Tree *model, int n_trees, int per_iter) {
@@ -543,7 +545,11 @@ int tgbm_booster_get_root_hist_f32(TgbmBooster *b, float *out) { return guard([&
 int tgbm_booster_get_quant_scale(TgbmBooster *b, double *out) { return guard([&] { auto v = b->b->get_quant_scale(); std::copy(v.begin(), v.end(), out); }); }
 int tgbm_booster_get_labels(TgbmBooster *b, float *out) { return guard([&] { std::copy(b->label.begin(), b->label.end(), out); }); }
 int tgbm_booster_to_model(TgbmBooster *b, ::Tree **model) { return guard([&] { *model = unwrap_model(b->b->get_model()); }); }
-void tgbm_booster_free(TgbmBooster *b) { delete b; }
+void tgbm_booster_free(TgbmBooster *b) {
+    delete b;
+    tgbm::dev_trim();
+}
+void tgbm_release_device_memory(void) { tgbm::dev_release_all(); }
 
 int tgbm_metric_score(const char *objective, int n_rows, int trees_per_round, const float *label, const float *raw,
                       const int *group, int num_group, float *out) {

@@ -15,6 +15,14 @@ namespace tgbm {
                                 std::to_string(__LINE__));                                                \
     } while (0)
 
+// Device memory of the library's buffers (tgbm_devmem.cu): cudaMalloc / cudaFree semantics on top of a per-device pool
+// that keeps released blocks.  dev_trim cuts what the pools hold back to their limit (the C entry points call it when
+// they return), dev_release_all gives everything unused back to the driver.
+void *dev_alloc(size_t bytes);
+void dev_free(void *p) noexcept;
+void dev_trim() noexcept;
+void dev_release_all() noexcept;
+
 // RAII device buffer; everything is allocated once at init and reused for every tree.
 template <typename T>
 struct DevBuf {
@@ -25,14 +33,14 @@ struct DevBuf {
     DevBuf &operator=(const DevBuf &) = delete;
     ~DevBuf() { release(); }
     void release() {
-        if (p) cudaFree(p);
+        if (p) dev_free(p);
         p = nullptr;
         n = 0;
     }
     void alloc(size_t count) {
         release();
         n = count;
-        if (count) TGBM_CUDA(cudaMalloc((void **)&p, sizeof(T) * count));
+        if (count) p = static_cast<T *>(dev_alloc(sizeof(T) * count));
     }
     void zero(cudaStream_t s) {
         if (n) TGBM_CUDA(cudaMemsetAsync(p, 0, sizeof(T) * n, s));
