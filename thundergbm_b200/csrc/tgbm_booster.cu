@@ -4,9 +4,12 @@
 #include "tgbm_booster.h"
 
 #include <cub/cub.cuh>
+#include <cub/device/device_merge.cuh>
+#include <cuda/std/functional>
 
 #include <algorithm>
 #include <chrono>
+#include <climits>
 #include <cmath>
 #include <cstddef>
 #include <cstdlib>
@@ -282,7 +285,7 @@ void BoosterImpl::column_builder_candidates(DevBuf<unsigned long long> &ukeys, D
 // ------------------------------------------------------------------------------------------------
 // Cut points (HistCut::get_cut_points_single, src/thundergbm/hist_cut.cu:205-286) and the bin matrix.
 // Radix sort of (feature, value) keys and DeviceSelect::Unique come from CUB; this runs once, before
-// the boosting loop.  With several ranks every rank contributes its distinct keys and all ranks
+// the boosting loop.  With several ranks every rank contributes its sorted distinct keys, all ranks merge the lists and
 // derive identical cut points from the union, so the bins equal the single-GPU ones.
 void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
     const bool timing = getenv("TGBM_TIMING") != nullptr;  // phase times of the set-up on stderr
@@ -360,7 +363,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
         agree("sorting its feature values");
         lap("  local sort + unique");
         if (multi) {
-            // union of the ranks' distinct keys: all-gather (padded to the largest rank), then sort + unique again
+            // union of the ranks' distinct keys: all-gather (padded to the largest rank), then merge (or sort) + unique
             TGBM_CUDA(cudaMemcpyAsync(mine.p, &nu, sizeof(long long), cudaMemcpyHostToDevice, stream));
             comm->allgather(mine.p, counts.p, 1, Comm::I64, stream);
             std::vector<long long> hc(comm->world);
@@ -387,14 +390,59 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             for (long long c : hc) tot += c;
             keys.alloc(std::max<long long>(tot, 1)); keys2.alloc(std::max<long long>(tot, 1));
             if (colb) { copies.alloc(std::max<long long>(tot, 1)); copies2.alloc(std::max<long long>(tot, 1)); }
-            long long o = 0;
-            for (int r = 0; r < comm->world; ++r) {
-                if (hc[r]) TGBM_CUDA(cudaMemcpyAsync(keys.p + o, all.p + (size_t)r * mx, sizeof(unsigned long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
-                if (hc[r] && colb) TGBM_CUDA(cudaMemcpyAsync(copies.p + o, all_c.p + (size_t)r * mx, sizeof(long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
-                o += hc[r];
+            if (!colb && tot < INT_MAX) {
+                // Every rank's list is sorted: the union is merged pairwise (log2 W passes over the keys) instead of
+                // radix-sorted (five passes and a histogram), then made distinct.
+                struct Run { const unsigned long long *p; long long n; };
+                std::vector<Run> runs;
+                for (int r = 0; r < comm->world; ++r)
+                    if (hc[r]) runs.push_back({all.p + (size_t)r * mx, hc[r]});
+                unsigned long long *bufs[2] = {keys.p, keys2.p};
+                int into = 0;
+                DevBuf<unsigned char> mtmp;
+                while (runs.size() > 1) {
+                    std::vector<Run> merged;
+                    unsigned long long *out = bufs[into];
+                    long long o = 0;
+                    for (size_t i = 0; i + 1 < runs.size(); i += 2) {
+                        size_t tb = 0;
+                        cub::DeviceMerge::MergeKeys(nullptr, tb, runs[i].p, (int)runs[i].n, runs[i + 1].p, (int)runs[i + 1].n, out + o,
+                                                    ::cuda::std::less<>{}, stream);
+                        if (tb > mtmp.bytes() || !mtmp.p) mtmp.alloc(std::max<size_t>(tb, 16));
+                        TGBM_CUDA(cub::DeviceMerge::MergeKeys(mtmp.p, tb, runs[i].p, (int)runs[i].n, runs[i + 1].p, (int)runs[i + 1].n, out + o,
+                                                              ::cuda::std::less<>{}, stream));
+                        merged.push_back({out + o, runs[i].n + runs[i + 1].n});
+                        o += runs[i].n + runs[i + 1].n;
+                    }
+                    if (runs.size() & 1) {
+                        const Run &last = runs.back();
+                        TGBM_CUDA(cudaMemcpyAsync(out + o, last.p, sizeof(unsigned long long) * last.n, cudaMemcpyDeviceToDevice, stream));
+                        merged.push_back({out + o, last.n});
+                    }
+                    runs.swap(merged);
+                    into ^= 1;
+                }
+                nu = 0;
+                if (!runs.empty()) {
+                    size_t tb = 0;
+                    cub::DeviceSelect::Unique(nullptr, tb, runs[0].p, bufs[into], d_nu.p, runs[0].n, stream);
+                    DevBuf<unsigned char> tmp;
+                    tmp.alloc(tb);
+                    TGBM_CUDA(cub::DeviceSelect::Unique(tmp.p, tb, runs[0].p, bufs[into], d_nu.p, runs[0].n, stream));
+                    TGBM_CUDA(cudaMemcpyAsync(&nu, d_nu.p, sizeof(long long), cudaMemcpyDeviceToHost, stream));
+                    TGBM_CUDA(cudaStreamSynchronize(stream));
+                    if (into == 1) std::swap(keys.p, keys2.p);   // the distinct keys are expected in `keys`
+                }
+            } else {
+                long long o = 0;
+                for (int r = 0; r < comm->world; ++r) {
+                    if (hc[r]) TGBM_CUDA(cudaMemcpyAsync(keys.p + o, all.p + (size_t)r * mx, sizeof(unsigned long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
+                    if (hc[r] && colb) TGBM_CUDA(cudaMemcpyAsync(copies.p + o, all_c.p + (size_t)r * mx, sizeof(long long) * hc[r], cudaMemcpyDeviceToDevice, stream));
+                    o += hc[r];
+                }
+                nu = sort_unique(tot);
             }
-            nu = sort_unique(tot);
-            lap("  sort + unique of the union");
+            lap("  union of the ranks' keys");
         }
         ukeys.alloc(std::max<long long>(nu, 1));
         if (nu) TGBM_CUDA(cudaMemcpyAsync(ukeys.p, keys.p, sizeof(unsigned long long) * nu, cudaMemcpyDeviceToDevice, stream));
