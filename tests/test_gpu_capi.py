@@ -108,7 +108,7 @@ def test_errors_leave_model_null(gpu, cases):
     lib.sparse_train_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(y), 5, 2, 1, 1.0, 1.0, 1.0, 64, 0, 1.0, 0, 1, 0.3,
                             b'reg:linear', C.byref(nc), b'approx', C.byref(model), C.byref(per), gl, None, 0)
     assert model.value is None and b'tree_method' in lib.tgbm_last_error()
-    # the exact builder runs on one GPU only
+    # an objective the library does not know
     model = C.c_void_p(123)
     lib.sparse_train_scikit(d.n_rows, _vp(val), _vp(rp), _vp(col), _vp(y), 5, 2, 1, 1.0, 1.0, 1.0, 64, 0, 1.0, 0, 1, 0.3,
                             b'reg:nonsense', C.byref(nc), b'exact', C.byref(model), C.byref(per), gl, None, 0)

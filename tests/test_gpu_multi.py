@@ -186,18 +186,21 @@ def test_column_builder_through_the_reference_entry_point(gpu, cases, monkeypatc
     assert threshold.tobytes() == t[0, 0]['split_value'].tobytes()
 
 
-def test_exact_builder_on_two_devices_is_refused_by_every_rank(gpu, cases):
-    """tree_method=exact runs on one GPU: with n_device=2 both host threads raise the same error before any collective
-    that only one of them would join, and the call returns it."""
+def test_exact_builder_ignores_n_device(gpu, cases, monkeypatch):
+    """tree_method=exact trains on one GPU: a call with n_device=2 returns what n_device=1 returns (the reference's
+    column-sharded exact builder has the same candidates on any number of devices)."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip('needs 2 GPUs')
+    monkeypatch.setenv('TGBM_HIST_MODE', 'exact')   # integer sums: two runs give the same bits
     d, params = cases('fixture_reg')
-    out, err = _scikit_train(d, 2, 3, 1, 'reg:linear', 1.0, tree_method=b'exact')
-    assert out is None and 'one GPU' in err
-    # and the next call on the same devices works (the failed call's communicators were dropped)
-    out, err = _scikit_train(d, 2, 3, 1, 'reg:linear', 1.0)
-    assert out is not None, err
+    two, err = _scikit_train(d, 2, 3, 2, 'reg:linear', 1.0, tree_method=b'exact')
+    assert two is not None, err
+    one, err = _scikit_train(d, 1, 3, 2, 'reg:linear', 1.0, tree_method=b'exact')
+    assert one is not None, err
+    assert one == two
+    hist, err = _scikit_train(d, 2, 3, 2, 'reg:linear', 1.0)
+    assert hist is not None and hist != two   # and it was the exact builder that ran
 
 
 def test_n_device_beyond_the_visible_gpus_is_refused(gpu, cases):
@@ -218,3 +221,6 @@ def test_bad_query_groups_on_one_rank_stop_every_rank(gpu, cases):
     bad.group[-1] += 5   # the last rank's groups no longer add up to its rows
     out, err = _scikit_train(bad, 2, 4, 2, 'rank:ndcg', 0.3)
     assert out is None and 'group sizes' in err
+    # and the next call on the same devices works (the failed call's communicators were dropped)
+    out, err = _scikit_train(d, 2, 4, 2, 'rank:ndcg', 0.3)
+    assert out is not None, err

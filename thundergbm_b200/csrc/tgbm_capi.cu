@@ -255,6 +255,15 @@ std::vector<std::vector<Tree>> train_model(GBMParam &p, const DataSet &ds) {
     // TGBM_COLUMN_BUILDER=1: n_device = D > 1 also selects what the reference's D-device builder computes
     if (const char *e = getenv("TGBM_COLUMN_BUILDER"))
         if (*e && strcmp(e, "0") && p.n_device > 1 && p.column_shards == 0) p.column_shards = p.n_device;
+    if (p.n_device > 1) {
+        // the exact builder (asked for, or what "auto" means above 20000 columns, trainer.cu:19-23) runs on one GPU
+        bool exact = p.tree_method == "exact";
+        if (p.tree_method == "auto") exact = (ds.n_features >= 0 ? ds.n_features : ds.count_features()) > 20000;
+        if (exact) {
+            log_info("tree_method = exact trains on one GPU; n_device = %d is not used", p.n_device);
+            return train(p, ds, nullptr);
+        }
+    }
     return p.n_device > 1 ? train_in_process(p, ds, p.n_device) : train(p, ds, nullptr);
 }
 void set_last_error(const std::string &msg) { g_err = msg; }

@@ -134,6 +134,7 @@ struct DataSet {
     void load_from_sparse(int n, const float *v, const int *rp, const int *ci, const float *yy, const int *grp,
                           int num_group, GBMParam &param, bool lazy = false);
     void distinct_labels(const float *yy, size_t n);
+    int count_features() const;   // largest column index + 1, scanned by a few host threads
     void load_from_file(const std::string &file, GBMParam &param);
     void load_group_file(const std::string &file);
     void group_label();

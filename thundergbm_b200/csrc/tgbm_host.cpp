@@ -45,20 +45,7 @@ void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *
     group.clear();
     // n_features = largest column index + 1 (dataset.cpp:54-57), scanned by a few threads
     n_features = -1;
-    if (!lazy) {
-        const int nt = (int)std::max<long long>(1, std::min<long long>(16, nnz / (1 << 22)));
-        std::vector<int> part(nt, 0);
-        std::vector<std::thread> th;
-        for (int t = 0; t < nt; ++t)
-            th.emplace_back([&, t] {
-                const long long a = nnz * t / nt, b = nnz * (t + 1) / nt;
-                int m = 0;
-                for (long long i = a; i < b; ++i) m = std::max(m, ci[i]);
-                part[t] = m;
-            });
-        for (auto &x : th) x.join();
-        n_features = *std::max_element(part.begin(), part.end()) + 1;
-    }
+    if (!lazy) n_features = count_features();
     const int o = objective_from_name(param.objective);
     if (yy && need_group_label(o)) {
         if (borrow) { distinct_labels(yy, (size_t)n); labels_raw = true; }
@@ -67,6 +54,22 @@ void DataSet::load_from_sparse(int n, const float *v, const int *rp, const int *
     }
     if (need_group_file(o))
         for (int i = 0; i < num_group; ++i) group.push_back(grp[i]);
+}
+
+int DataSet::count_features() const {
+    const long long nnz = rp ? rp[n_rows] : 0;
+    const int nt = (int)std::max<long long>(1, std::min<long long>(16, nnz / (1 << 22)));
+    std::vector<int> part(nt, -1);
+    std::vector<std::thread> th;
+    for (int t = 0; t < nt; ++t)
+        th.emplace_back([&, t] {
+            const long long a = nnz * t / nt, b = nnz * (t + 1) / nt;
+            int m = -1;
+            for (long long i = a; i < b; ++i) m = std::max(m, ci[i]);
+            part[t] = m;
+        });
+    for (auto &x : th) x.join();
+    return *std::max_element(part.begin(), part.end()) + 1;
 }
 
 // src/thundergbm/dataset.cpp:83-101: labels cast to int, sorted, uniqued; y -> index of its value
