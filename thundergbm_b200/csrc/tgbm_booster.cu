@@ -327,12 +327,12 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             if (colb) {  // ... and copies -> copies (summed over equal keys)
                 cub::DeviceRadixSort::SortPairs(nullptr, tb, keys.p, keys2.p, copies.p, copies2.p, (long long)n, 0, end_bit, stream);
                 DevBuf<unsigned char> tmp;
-                tmp.alloc(tb);
+                tmp.alloc(std::max<size_t>(tb, 16));
                 cub::DeviceRadixSort::SortPairs(tmp.p, tb, keys.p, keys2.p, copies.p, copies2.p, (long long)n, 0, end_bit, stream);
                 size_t tb2 = 0;
                 cub::DeviceReduce::ReduceByKey(nullptr, tb2, keys2.p, keys.p, copies2.p, copies.p, d_nu.p, cub::Sum(), (long long)n, stream);
                 DevBuf<unsigned char> tmp2;
-                tmp2.alloc(tb2);
+                tmp2.alloc(std::max<size_t>(tb2, 16));
                 cub::DeviceReduce::ReduceByKey(tmp2.p, tb2, keys2.p, keys.p, copies2.p, copies.p, d_nu.p, cub::Sum(), (long long)n, stream);
                 long long r = 0;
                 TGBM_CUDA(cudaMemcpyAsync(&r, d_nu.p, sizeof(long long), cudaMemcpyDeviceToHost, stream));
@@ -341,12 +341,12 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
             }
             cub::DeviceRadixSort::SortKeys(nullptr, tb, keys.p, keys2.p, (long long)n, 0, end_bit, stream);
             DevBuf<unsigned char> tmp;
-            tmp.alloc(tb);
+            tmp.alloc(std::max<size_t>(tb, 16));
             cub::DeviceRadixSort::SortKeys(tmp.p, tb, keys.p, keys2.p, (long long)n, 0, end_bit, stream);
             size_t tb2 = 0;
             cub::DeviceSelect::Unique(nullptr, tb2, keys2.p, keys.p, d_nu.p, (long long)n, stream);
             DevBuf<unsigned char> tmp2;
-            tmp2.alloc(tb2);
+            tmp2.alloc(std::max<size_t>(tb2, 16));
             cub::DeviceSelect::Unique(tmp2.p, tb2, keys2.p, keys.p, d_nu.p, (long long)n, stream);
             long long r = 0;
             TGBM_CUDA(cudaMemcpyAsync(&r, d_nu.p, sizeof(long long), cudaMemcpyDeviceToHost, stream));
@@ -427,7 +427,7 @@ void BoosterImpl::find_cuts_and_bins(const DataSet &ds) {
                     size_t tb = 0;
                     cub::DeviceSelect::Unique(nullptr, tb, runs[0].p, bufs[into], d_nu.p, runs[0].n, stream);
                     DevBuf<unsigned char> tmp;
-                    tmp.alloc(tb);
+                    tmp.alloc(std::max<size_t>(tb, 16));
                     TGBM_CUDA(cub::DeviceSelect::Unique(tmp.p, tb, runs[0].p, bufs[into], d_nu.p, runs[0].n, stream));
                     TGBM_CUDA(cudaMemcpyAsync(&nu, d_nu.p, sizeof(long long), cudaMemcpyDeviceToHost, stream));
                     TGBM_CUDA(cudaStreamSynchronize(stream));
