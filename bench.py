@@ -271,6 +271,8 @@ def e2e_child(args):
     full = make_shard(args.config, n_rows, 0, 1)[0]
 
     def pin(a, dt):  # the caller's CSR sits in pinned host memory (page-locked once, outside the timed region)
+        if args.e2e_pageable:  # ... or stays pageable, as the arrays of a NumPy caller are
+            return np.ascontiguousarray(a, dt)
         return torch.from_numpy(np.ascontiguousarray(a, dt)).pin_memory().numpy()
     val = pin(full.val, np.float32); rp = pin(full.row_ptr, np.int32)
     col = pin(full.col, np.int32); y = pin(full.y, np.float32)
@@ -308,7 +310,7 @@ def e2e_child(args):
                       'd2h_bytes_per_step': d2h / n, 'calls_s': times, 'rounds_per_call': n,
                       'hist_mode': 'fp32 (library default on this entry point)',
                       'note': f'median wall clock of {len(times)} calls of sparse_train_scikit(n_device={world}) with {n} rounds each, '
-                              f'CSR in pinned host memory; the calls run in a child process of rank 0'}), flush=True)
+                              f'CSR in {"pageable" if args.e2e_pageable else "pinned"} host memory; the calls run in a child process of rank 0'}), flush=True)
 
 
 def main():
@@ -326,6 +328,7 @@ def main():
     ap.add_argument('--no-e2e', action='store_true')
     ap.add_argument('--no-predict', action='store_true')
     ap.add_argument('--e2e-child', action='store_true', help=argparse.SUPPRESS)
+    ap.add_argument('--e2e-pageable', action='store_true', help='end-to-end leg with the host CSR in pageable memory instead of pinned')
     ap.add_argument('--e2e-timeout', type=float, default=300.0, help='seconds the end-to-end leg may take before it is given up')
     args = ap.parse_args()
     if args.e2e_child:
@@ -480,7 +483,7 @@ def main():
             store.wait(['tgbm_e2e_done'], datetime.timedelta(seconds=3600))
         if rank == 0:
             cmd = [sys.executable, os.path.abspath(__file__), '--e2e-child', '--config', args.config, '--rows', str(n_rows), '--gpus', str(world),
-                   '--steps', str(k), '--e2e-repeats', str(args.e2e_repeats)]
+                   '--steps', str(k), '--e2e-repeats', str(args.e2e_repeats)] + (['--e2e-pageable'] if args.e2e_pageable else [])
             env = {key: v for key, v in os.environ.items() if key not in ('RANK', 'LOCAL_RANK', 'WORLD_SIZE', 'MASTER_ADDR', 'MASTER_PORT',
                                                                           'TORCHELASTIC_RUN_ID', 'GROUP_RANK', 'ROLE_RANK', 'LOCAL_WORLD_SIZE')}
             try:

@@ -162,9 +162,11 @@ static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) 
 void BoosterImpl::upload_csr(const DataSet &ds) {
     const size_t nnz = (size_t)ds.rp[N];
     d_row_ptr.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1));
-    TGBM_CUDA(cudaMemcpyAsync(d_row_ptr.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, stream));
-    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, stream));
-    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, stream));
+    // host threads that stage a pageable source (fewer per rank when the ranks of one process upload side by side)
+    const int up_threads = comm && comm->active() ? std::max(1, upload_threads() / comm->world) : upload_threads();
+    upload_h2d(d_row_ptr.p, ds.rp, sizeof(int) * (size_t)(N + 1), stream, up_threads);
+    upload_h2d(d_col.p, ds.ci, sizeof(int) * nnz, stream, up_threads);
+    upload_h2d(d_val.p, ds.vv, sizeof(float) * nnz, stream, up_threads);
     // Largest and smallest column index, found here at HBM speed: the largest gives the feature count when the caller
     // did not count (dataset.cpp:54-57), a negative one would send the binning kernels out of bounds.
     const bool count_features = F < 0;
@@ -786,7 +788,7 @@ void Booster::init(const DataSet &ds) {
     const int N = m.N, K = m.K, depth = m.depth;
     const size_t n1 = std::max<size_t>(N, 1);
     m.y.alloc(n1); m.ypred.alloc(n1 * K); m.gh.alloc(n1 * K); m.ghq.alloc(n1 * K);
-    TGBM_CUDA(cudaMemcpyAsync(m.y.p, ds.yv ? ds.yv : ds.y.data(), sizeof(float) * N, cudaMemcpyHostToDevice, m.stream));
+    upload_h2d(m.y.p, ds.yv ? ds.yv : ds.y.data(), sizeof(float) * (size_t)N, m.stream, std::min(4, upload_threads()));
     if (ds.labels_raw && N) {  // label value -> class index (dataset.cpp:83-101), on the device
         DevBuf<float> d_label;
         d_label.alloc(std::max<size_t>(ds.label.size(), 1));

@@ -22,6 +22,10 @@ void *dev_alloc(size_t bytes);
 void dev_free(void *p) noexcept;
 void dev_trim() noexcept;
 void dev_release_all() noexcept;
+// host -> device copy that also runs at the speed of the link when the source is pageable memory (then it returns
+// when the data is on the device; from page-locked memory it is cudaMemcpyAsync on `stream`)
+void upload_h2d(void *dst, const void *src, size_t bytes, cudaStream_t stream, int n_threads);
+int upload_threads();   // host threads one upload may use: TGBM_UPLOAD_THREADS, else half of the cores, at most 8
 
 // RAII device buffer; everything is allocated once at init and reused for every tree.
 template <typename T>

@@ -19,10 +19,12 @@
 
 #include <algorithm>
 #include <cstdlib>
+#include <cstring>
 #include <iterator>
 #include <map>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <unordered_map>
 #include <vector>
 
@@ -160,7 +162,121 @@ static void trim_all(size_t keep, bool only_dirty) noexcept {
     if (cur >= 0) cudaSetDevice(cur);
 }
 
+// ---- large host -> device copies ---------------------------------------------------------------------------------
+// cudaMemcpyAsync from pageable memory (what a NumPy caller hands over) is staged by the driver through one small
+// pinned buffer: 10.8 GB/s measured for the 2.4 GB of a Higgs-sized CSR, a fifth of what the link carries from pinned
+// memory (page-locking the caller's arrays in place with cudaHostRegister runs at 11 GB/s too).  upload_h2d does the staging itself: a few host threads copy 8 MB pieces into page-locked slots (two per
+// thread, kept for the next call) and send each slot on with cudaMemcpyAsync on the thread's own stream.  Page-locked
+// or registered sources, and small copies, go to cudaMemcpyAsync directly.
+namespace {
+
+constexpr size_t STAGE_BYTES = 8u << 20;
+constexpr int STAGE_KEEP = 16;   // slots that stay allocated between calls (128 MB)
+
+std::mutex g_stage_mutex;
+std::vector<void *> g_stage_free;
+
+void *stage_acquire() {
+    {
+        std::lock_guard<std::mutex> lock(g_stage_mutex);
+        if (!g_stage_free.empty()) { void *p = g_stage_free.back(); g_stage_free.pop_back(); return p; }
+    }
+    void *p = nullptr;
+    if (cudaHostAlloc(&p, STAGE_BYTES, cudaHostAllocPortable) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return p;
+}
+
+void stage_release(void *p) {
+    if (!p) return;
+    {
+        std::lock_guard<std::mutex> lock(g_stage_mutex);
+        if ((int)g_stage_free.size() < STAGE_KEEP) { g_stage_free.push_back(p); return; }
+    }
+    cudaFreeHost(p);
+}
+
+bool host_is_pageable(const void *p) {
+    cudaPointerAttributes attr = {};
+    if (cudaPointerGetAttributes(&attr, p) != cudaSuccess) { cudaGetLastError(); return true; }
+    return attr.type == cudaMemoryTypeUnregistered;
+}
+
+}  // namespace
+
+int upload_threads() {
+    static const int n = [] {
+        if (const char *e = getenv("TGBM_UPLOAD_THREADS")) return std::max(1, std::min(STAGE_KEEP / 2, atoi(e)));
+        const int hw = (int)std::thread::hardware_concurrency();
+        return std::max(1, std::min(8, hw / 2));   // 16 cores: 4 / 6 / 8 threads bring 2.4 GB over in 100 / 82 / 65 ms, 12 and more in 0.2-1.2 s
+    }();
+    return n;
+}
+
+void upload_h2d(void *dst, const void *src, size_t bytes, cudaStream_t stream, int n_threads) {
+    if (bytes == 0) return;
+    static const bool staged = getenv("TGBM_NO_STAGED_UPLOAD") == nullptr;
+    if (!staged || bytes < 4 * STAGE_BYTES || n_threads < 1 || !host_is_pageable(src)) {
+        TGBM_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, stream));
+        return;
+    }
+    int dev = 0;
+    TGBM_CUDA(cudaGetDevice(&dev));
+    const size_t n_chunks = (bytes + STAGE_BYTES - 1) / STAGE_BYTES;
+    const int T = (int)std::min<size_t>((size_t)n_threads, n_chunks);
+    std::vector<std::string> errors(T);
+    std::vector<std::thread> workers;
+    for (int t = 0; t < T; ++t)
+        workers.emplace_back([&, t] {
+            void *slot[2] = {nullptr, nullptr};
+            cudaEvent_t done[2] = {nullptr, nullptr};
+            bool busy[2] = {false, false};
+            cudaStream_t st = nullptr;
+            auto check = [&](cudaError_t e, const char *what) {
+                if (e != cudaSuccess) { cudaGetLastError(); throw Error(std::string("CUDA error: ") + cudaGetErrorString(e) + " in " + what); }
+            };
+            try {
+                check(cudaSetDevice(dev), "cudaSetDevice");
+                check(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking), "cudaStreamCreate");
+                for (int k = 0; k < 2; ++k) {
+                    slot[k] = stage_acquire();
+                    if (!slot[k]) throw Error("no page-locked memory for the upload");
+                    check(cudaEventCreateWithFlags(&done[k], cudaEventDisableTiming), "cudaEventCreate");
+                }
+                int k = 0;
+                for (size_t c = t; c < n_chunks; c += T, k ^= 1) {
+                    const size_t off = c * STAGE_BYTES, len = std::min(STAGE_BYTES, bytes - off);
+                    if (busy[k]) check(cudaEventSynchronize(done[k]), "cudaEventSynchronize");
+                    memcpy(slot[k], static_cast<const char *>(src) + off, len);
+                    check(cudaMemcpyAsync(static_cast<char *>(dst) + off, slot[k], len, cudaMemcpyHostToDevice, st), "cudaMemcpyAsync");
+                    check(cudaEventRecord(done[k], st), "cudaEventRecord");
+                    busy[k] = true;
+                }
+                check(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+            } catch (const std::exception &e) {
+                errors[t] = e.what();
+                if (st) cudaStreamSynchronize(st);   // nothing may still read the slots when they go back
+            }
+            for (int k = 0; k < 2; ++k) {
+                if (done[k]) cudaEventDestroy(done[k]);
+                stage_release(slot[k]);
+            }
+            if (st) cudaStreamDestroy(st);
+        });
+    for (auto &w : workers) w.join();
+    for (const auto &e : errors)
+        if (!e.empty()) throw Error(e);
+    (void)stream;   // the pieces are on the device when the workers return: whatever is queued next sees them
+}
+
 void dev_trim() noexcept { trim_all(keep_bytes(), true); }
-void dev_release_all() noexcept { trim_all(0, false); }
+void dev_release_all() noexcept {
+    trim_all(0, false);
+    std::vector<void *> slots;
+    {
+        std::lock_guard<std::mutex> lock(g_stage_mutex);
+        slots.swap(g_stage_free);
+    }
+    for (void *p : slots) cudaFreeHost(p);
+}
 
 }  // namespace tgbm

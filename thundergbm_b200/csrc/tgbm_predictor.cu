@@ -683,9 +683,9 @@ void predict_raw(const DataSet &ds, const std::vector<std::vector<Tree>> &model,
     DevBuf<PNode> d_model;
     DevBuf<HNode> d_hmodel;
     d_rp.alloc(N + 1); d_col.alloc(std::max<size_t>(nnz, 1)); d_val.alloc(std::max<size_t>(nnz, 1)); d_out.alloc((size_t)N * K);
-    TGBM_CUDA(cudaMemcpyAsync(d_rp.p, ds.rp, sizeof(int) * (N + 1), cudaMemcpyHostToDevice, st));
-    TGBM_CUDA(cudaMemcpyAsync(d_col.p, ds.ci, sizeof(int) * nnz, cudaMemcpyHostToDevice, st));
-    TGBM_CUDA(cudaMemcpyAsync(d_val.p, ds.vv, sizeof(float) * nnz, cudaMemcpyHostToDevice, st));
+    upload_h2d(d_rp.p, ds.rp, sizeof(int) * (size_t)(N + 1), st, upload_threads());
+    upload_h2d(d_col.p, ds.ci, sizeof(int) * nnz, st, upload_threads());
+    upload_h2d(d_val.p, ds.vv, sizeof(float) * nnz, st, upload_threads());
     if (heap) {
         d_hmodel.alloc(hflat.size());
         TGBM_CUDA(cudaMemcpyAsync(d_hmodel.p, hflat.data(), sizeof(HNode) * hflat.size(), cudaMemcpyHostToDevice, st));
