@@ -284,3 +284,38 @@ def test_released_buffers_are_kept_and_given_back_on_request(gpu, cases):
     lib.get_n_nodes(C.byref(m2), C.byref(n2), 3, per)
     assert n1.value == n2.value
     lib.model_free(C.byref(m1)); lib.model_free(C.byref(m2))
+
+
+def test_pageable_and_page_locked_arrays_give_the_same_model(gpu, monkeypatch):
+    """Arrays of more than 32 MB in pageable memory travel through the library's own staging slots (several host threads,
+    pieces of 8 MB, the last one ragged), page-locked ones through one cudaMemcpyAsync: same trees, same predictions."""
+    import torch
+    from thundergbm_b200 import _lib
+    from thundergbm_b200.synth import CsrData
+    lib = _lib.lib()
+    monkeypatch.setenv('TGBM_HIST_MODE', 'exact')     # integer sums: the two runs must agree to the bit
+    rng = np.random.default_rng(3)
+    n, f = 1_250_003, 8                                # 40 MB of values, 40 MB of column indices, odd sizes
+    x = rng.standard_normal((n, f)).astype(np.float32)
+    y = (x[:, 0] * x[:, 1] + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    rp = (np.arange(n + 1, dtype=np.int64) * f).astype(np.int32)
+    col = np.tile(np.arange(f, dtype=np.int32), n)
+    d = CsrData(n, f, rp, col, x.reshape(-1), y, np.zeros(0, np.int32))
+
+    def run(arrays):
+        val, rp_, col_, y_ = arrays
+        model = C.c_void_p(None); nc = C.c_int(1); per = C.c_int(0); gl = (C.c_float * 4)()
+        lib.sparse_train_scikit(n, _vp(val), _vp(rp_), _vp(col_), _vp(y_), 5, 3, 1, 1.0, 1.0, 1.0, 64, 0, 1.0, 0, 1, 0.3,
+                                b'reg:linear', C.byref(nc), b'hist', C.byref(model), C.byref(per), gl, None, 0)
+        assert model.value, lib.tgbm_last_error().decode()
+        out = np.zeros(n, np.float32)
+        lib.sparse_predict_scikit(n, _vp(val), _vp(rp_), _vp(col_), _vp(out), C.byref(model), 3, 1, b'reg:linear', 1, 0.3,
+                                  gl, None, 0, 0)
+        lib.model_free(C.byref(model))
+        return out
+
+    pageable = (d.val, d.row_ptr, d.col, d.y)
+    locked = tuple(torch.from_numpy(a).pin_memory().numpy() for a in pageable)
+    a, b = run(pageable), run(locked)
+    assert np.array_equal(a, b)
+    assert np.std(a) > 0.1    # and the model learnt something from the data it was given
