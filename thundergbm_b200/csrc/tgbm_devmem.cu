@@ -45,7 +45,9 @@ struct DeviceCache {
     bool dirty = false;                               // something was released since the last trim
 };
 
-DeviceCache g_cache[MAX_DEVICES];
+// never destroyed: a buffer may be released while the process exits (a binding's finaliser, a static object of the
+// host program), after the static destructors of this file would have run
+DeviceCache *const g_cache = new DeviceCache[MAX_DEVICES];
 
 bool cache_enabled() {
     static const bool on = getenv("TGBM_NO_POOL") == nullptr;
@@ -173,8 +175,8 @@ namespace {
 constexpr size_t STAGE_BYTES = 8u << 20;
 constexpr int STAGE_KEEP = 16;   // slots that stay allocated between calls (128 MB)
 
-std::mutex g_stage_mutex;
-std::vector<void *> g_stage_free;
+std::mutex &g_stage_mutex = *new std::mutex;
+std::vector<void *> &g_stage_free = *new std::vector<void *>;
 
 void *stage_acquire() {
     {
